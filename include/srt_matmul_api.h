@@ -1,0 +1,188 @@
+/*
+ * srt_matmul_api.h -- C ABI of the B200 (sm_100a) matmul / batched matmul / Dense path.
+ *
+ * A sibling of the reference's Modules/SwiftRTCuda/*_api.h headers: every operator is
+ *     cudaError_t srtOp(const void* a, const srtTensorDescriptor* aDesc, ...,
+ *                       void* out, const srtTensorDescriptor* oDesc, cudaStream_t stream);
+ * (Modules/SwiftRTCuda/math_api.h:75-87).  Pointers are device addresses of the first
+ * element of the view; descriptors and their arrays only need to live for the call;
+ * work is enqueued on `stream` and the call returns without synchronising.
+ * cudaErrorNotSupported means "this dtype / layout is outside this library" (the Swift
+ * caller then takes its own CPU route, cuda/device/CudaPlatform.swift:135-144); any
+ * other non-zero code is an error.  The library has no CPU fallback and calls no
+ * cuBLAS / cublasLt.
+ */
+#ifndef SRT_MATMUL_API_H
+#define SRT_MATMUL_API_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include <stdbool.h>
+
+#ifdef SRT_MATMUL_NO_CUDA_HEADERS
+/* for FFI generators that cannot see the CUDA toolkit: same ABI */
+typedef int cudaError_t;
+typedef struct CUstream_st* cudaStream_t;
+#else
+#include <cuda_runtime_api.h>
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------------------------
+ * Data types.  Values equal the reference's srtDataType, which aliases cudaDataType
+ * (Modules/SwiftRTCuda/tensor_api.h:31-38): CUDA_R_32F = 0, CUDA_R_16F = 2, CUDA_R_16BF = 14.
+ * Only these three are computed; every other value returns cudaErrorNotSupported.
+ */
+#ifndef SRT_TENSOR_API_TYPES
+#define SRT_TENSOR_API_TYPES
+typedef enum {
+    srtUnknownType = -1,
+    real32F  = 0,
+    real64F  = 1,
+    real16F  = 2,
+    real8I   = 3,
+    real16BF = 14
+} srtDataType;
+
+/* Storage order.  Values equal cublasLtOrder_t, which the reference's descriptor uses
+ * (tensor_api.h:76): CUBLASLT_ORDER_COL = 0, CUBLASLT_ORDER_ROW = 1.  Tiled orders
+ * (values >= 2) return cudaErrorNotSupported. */
+typedef enum {
+    srtOrderCol = 0,
+    srtOrderRow = 1
+} srtOrder;
+
+/* Replaces srtTensorDescriptor of Modules/SwiftRTCuda/tensor_api.h:70-87 field for field
+ * (`order` keeps the width and values of cublasLtOrder_t, so the struct layout is equal).
+ * `shape`, `strides` and `logicalStrides` have `rank` entries; strides are in elements.
+ * The matmul entry points read type, rank, shape and strides only: majorness and leading
+ * dimensions are derived from strides[], never from `order` (for col order the reference's
+ * Tensor.leadingDimension, cuda/device/CudaPlatform.swift:298-311, would be 1). */
+typedef struct {
+    srtDataType type;
+    uint32_t rank;
+    srtOrder order;
+    size_t count;
+    size_t spanCount;
+    const size_t* shape;
+    const size_t* strides;
+    const size_t* logicalStrides;
+} srtTensorDescriptor;
+#endif
+
+/* Raw values equal ActivationType (Sources/SwiftRTCore/platform/common/
+ * FunctionProperties.swift:44-51).  srtActivationGelu / GeluTanh are additions (the
+ * reference enum has no GELU).  clippedRelu and elu take coefficients the Dense layer
+ * never supplies and return cudaErrorNotSupported. */
+typedef enum {
+    srtActivationSigmoid     = 0,
+    srtActivationRelu        = 1,
+    srtActivationTanh        = 2,
+    srtActivationClippedRelu = 3,
+    srtActivationElu         = 4,
+    srtActivationIdentity    = 5,
+    srtActivationGelu        = 6,
+    srtActivationGeluTanh    = 7
+} srtActivationType;
+
+/* ---------------------------------------------------------------------------------------
+ * srtMatmul: out = op(a) . op(b), fp32 accumulation, one rounding to the element type.
+ *
+ * Replaces the bodies of CudaQueue.matmul for TensorR2 and TensorR3
+ * (Sources/SwiftRTCore/platform/cuda/functions/CudaMatmul.swift:25-42 and :44-61, which
+ * today always run the CPU loop CpuMath.swift:1141-1186) and with them the cublasLt
+ * descriptor plumbing under platform/cuda/cublaslt/.
+ *
+ * rank 2: a [M x K] (or [K x M] when transA), b [K x N] (or [N x K] when transB), out [M x N].
+ * rank 3: dimension 0 is the batch (shape[0] of `out`); an input whose shape[0] is 1 or
+ *         whose strides[0] is 0 is broadcast over the batch.  An input may also be rank 2
+ *         while `out` is rank 3 (the reference's left/right batch forms).
+ * All three tensors have the same `type`.  Any non-negative element strides are accepted:
+ * views that meet the TMA rules (16-byte aligned base, one unit stride in the last two
+ * dims, the other strides multiples of 16 bytes) run on the tensor-core kernel, the rest
+ * on a strided SIMT kernel.  `out` is write-only, may be a strided view, and must not
+ * alias an input.  Inputs may alias each other.
+ */
+cudaError_t srtMatmul(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    void* out, const srtTensorDescriptor* oDesc,
+    cudaStream_t stream);
+
+/* srtMatmulBiasActivation: out = activation(op(a) . op(b) + bias), bias broadcast along
+ * rows (bias[n] is added to column n), everything after the dot product in fp32 with one
+ * final rounding.  `bias` may be NULL (then biasDesc is ignored); it is rank 1 with N
+ * elements and the same `type` as the other tensors.
+ *
+ * Supplies what matmul(_:transposed:_:transposed:bias:) declares but does not compute
+ * (Sources/SwiftRTCore/operators/Matmul.swift:57-72 drops the bias at :70) and what
+ * Dense.callAsFunction declares (Sources/SwiftRTLayers/Dense.swift:21-40 returns its
+ * input); the fused epilogue stands in for MatmulEpilogue {none, relu, bias, biasRelu}
+ * (platform/cuda/cublaslt/MatmulOperation.swift:384-411) and for the separate cuDNN
+ * activation call (platform/cuda/layers/CudaActivation.swift:61-83).
+ */
+cudaError_t srtMatmulBiasActivation(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* bias, const srtTensorDescriptor* biasDesc,
+    srtActivationType activation,
+    void* out, const srtTensorDescriptor* oDesc,
+    cudaStream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Plan query and tuning knobs.  Stand in for MatmulAlgorithm.query / .search
+ * (platform/cuda/cublaslt/MatmulAlgorithmSearch.swift:51-100, 128-216), MatmulTile /
+ * MatmulStages (MatmulAlgorithm.swift:593-800) and MatmulPreferences.maxWorkspaceSize
+ * (MatmulPreferences.swift:85-254).
+ */
+typedef enum {
+    srtMatmulKernelNone    = 0,
+    srtMatmulKernelSimt    = 1,   /* strided SIMT kernel, fp32 FMA */
+    srtMatmulKernelTcgen05 = 2,   /* TMA + tcgen05 tensor-core kernel, one CTA per tile */
+    srtMatmulKernelTcgen05Pair = 3 /* TMA + tcgen05 cta_group::2 kernel, CTA pair per tile */
+} srtMatmulKernel;
+
+typedef struct {
+    int32_t kernel;        /* srtMatmulKernel that a call with these arguments launches */
+    int32_t tileM, tileN, tileK;
+    int32_t stages;        /* shared-memory pipeline depth */
+    int32_t ctas;          /* grid size (persistent CTAs) */
+    int32_t tiles;         /* output tiles over all batch items */
+    int32_t swapped;       /* 1 when computed as out^T = op(b)^T . op(a)^T (col-order out) */
+    int32_t aMajor, bMajor;/* 0 = K-major, 1 = MN-major operand as the kernel sees it */
+    int32_t fp32Split;     /* 1 when fp32 runs as 3 x TF32 on the tensor cores */
+    size_t  workspaceBytes;/* device scratch the call needs: always 0 */
+    size_t  dynamicSmemBytes;
+} srtMatmulPlan;
+
+/* Fills `plan` with what srtMatmulBiasActivation would launch for these descriptors and
+ * pointers (alignment matters, so the pointers are part of the key).  Launches nothing. */
+cudaError_t srtMatmulQueryPlan(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* out, const srtTensorDescriptor* oDesc,
+    srtMatmulPlan* plan);
+
+/* Process-wide overrides, 0 = automatic.  forceKernel: an srtMatmulKernel value (a forced
+ * tensor-core kernel still falls back to SIMT for views that TMA cannot address);
+ * tileN: 64, 128 or 256; stages: 2..8; maxCtas: cap on the persistent grid. */
+cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas);
+
+/* Device-side status of the last tensor-core launches on the current device: 0 = all
+ * pipeline waits completed; non-zero = a bounded wait gave up (the code says which) and
+ * the result of that launch is invalid.  Synchronises `stream` and resets the status. */
+cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status);
+
+/* Number of kernels this library has launched since it was loaded (all streams). */
+uint64_t srtMatmulLaunchCount(void);
+
+/* Text of the last argument error on the calling thread ("" when none). */
+const char* srtMatmulGetLastErrorString(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SRT_MATMUL_API_H */

@@ -1,0 +1,70 @@
+"""ctypes binding of libsrt_b200.so (the C ABI declared in include/srt_matmul_api.h).
+
+There is no fallback: if the compiled CUDA library is missing, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+SO = os.path.join(PKG, "libsrt_b200.so")
+
+cudaSuccess = 0
+cudaErrorInvalidValue = 1
+cudaErrorNotSupported = 801
+
+
+class TensorDescriptor(ctypes.Structure):
+    """Field-for-field srtTensorDescriptor (Modules/SwiftRTCuda/tensor_api.h:70-87)."""
+    _fields_ = [("type", ctypes.c_int),
+                ("rank", ctypes.c_uint32),
+                ("order", ctypes.c_int),
+                ("count", ctypes.c_size_t),
+                ("spanCount", ctypes.c_size_t),
+                ("shape", ctypes.POINTER(ctypes.c_size_t)),
+                ("strides", ctypes.POINTER(ctypes.c_size_t)),
+                ("logicalStrides", ctypes.POINTER(ctypes.c_size_t))]
+
+
+class MatmulPlan(ctypes.Structure):
+    """srtMatmulPlan."""
+    _fields_ = [("kernel", ctypes.c_int32),
+                ("tileM", ctypes.c_int32), ("tileN", ctypes.c_int32), ("tileK", ctypes.c_int32),
+                ("stages", ctypes.c_int32), ("ctas", ctypes.c_int32), ("tiles", ctypes.c_int32),
+                ("swapped", ctypes.c_int32), ("aMajor", ctypes.c_int32), ("bMajor", ctypes.c_int32),
+                ("fp32Split", ctypes.c_int32),
+                ("workspaceBytes", ctypes.c_size_t), ("dynamicSmemBytes", ctypes.c_size_t)]
+
+
+# every symbol include/srt_matmul_api.h declares
+EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning",
+           "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString"]
+
+if not os.path.exists(SO):
+    raise ImportError(
+        f"{SO} is missing: the CUDA library has not been built. Run "
+        "`python -m swiftrt_b200.build` (needs nvcc); there is no CPU or PyTorch fallback.")
+
+lib = ctypes.CDLL(SO)
+
+_D = ctypes.POINTER(TensorDescriptor)
+_P = ctypes.c_void_p
+lib.srtMatmul.restype = ctypes.c_int
+lib.srtMatmul.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, _P]
+lib.srtMatmulBiasActivation.restype = ctypes.c_int
+lib.srtMatmulBiasActivation.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_int, _P, _D, _P]
+lib.srtMatmulQueryPlan.restype = ctypes.c_int
+lib.srtMatmulQueryPlan.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.POINTER(MatmulPlan)]
+lib.srtMatmulSetTuning.restype = ctypes.c_int
+lib.srtMatmulSetTuning.argtypes = [ctypes.c_int32] * 4
+lib.srtMatmulCheckStatus.restype = ctypes.c_int
+lib.srtMatmulCheckStatus.argtypes = [_P, ctypes.POINTER(ctypes.c_uint32)]
+lib.srtMatmulLaunchCount.restype = ctypes.c_uint64
+lib.srtMatmulLaunchCount.argtypes = []
+lib.srtMatmulGetLastErrorString.restype = ctypes.c_char_p
+lib.srtMatmulGetLastErrorString.argtypes = []
+
+
+def last_error() -> str:
+    return lib.srtMatmulGetLastErrorString().decode()

@@ -1,0 +1,339 @@
+// Tensor-core GEMM for sm_100a: one CTA per 128 x BN output tile, persistent over tiles.
+//
+//   warp 0      TMA producer: fills a ring of shared-memory stages (A tile + B tile, 128-byte
+//               swizzled rows) with cp.async.bulk.tensor loads, one mbarrier per stage.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 32 bytes of K per
+//               instruction) from the shared-memory descriptors into a TMEM accumulator;
+//               tcgen05.commit hands each stage back to the producer and each finished
+//               accumulator to the epilogue.  Also owns the TMEM allocation.
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (each warp its 32 TMEM lanes),
+//               add bias, apply the activation, round once to the output type, store.
+//
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i
+// overlaps the main loop of tile i + 1.  Operands may be K-major (K contiguous) or
+// MN-major (M or N contiguous); the difference is confined to the TMA box shapes and the
+// descriptor fields the host prepares in GemmParams.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace srt {
+
+constexpr uint32_t kTileM = 128;        // rows of one MMA (all 128 TMEM lanes)
+constexpr uint32_t kRowBytes = 128;     // swizzle span = bytes of one shared-memory tile row
+constexpr uint32_t kATileBytes = kTileM * kRowBytes;
+constexpr uint32_t kKStepsPerStage = 4; // MMAs per stage: each consumes 32 bytes of K
+constexpr uint32_t kGemmThreads = 192;
+
+enum : uint32_t {
+    kStatusProducerTimeout = 1u,
+    kStatusMmaTimeout = 2u,
+    kStatusEpilogueTimeout = 4u,
+    kStatusPairTimeout = 8u
+};
+
+// Status word of the tensor-core kernels, one per device that loads the module.
+__device__ uint32_t g_gemm_status;
+
+struct OperandParams {
+    uint32_t mn_major;      // 0: K contiguous, 1: M/N contiguous
+    uint32_t chunks;        // TMA boxes per stage (1 for K-major)
+    uint32_t chunk_elems;   // M/N elements per box (MN-major)
+    uint32_t chunk_bytes;   // shared-memory bytes per box
+    uint32_t batch_mul;     // 0 broadcasts the operand over the batch
+    uint32_t desc_hi;       // upper half of the shared-memory matrix descriptor
+    uint32_t desc_lo_fixed; // leading-byte-offset field, already shifted
+    uint32_t kstep;         // descriptor start-address increment per MMA (bytes >> 4)
+};
+
+struct GemmParams {
+    uint32_t M, N, K, batch;
+    uint32_t tiles_m, tiles_n, tiles_per_batch, num_tiles;
+    uint32_t k_blocks, kb_elems, group_m;
+    OperandParams a, b;
+    uint32_t idesc;
+    uint32_t stage_tx_bytes;
+    uint32_t stages;
+    // epilogue
+    void* out;
+    long long ldo;               // elements between output rows (columns are contiguous)
+    long long out_batch_stride;  // elements
+    const void* bias;
+    long long bias_stride;
+    uint32_t bias_mode;          // 0 none, 1 one value per column, 2 one value per row
+    uint32_t act;
+    uint32_t out_vec_ok;         // 16-byte vector stores are aligned for every full chunk
+};
+
+enum : uint32_t { kActSigmoid = 0, kActRelu = 1, kActTanh = 2, kActIdentity = 5, kActGelu = 6, kActGeluTanh = 7 };
+
+__device__ __forceinline__ float apply_activation(uint32_t act, float x)
+{
+    switch (act) {
+    case kActRelu: return x >= 0.0f ? x : 0.0f;
+    case kActSigmoid: return 1.0f / (1.0f + expf(-x));
+    case kActTanh: return tanhf(x);
+    case kActGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    case kActGeluTanh: {
+        float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.0f + tanhf(u));
+    }
+    default: return x;
+    }
+}
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi)
+{
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi)
+{
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// tile index -> (batch, first row, first column); m-tiles are visited in groups of group_m
+// so that the CTAs running at the same time share A and B tiles in L2.
+__device__ __forceinline__ void decode_tile(const GemmParams& p, uint32_t tile, uint32_t bn,
+                                            uint32_t& batch, uint32_t& m0, uint32_t& n0)
+{
+    batch = tile / p.tiles_per_batch;
+    uint32_t t = tile - batch * p.tiles_per_batch;
+    uint32_t per_group = p.group_m * p.tiles_n;
+    uint32_t group = t / per_group;
+    uint32_t first_m = group * p.group_m;
+    uint32_t gm = min(p.group_m, p.tiles_m - first_m);
+    uint32_t r = t - group * per_group;
+    m0 = (first_m + r % gm) * kTileM;
+    n0 = (r / gm) * bn;
+}
+
+// Stores 32 consecutive columns of one output row held as fp32 in v[].
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, OutT* row_ptr, uint32_t col0,
+                                                const float (&v)[32])
+{
+    if (p.out_vec_ok && col0 + 32 <= p.N) {
+        if constexpr (sizeof(OutT) == 4) {
+            float4* dst = reinterpret_cast<float4*>(row_ptr + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+            uint4* dst = reinterpret_cast<uint4*>(row_ptr + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 q;
+                q.x = pack2<OutT>(v[8 * j + 0], v[8 * j + 1]);
+                q.y = pack2<OutT>(v[8 * j + 2], v[8 * j + 3]);
+                q.z = pack2<OutT>(v[8 * j + 4], v[8 * j + 5]);
+                q.w = pack2<OutT>(v[8 * j + 6], v[8 * j + 7]);
+                dst[j] = q;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) row_ptr[col0 + j] = from_float<OutT>(v[j]);
+    }
+}
+
+// InT / OutT: element type of the inputs and of the output (float, __half, __nv_bfloat16).
+// BN: tile width (64, 128 or 256).  fp32 inputs are multiplied as TF32.
+template <typename T, uint32_t BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ GemmParams p)
+{
+    constexpr uint32_t kBTileBytes = BN * kRowBytes;
+    constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+    constexpr uint32_t kTmemCols = 2 * BN;
+    constexpr uint32_t kMaxStages = 8;
+
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tmem_full_bar[2];
+    __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t stages = p.stages;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&tmem_full_bar[i]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[i]), 4);   // one arrive per epilogue warp
+        }
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_cta1(smem_u32(&tmem_holder), kTmemCols);
+        tmem_relinquish_cta1();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                uint32_t batch, m0, n0;
+                decode_tile(p, tile, BN, batch, m0, n0);
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_bar[stage]);
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+                    const int32_t k0 = static_cast<int32_t>(kb * p.kb_elems);
+                    mbar_arrive_expect_tx(bar, p.stage_tx_bytes);
+                    if (!p.a.mn_major) {
+                        tma_load_3d(sa, &tmap_a, bar, k0, m0, batch * p.a.batch_mul);
+                    } else {
+                        for (uint32_t c = 0; c < p.a.chunks; ++c)
+                            tma_load_3d(sa + c * p.a.chunk_bytes, &tmap_a, bar, m0 + c * p.a.chunk_elems, k0,
+                                        batch * p.a.batch_mul);
+                    }
+                    if (!p.b.mn_major) {
+                        tma_load_3d(sb, &tmap_b, bar, k0, n0, batch * p.b.batch_mul);
+                    } else {
+                        for (uint32_t c = 0; c < p.b.chunks; ++c)
+                            tma_load_3d(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0,
+                                        batch * p.b.batch_mul);
+                    }
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                abort_flag = 1;
+                atomicOr(&g_gemm_status, kStatusProducerTimeout);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+                const uint32_t buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1;
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+                    const uint32_t a_lo = ((sa >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t b_lo = ((sb >> 4) & 0x3fffu) | p.b.desc_lo_fixed;
+#pragma unroll
+                    for (uint32_t k = 0; k < kKStepsPerStage; ++k) {
+                        const uint64_t adesc = (static_cast<uint64_t>(p.a.desc_hi) << 32) | (a_lo + k * p.a.kstep);
+                        const uint64_t bdesc = (static_cast<uint64_t>(p.b.desc_hi) << 32) | (b_lo + k * p.b.kstep);
+                        if constexpr (sizeof(T) == 4) umma_tf32_cta1(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+                        else                          umma_f16_cta1(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+                    }
+                    umma_commit_cta1(smem_u32(&empty_bar[stage]));
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit_cta1(smem_u32(&tmem_full_bar[buf]));
+            }
+            if (!ok) {
+                abort_flag = 1;
+                atomicOr(&g_gemm_status, kStatusMmaTimeout);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t quarter = warp & 3;       // TMEM lanes this warp may read
+        uint32_t local = 0;
+        bool ok = true;
+        T* const out = static_cast<T*>(p.out);
+        const T* const bias = static_cast<const T*>(p.bias);
+        for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+            uint32_t batch, m0, n0;
+            decode_tile(p, tile, BN, batch, m0, n0);
+            const uint32_t buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t row = m0 + quarter * 32 + lane;
+            T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
+            float row_bias = 0.0f;
+            if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                const uint32_t col0 = n0 + c * 32;
+                if (col0 >= p.N) break;                       // uniform over the warp
+                uint32_t raw[32];
+                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32, raw);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                if (p.bias_mode == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) v[j] += to_float<T>(__ldg(bias + static_cast<long long>(col0 + j) * p.bias_stride));
+                } else if (p.bias_mode == 2) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += row_bias;
+                }
+                if (p.act != kActIdentity) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = apply_activation(p.act, v[j]);
+                }
+                if (row < p.M) store_row_chunk<T>(p, row_ptr, col0, v);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+        }
+        if (!ok) {
+            abort_flag = 1;
+            if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        if (abort_flag != 0) __nanosleep(1000000);   // let copies and MMAs in flight drain
+        tmem_dealloc_cta1(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace srt

@@ -1,0 +1,537 @@
+// C ABI of the B200 matmul path: argument validation, plan selection, TMA descriptor
+// construction and kernel launches.  Declarations and the reference interfaces they replace
+// are in include/srt_matmul_api.h.
+#include "srt_matmul_api.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "gemm_simt.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace {
+
+using namespace srt;
+
+thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+struct Tuning {
+    std::atomic<int32_t> force_kernel{0}, tile_n{0}, stages{0}, max_ctas{0};
+} g_tuning;
+
+cudaError_t fail(cudaError_t code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// ------------------------------------------------------------------ problem description
+struct Problem {
+    srtDataType type;
+    uint32_t elem;                 // bytes per element
+    uint64_t batch, M, N, K;
+    const char* a; const char* b; char* out;
+    long long a_b, a_m, a_k;       // element strides of op(a): batch, row, reduction
+    long long b_b, b_k, b_n;
+    long long o_b, o_m, o_n;
+    const char* bias; long long bias_stride;
+    uint32_t act;
+};
+
+uint32_t elem_size(srtDataType t)
+{
+    switch (t) {
+    case real32F: return 4;
+    case real16F: case real16BF: return 2;
+    default: return 0;
+    }
+}
+
+cudaError_t parse(const void* a, const srtTensorDescriptor* ad, bool ta,
+                  const void* b, const srtTensorDescriptor* bd, bool tb,
+                  const void* bias, const srtTensorDescriptor* biasd, int act,
+                  const void* out, const srtTensorDescriptor* od, Problem& P)
+{
+    if (!a || !b || !out || !ad || !bd || !od) return fail(cudaErrorInvalidValue, "null tensor or descriptor");
+    if (!ad->shape || !ad->strides || !bd->shape || !bd->strides || !od->shape || !od->strides)
+        return fail(cudaErrorInvalidValue, "descriptor without shape or strides");
+    if (ad->type != od->type || bd->type != od->type)
+        return fail(cudaErrorInvalidValue, "a, b and out must have the same element type");
+    P.type = od->type;
+    P.elem = elem_size(P.type);
+    if (P.elem == 0) return fail(cudaErrorNotSupported, "element type %d is not computed by this library", (int)P.type);
+    if ((int)ad->order > 1 || (int)bd->order > 1 || (int)od->order > 1)
+        return fail(cudaErrorNotSupported, "tiled storage orders are not supported");
+    if (od->rank != 2 && od->rank != 3) return fail(cudaErrorNotSupported, "out must have rank 2 or 3");
+    if (ad->rank < 2 || ad->rank > od->rank || bd->rank < 2 || bd->rank > od->rank)
+        return fail(cudaErrorInvalidValue, "input rank must be 2 or the rank of out");
+
+    const uint32_t oq = od->rank - 2, aq = ad->rank - 2, bq = bd->rank - 2;
+    P.batch = od->rank == 3 ? od->shape[0] : 1;
+    P.M = od->shape[oq];
+    P.N = od->shape[oq + 1];
+    const uint64_t a_rows = ad->shape[aq], a_cols = ad->shape[aq + 1];
+    const uint64_t b_rows = bd->shape[bq], b_cols = bd->shape[bq + 1];
+    const uint64_t aM = ta ? a_cols : a_rows, aK = ta ? a_rows : a_cols;
+    const uint64_t bK = tb ? b_cols : b_rows, bN = tb ? b_rows : b_cols;
+    if (aK != bK) return fail(cudaErrorInvalidValue, "matmul inner dimensions must be equal (%llu vs %llu)",
+                              (unsigned long long)aK, (unsigned long long)bK);
+    if (aM != P.M || bN != P.N)
+        return fail(cudaErrorInvalidValue, "out shape [%llu x %llu] does not match op(a).op(b) [%llu x %llu]",
+                    (unsigned long long)P.M, (unsigned long long)P.N, (unsigned long long)aM, (unsigned long long)bN);
+    P.K = aK;
+    if (P.M == 0 || P.N == 0 || P.K == 0 || P.batch == 0) return fail(cudaErrorInvalidValue, "zero-sized dimension");
+    const uint64_t lim = 0x7fffffffull;       // the reference limits dims to Int32.max (MatrixLayout.swift:117-142)
+    if (P.M > lim || P.N > lim || P.K > lim || P.batch > 65535)
+        return fail(cudaErrorInvalidValue, "dimension exceeds the supported range");
+
+    P.a_m = (long long)(ta ? ad->strides[aq + 1] : ad->strides[aq]);
+    P.a_k = (long long)(ta ? ad->strides[aq] : ad->strides[aq + 1]);
+    P.b_k = (long long)(tb ? bd->strides[bq + 1] : bd->strides[bq]);
+    P.b_n = (long long)(tb ? bd->strides[bq] : bd->strides[bq + 1]);
+    P.o_m = (long long)od->strides[oq];
+    P.o_n = (long long)od->strides[oq + 1];
+    P.a_b = P.b_b = P.o_b = 0;
+    if (od->rank == 3) {
+        P.o_b = (long long)od->strides[0];
+        if (ad->rank == 3) {
+            if (ad->shape[0] != P.batch && ad->shape[0] != 1) return fail(cudaErrorInvalidValue, "batch size of a does not match out");
+            P.a_b = ad->shape[0] == 1 ? 0 : (long long)ad->strides[0];
+        }
+        if (bd->rank == 3) {
+            if (bd->shape[0] != P.batch && bd->shape[0] != 1) return fail(cudaErrorInvalidValue, "batch size of b does not match out");
+            P.b_b = bd->shape[0] == 1 ? 0 : (long long)bd->strides[0];
+        }
+    }
+    if ((P.M > 1 && P.o_m == 0) || (P.N > 1 && P.o_n == 0) || (P.batch > 1 && P.o_b == 0))
+        return fail(cudaErrorInvalidValue, "out must not repeat elements (zero stride)");
+    P.a = static_cast<const char*>(a);
+    P.b = static_cast<const char*>(b);
+    P.out = static_cast<char*>(const_cast<void*>(out));
+
+    P.bias = nullptr;
+    P.bias_stride = 0;
+    if (bias) {
+        if (!biasd || !biasd->shape || !biasd->strides) return fail(cudaErrorInvalidValue, "bias without descriptor");
+        if (biasd->type != P.type) return fail(cudaErrorInvalidValue, "bias must have the element type of out");
+        if (biasd->rank != 1 || biasd->shape[0] != P.N)
+            return fail(cudaErrorInvalidValue, "bias must be rank 1 with %llu elements", (unsigned long long)P.N);
+        P.bias = static_cast<const char*>(bias);
+        P.bias_stride = (long long)biasd->strides[0];
+    }
+    switch (act) {
+    case srtActivationSigmoid: case srtActivationRelu: case srtActivationTanh:
+    case srtActivationIdentity: case srtActivationGelu: case srtActivationGeluTanh:
+        P.act = (uint32_t)act;
+        break;
+    case srtActivationClippedRelu: case srtActivationElu:
+        return fail(cudaErrorNotSupported, "clippedRelu and elu need coefficients that this entry point does not carry");
+    default:
+        return fail(cudaErrorInvalidValue, "unknown activation %d", act);
+    }
+    g_error[0] = 0;
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ per-device state
+struct DeviceInfo {
+    int sms = 0;
+    bool sm100 = false;
+    bool attrs_set = false;
+};
+std::mutex g_mutex;
+DeviceInfo g_devices[64];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+cudaError_t device_info(int dev, DeviceInfo& out)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (dev < 0 || dev >= 64) return fail(cudaErrorInvalidDevice, "device ordinal %d out of range", dev);
+    DeviceInfo& d = g_devices[dev];
+    if (d.sms == 0) {
+        int major = 0, sms = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        d.sm100 = (major == 10);
+        d.sms = sms;
+    }
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return fail(cudaErrorNotSupported, "driver does not export cuTensorMapEncodeTiled");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    out = d;
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ planning
+struct TcOperand {
+    bool ok = false;
+    bool mn_major = false;
+    long long ld = 0;          // elements between consecutive indices of the non-contiguous dim
+};
+
+// Can TMA address op(x) [rows x K] with element strides (s_r, s_k), batch stride s_b?
+TcOperand classify(const char* ptr, uint64_t rows, uint64_t K, uint64_t batch, long long s_r, long long s_k,
+                   long long s_b, uint32_t elem)
+{
+    TcOperand r;
+    if (reinterpret_cast<uintptr_t>(ptr) % 16) return r;
+    const bool k_unit = (s_k == 1 || K == 1), r_unit = (s_r == 1 || rows == 1);
+    auto ok_stride = [&](long long s, uint64_t extent_inner) {
+        return s > 0 && (s * (long long)elem) % 16 == 0 && (uint64_t)s >= extent_inner &&
+               (unsigned long long)s * elem < (1ull << 40);
+    };
+    if (batch > 1 && s_b != 0 && !((s_b * (long long)elem) % 16 == 0 && s_b > 0 && (unsigned long long)s_b * elem < (1ull << 40)))
+        return r;
+    if (k_unit && (rows == 1 || ok_stride(s_r, K))) {
+        r.ok = true; r.mn_major = false; r.ld = rows == 1 ? (long long)((K * elem + 15) / 16 * 16 / elem) : s_r;
+        return r;
+    }
+    if (r_unit && (K == 1 || ok_stride(s_k, rows))) {
+        r.ok = true; r.mn_major = true; r.ld = K == 1 ? (long long)((rows * elem + 15) / 16 * 16 / elem) : s_k;
+        return r;
+    }
+    return r;
+}
+
+struct Plan {
+    srtMatmulPlan pub;
+    bool swapped = false;
+    Problem Q;                 // the problem as the kernel sees it (after a possible swap)
+    TcOperand ta, tb;
+    uint32_t bias_mode = 0;
+};
+
+void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
+{
+    memset(&plan.pub, 0, sizeof plan.pub);
+    plan.Q = P;
+    plan.swapped = false;
+    plan.bias_mode = P.bias ? 1 : 0;
+    const int32_t force = g_tuning.force_kernel.load();
+
+    bool tc = dev.sm100 && force != srtMatmulKernelSimt;
+    // the tensor-core path writes rows of contiguous columns; a col-order out is computed
+    // as out^T = op(b)^T . op(a)^T, which is the same memory
+    Problem Q = P;
+    if (tc) {
+        if (P.o_n == 1 || P.N == 1) {
+            // as is
+        } else if (P.o_m == 1 || P.M == 1) {
+            Q.M = P.N; Q.N = P.M;
+            Q.a = P.b; Q.a_b = P.b_b; Q.a_m = P.b_n; Q.a_k = P.b_k;
+            Q.b = P.a; Q.b_b = P.a_b; Q.b_k = P.a_k; Q.b_n = P.a_m;
+            Q.o_m = P.o_n; Q.o_n = P.o_m;
+            plan.swapped = true;
+            if (P.bias) plan.bias_mode = 2;
+        } else {
+            tc = false;
+        }
+    }
+    if (tc) {
+        plan.ta = classify(Q.a, Q.M, Q.K, Q.batch, Q.a_m, Q.a_k, Q.a_b, Q.elem);
+        plan.tb = classify(Q.b, Q.N, Q.K, Q.batch, Q.b_n, Q.b_k, Q.b_b, Q.elem);
+        if (!plan.ta.ok || !plan.tb.ok) tc = false;
+        if (Q.N > 1 && Q.o_m < (long long)Q.N && Q.M > 1) tc = false;   // overlapping output rows
+    }
+    // fp32 on the tensor cores is TF32 (10-bit mantissa): only on explicit request
+    if (tc && Q.type == real32F && force != srtMatmulKernelTcgen05) tc = false;
+    // tiny problems are launch-bound either way; keep them on the exact kernel
+    if (tc && force != srtMatmulKernelTcgen05 && Q.M * Q.N * Q.K * Q.batch < (1ull << 18)) tc = false;
+
+    if (!tc) {
+        plan.Q = P;
+        plan.swapped = false;
+        plan.bias_mode = P.bias ? 1 : 0;
+        plan.pub.kernel = srtMatmulKernelSimt;
+        plan.pub.tileM = kSimtTile; plan.pub.tileN = kSimtTile; plan.pub.tileK = kSimtK;
+        plan.pub.stages = 1;
+        const uint64_t tm = (P.M + kSimtTile - 1) / kSimtTile, tn = (P.N + kSimtTile - 1) / kSimtTile;
+        plan.pub.tiles = (int32_t)(tm * tn * P.batch);
+        plan.pub.ctas = plan.pub.tiles;
+        plan.pub.dynamicSmemBytes = 0;
+        return;
+    }
+
+    plan.Q = Q;
+    uint32_t bn = (uint32_t)g_tuning.tile_n.load();
+    if (bn != 64 && bn != 128 && bn != 256) {
+        // widest tile that still gives every SM work; narrow tiles for narrow outputs
+        const uint64_t tm = (Q.M + kTileM - 1) / kTileM;
+        bn = 256;
+        while (bn > 64 && (Q.N <= bn / 2 || tm * ((Q.N + bn - 1) / bn) * Q.batch < (uint64_t)dev.sms)) bn /= 2;
+    }
+    const uint32_t stage_bytes = kATileBytes + bn * kRowBytes;
+    uint32_t stages = (uint32_t)g_tuning.stages.load();
+    const uint32_t max_stages = (227u * 1024u - 2048u) / stage_bytes;
+    if (stages < 2 || stages > 8) stages = 8;
+    if (stages > max_stages) stages = max_stages;
+    const uint32_t kb_elems = kRowBytes / Q.elem;
+    const uint64_t tiles_m = (Q.M + kTileM - 1) / kTileM, tiles_n = (Q.N + bn - 1) / bn;
+    const uint64_t tiles = tiles_m * tiles_n * Q.batch;
+    uint32_t ctas = (uint32_t)(tiles < (uint64_t)dev.sms ? tiles : (uint64_t)dev.sms);
+    const int32_t cap = g_tuning.max_ctas.load();
+    if (cap > 0 && ctas > (uint32_t)cap) ctas = (uint32_t)cap;
+
+    plan.pub.kernel = srtMatmulKernelTcgen05;
+    plan.pub.tileM = kTileM; plan.pub.tileN = (int32_t)bn; plan.pub.tileK = (int32_t)kb_elems;
+    plan.pub.stages = (int32_t)stages;
+    plan.pub.ctas = (int32_t)ctas;
+    plan.pub.tiles = (int32_t)tiles;
+    plan.pub.swapped = plan.swapped;
+    plan.pub.aMajor = plan.ta.mn_major; plan.pub.bMajor = plan.tb.mn_major;
+    plan.pub.fp32Split = 0;
+    plan.pub.workspaceBytes = 0;
+    plan.pub.dynamicSmemBytes = (size_t)stages * stage_bytes + 1024;
+}
+
+// ------------------------------------------------------------------ tensor maps
+cudaError_t encode_operand(CUtensorMap* map, const Problem& Q, const char* ptr, const TcOperand& t, uint64_t rows,
+                           long long s_b, uint32_t box_rows, OperandParams& op)
+{
+    const uint32_t elem = Q.elem;
+    const uint32_t kb_elems = kRowBytes / elem;
+    const bool bcast = (Q.batch == 1 || s_b == 0);
+    CUtensorMapDataType dt = Q.type == real32F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : Q.type == real16F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    cuuint64_t gdim[3], gstride[2];
+    cuuint32_t box[3], estr[3] = {1, 1, 1};
+    if (!t.mn_major) {
+        gdim[0] = Q.K; gdim[1] = rows;
+        box[0] = kb_elems; box[1] = box_rows;
+        op.chunks = 1; op.chunk_elems = box_rows; op.chunk_bytes = box_rows * kRowBytes;
+        // rows of 128 bytes, groups of 8 rows 1024 bytes apart; the leading offset is unused
+        op.desc_lo_fixed = 1u << 16;
+        op.kstep = 32 >> 4;                       // next 32 bytes of K inside the swizzled row
+    } else {
+        gdim[0] = rows; gdim[1] = Q.K;
+        box[0] = kb_elems; box[1] = kb_elems;     // 128 bytes of M/N by one stage of K
+        op.chunks = box_rows / kb_elems; op.chunk_elems = kb_elems; op.chunk_bytes = kb_elems * kRowBytes;
+        // 128 bytes of M/N per row, one row per k; 8-row groups 1024 bytes apart (stride
+        // offset), the next 128 bytes of M/N one chunk further (leading offset)
+        op.desc_lo_fixed = ((op.chunk_bytes >> 4) & 0x3fffu) << 16;
+        op.kstep = ((32 / elem) * kRowBytes) >> 4;  // one MMA consumes 32/elem rows of k
+    }
+    op.mn_major = t.mn_major;
+    op.batch_mul = bcast ? 0 : 1;
+    // stride offset 1024 bytes, descriptor version 1 (bit 46), 128-byte swizzle (bits 61-63 = 2)
+    op.desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    gdim[2] = bcast ? 1 : Q.batch;
+    gstride[0] = (cuuint64_t)t.ld * elem;
+    gstride[1] = bcast ? gstride[0] * gdim[1] : (cuuint64_t)s_b * elem;
+    box[2] = 1;
+    CUresult r = g_encode(map, dt, 3, const_cast<char*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return cudaSuccess;
+}
+
+template <typename T, uint32_t BN>
+cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas, size_t smem,
+                      cudaStream_t stream)
+{
+    auto kernel = gemm_tcgen05_kernel<T, BN>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<ctas, kGemmThreads, smem, stream>>>(ma, mb, gp);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_tc_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas,
+                         size_t smem, cudaStream_t stream)
+{
+    switch (bn) {
+    case 64: return launch_tc<T, 64>(ma, mb, gp, ctas, smem, stream);
+    case 128: return launch_tc<T, 128>(ma, mb, gp, ctas, smem, stream);
+    default: return launch_tc<T, 256>(ma, mb, gp, ctas, smem, stream);
+    }
+}
+
+cudaError_t run_tc(const Plan& plan, cudaStream_t stream)
+{
+    const Problem& Q = plan.Q;
+    const uint32_t bn = (uint32_t)plan.pub.tileN;
+    GemmParams gp;
+    memset(&gp, 0, sizeof gp);
+    CUtensorMap ma, mb;
+    cudaError_t e = encode_operand(&ma, Q, Q.a, plan.ta, Q.M, Q.a_b, kTileM, gp.a);
+    if (e != cudaSuccess) return e;
+    e = encode_operand(&mb, Q, Q.b, plan.tb, Q.N, Q.b_b, bn, gp.b);
+    if (e != cudaSuccess) return e;
+
+    gp.M = (uint32_t)Q.M; gp.N = (uint32_t)Q.N; gp.K = (uint32_t)Q.K; gp.batch = (uint32_t)Q.batch;
+    gp.tiles_m = (uint32_t)((Q.M + kTileM - 1) / kTileM);
+    gp.tiles_n = (uint32_t)((Q.N + bn - 1) / bn);
+    gp.tiles_per_batch = gp.tiles_m * gp.tiles_n;
+    gp.num_tiles = (uint32_t)plan.pub.tiles;
+    gp.kb_elems = kRowBytes / Q.elem;
+    gp.k_blocks = (uint32_t)((Q.K + gp.kb_elems - 1) / gp.kb_elems);
+    gp.group_m = 16;
+    gp.stages = (uint32_t)plan.pub.stages;
+    gp.stage_tx_bytes = kATileBytes + bn * kRowBytes;
+    // instruction descriptor: fp32 accumulator, input format, majorness, N >> 3, M >> 4
+    const uint32_t fmt = Q.type == real16F ? 0u : Q.type == real16BF ? 1u : 2u;
+    gp.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)plan.ta.mn_major << 15) |
+               ((uint32_t)plan.tb.mn_major << 16) | ((bn >> 3) << 17) | ((kTileM >> 4) << 24);
+    gp.out = Q.out;
+    gp.ldo = Q.N == 1 ? (Q.M == 1 ? 1 : Q.o_m) : (Q.M == 1 ? (long long)Q.N : Q.o_m);
+    gp.out_batch_stride = Q.o_b;
+    gp.bias = Q.bias;
+    gp.bias_stride = Q.bias_stride;
+    gp.bias_mode = plan.bias_mode;
+    gp.act = Q.act;
+    gp.out_vec_ok = (reinterpret_cast<uintptr_t>(Q.out) % 16 == 0) && ((gp.ldo * (long long)Q.elem) % 16 == 0) &&
+                    ((Q.o_b * (long long)Q.elem) % 16 == 0) && (Q.N > 1 ? Q.o_n == 1 : true);
+
+    const size_t smem = plan.pub.dynamicSmemBytes;
+    const uint32_t ctas = (uint32_t)plan.pub.ctas;
+    switch (Q.type) {
+    case real32F: e = launch_tc_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
+    case real16F: e = launch_tc_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
+    default: e = launch_tc_bn<__nv_bfloat16>(bn, ma, mb, gp, ctas, smem, stream); break;
+    }
+    if (e == cudaSuccess) g_launches.fetch_add(1);
+    return e;
+}
+
+cudaError_t run_simt(const Plan& plan, cudaStream_t stream)
+{
+    const Problem& P = plan.Q;
+    SimtParams sp;
+    memset(&sp, 0, sizeof sp);
+    sp.M = (uint32_t)P.M; sp.N = (uint32_t)P.N; sp.K = (uint32_t)P.K; sp.batch = (uint32_t)P.batch;
+    sp.a = P.a; sp.b = P.b; sp.out = P.out; sp.bias = P.bias;
+    sp.a_b = P.a_b; sp.a_m = P.a_m; sp.a_k = P.a_k;
+    sp.b_b = P.b_b; sp.b_k = P.b_k; sp.b_n = P.b_n;
+    sp.o_b = P.o_b; sp.o_m = P.o_m; sp.o_n = P.o_n;
+    sp.bias_stride = P.bias_stride;
+    sp.has_bias = P.bias != nullptr;
+    sp.act = P.act;
+    sp.a_k_fast = (P.a_k == 1) || (P.a_m != 1);
+    sp.b_n_fast = (P.b_n == 1) || (P.b_k != 1);
+    const uint64_t tm = (P.M + kSimtTile - 1) / kSimtTile, tn = (P.N + kSimtTile - 1) / kSimtTile;
+    if (tm > 65535) return fail(cudaErrorNotSupported, "strided kernel: more than 65535 row tiles");
+    dim3 grid((unsigned)tn, (unsigned)tm, (unsigned)P.batch);
+    switch (P.type) {
+    case real32F: gemm_simt_kernel<float><<<grid, 256, 0, stream>>>(sp); break;
+    case real16F: gemm_simt_kernel<__half><<<grid, 256, 0, stream>>>(sp); break;
+    default: gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(sp); break;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1);
+    return e;
+}
+
+cudaError_t plan_for(const Problem& P, Plan& plan)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    DeviceInfo info;
+    e = device_info(dev, info);
+    if (e != cudaSuccess) return e;
+    if (!info.sm100) return fail(cudaErrorNotSupported, "this library is built for sm_100a devices only");
+    make_plan(P, info, plan);
+    return cudaSuccess;
+}
+
+}  // namespace
+
+// ===================================================================== exported entry points
+extern "C" {
+
+cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                                    const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                                    const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                                    const srtTensorDescriptor* oDesc, cudaStream_t stream)
+{
+    Problem P;
+    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
+    if (e != cudaSuccess) return e;
+    Plan plan;
+    e = plan_for(P, plan);
+    if (e != cudaSuccess) return e;
+    return plan.pub.kernel == srtMatmulKernelSimt ? run_simt(plan, stream) : run_tc(plan, stream);
+}
+
+cudaError_t srtMatmul(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                      const srtTensorDescriptor* bDesc, bool transB, void* out, const srtTensorDescriptor* oDesc,
+                      cudaStream_t stream)
+{
+    return srtMatmulBiasActivation(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out,
+                                   oDesc, stream);
+}
+
+cudaError_t srtMatmulQueryPlan(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                               const srtTensorDescriptor* bDesc, bool transB, const void* out,
+                               const srtTensorDescriptor* oDesc, srtMatmulPlan* plan_out)
+{
+    if (!plan_out) return fail(cudaErrorInvalidValue, "null plan");
+    Problem P;
+    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out, oDesc, P);
+    if (e != cudaSuccess) return e;
+    Plan plan;
+    e = plan_for(P, plan);
+    if (e != cudaSuccess) return e;
+    *plan_out = plan.pub;
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas)
+{
+    if (forceKernel < 0 || forceKernel > srtMatmulKernelTcgen05Pair) return fail(cudaErrorInvalidValue, "unknown kernel id");
+    if (tileN != 0 && tileN != 64 && tileN != 128 && tileN != 256) return fail(cudaErrorInvalidValue, "tileN must be 0, 64, 128 or 256");
+    if (stages != 0 && (stages < 2 || stages > 8)) return fail(cudaErrorInvalidValue, "stages must be 0 or 2..8");
+    if (maxCtas < 0) return fail(cudaErrorInvalidValue, "maxCtas must be >= 0");
+    g_tuning.force_kernel = forceKernel;
+    g_tuning.tile_n = tileN;
+    g_tuning.stages = stages;
+    g_tuning.max_ctas = maxCtas;
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status)
+{
+    if (!status) return fail(cudaErrorInvalidValue, "null status");
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    uint32_t v = 0;
+    e = cudaMemcpyFromSymbol(&v, srt::g_gemm_status, sizeof v);
+    if (e != cudaSuccess) return e;
+    if (v != 0) {
+        const uint32_t zero = 0;
+        e = cudaMemcpyToSymbol(srt::g_gemm_status, &zero, sizeof zero);
+        if (e != cudaSuccess) return e;
+    }
+    *status = v;
+    return cudaSuccess;
+}
+
+uint64_t srtMatmulLaunchCount(void) { return g_launches.load(); }
+
+const char* srtMatmulGetLastErrorString(void) { return g_error; }
+
+}  // extern "C"

@@ -1,0 +1,146 @@
+"""Host-side mirror of the reference's matmul operators over the C ABI.
+
+Same names, argument meaning and error behaviour as
+  matmul(_:transposed:_:transposed:)        Sources/SwiftRTCore/operators/Matmul.swift:29-45
+  matmul(_:transposed:_:transposed:bias:)   Matmul.swift:57-72
+  matmulGradients                           differentiable/MathDerivatives.swift:460-482
+and the queue-level rank-3 (batched) form   platform/cpu/functions/CpuMath.swift:363-369.
+Every call goes to the CUDA library; there is no other path.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import lib
+from .tensor import ActivationType, Descriptor, Order, empty, order_of
+
+
+class MatmulError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"srtMatmul failed with cudaError {code}: {what}")
+        self.code = code
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _result_shape(lhs, transpose_lhs, rhs, transpose_rhs):
+    ls = tuple(lhs.shape[-2:])[::-1] if transpose_lhs else tuple(lhs.shape[-2:])
+    rs = tuple(rhs.shape[-2:])[::-1] if transpose_rhs else tuple(rhs.shape[-2:])
+    # the reference asserts here (Matmul.swift:35)
+    assert ls[1] == rs[0], "matmul inner dimensions must be equal"
+    batch = ()
+    if lhs.dim() == 3 or rhs.dim() == 3:
+        nb = max(lhs.shape[0] if lhs.dim() == 3 else 1, rhs.shape[0] if rhs.dim() == 3 else 1)
+        batch = (nb,)
+    return batch + (ls[0], rs[1])
+
+
+def matmul_into(out: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
+                transpose_rhs: bool, bias: torch.Tensor | None = None,
+                activation: ActivationType | None = None) -> torch.Tensor:
+    """The queue-level call: writes op(lhs).op(rhs) [+ bias, activation] into `out`, which may be a
+    strided view (CpuMath.swift:355-369 takes the result inout).  Asynchronous on torch's current
+    stream of out's device."""
+    if not (lhs.is_cuda and rhs.is_cuda and out.is_cuda):
+        raise ValueError("device tensors expected; use matmul_host for host buffers")
+    da, db, do = Descriptor(lhs), Descriptor(rhs), Descriptor(out)
+    with torch.cuda.device(out.device):
+        stream = _stream_ptr(out.device)
+        if bias is None and activation is None:
+            rc = lib.srtMatmul(lhs.data_ptr(), da.ref(), transpose_lhs, rhs.data_ptr(), db.ref(), transpose_rhs,
+                               out.data_ptr(), do.ref(), stream)
+        else:
+            dbias = Descriptor(bias) if bias is not None else None
+            rc = lib.srtMatmulBiasActivation(
+                lhs.data_ptr(), da.ref(), transpose_lhs, rhs.data_ptr(), db.ref(), transpose_rhs,
+                bias.data_ptr() if bias is not None else None, dbias.ref() if dbias is not None else None,
+                int(activation if activation is not None else ActivationType.identity),
+                out.data_ptr(), do.ref(), stream)
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+    return out
+
+
+def matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,
+           bias: torch.Tensor | None = None, activation: ActivationType | None = None) -> torch.Tensor:
+    """result = op(lhs) . op(rhs), allocated dense in lhs's order (Matmul.swift:36-38).
+
+    With `bias` (rank 1, one value per output column) the sum is added before the single
+    rounding to the element type -- what matmul(bias:) declares.  Rank-3 operands are batched
+    over dimension 0; a rank-2 operand next to a rank-3 one is used for every batch item."""
+    shape = _result_shape(lhs, transposed_lhs, rhs, transposed_rhs)
+    out = empty(shape, lhs.dtype, lhs.device, order_of(lhs))
+    return matmul_into(out, lhs, transposed_lhs, rhs, transposed_rhs, bias, activation)
+
+
+def matmul_gradients(out_grad: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
+                     transpose_rhs: bool):
+    """(lhsGrad, rhsGrad) exactly as matmulGradients composes them from two more matmul calls
+    (MathDerivatives.swift:460-482), including its formulas for the transposed cases."""
+    if not transpose_lhs and not transpose_rhs:
+        return (matmul(out_grad, rhs, False, True), matmul(lhs, out_grad, True, False))
+    if not transpose_lhs and transpose_rhs:
+        return (matmul(out_grad, rhs), matmul(lhs, out_grad, True, False))
+    if transpose_lhs and not transpose_rhs:
+        return (matmul(out_grad, rhs, False, True), matmul(lhs, out_grad))
+    return (matmul(out_grad, rhs, True, True), matmul(lhs, out_grad, True, True))
+
+
+def matmul_host(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,
+                bias: torch.Tensor | None = None, activation: ActivationType | None = None,
+                device="cuda:0", out_host: torch.Tensor | None = None) -> torch.Tensor:
+    """The same operator for HOST tensors: inputs are copied to `device`, multiplied there and the
+    result is copied back, all on the current stream, which is synchronised before returning.
+    This is what the reference's storage does around a queue call (host replicas migrate on
+    deviceRead, DiscreteStorage.swift:310-381).  Pinned host memory makes the copies asynchronous."""
+    dev = torch.device(device)
+    a = lhs.to(dev, non_blocking=True)
+    b = rhs.to(dev, non_blocking=True)
+    bz = bias.to(dev, non_blocking=True) if bias is not None else None
+    c = matmul(a, b, transposed_lhs, transposed_rhs, bz, activation)
+    if out_host is None:
+        out_host = torch.empty(c.shape, dtype=c.dtype, pin_memory=True)
+    out_host.copy_(c, non_blocking=True)
+    torch.cuda.current_stream(dev).synchronize()
+    return out_host
+
+
+def query_plan(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, transposed_lhs: bool = False,
+               transposed_rhs: bool = False) -> dict:
+    """What a call with these tensors would launch (stands in for MatmulAlgorithm.query,
+    cublaslt/MatmulAlgorithmSearch.swift:51-100)."""
+    plan = _lib.MatmulPlan()
+    da, db, do = Descriptor(lhs), Descriptor(rhs), Descriptor(out)
+    with torch.cuda.device(out.device):
+        rc = lib.srtMatmulQueryPlan(lhs.data_ptr(), da.ref(), transposed_lhs, rhs.data_ptr(), db.ref(), transposed_rhs,
+                                    out.data_ptr(), do.ref(), ctypes.byref(plan))
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+    return {name: getattr(plan, name) for name, _ in plan._fields_}
+
+
+def set_tuning(force_kernel: int = 0, tile_n: int = 0, stages: int = 0, max_ctas: int = 0) -> None:
+    rc = lib.srtMatmulSetTuning(force_kernel, tile_n, stages, max_ctas)
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+
+
+def check_status(device=None) -> int:
+    """Synchronises the current stream and returns the tensor-core kernels' status word
+    (0 = every pipeline wait completed)."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    status = ctypes.c_uint32(0)
+    with torch.cuda.device(dev):
+        rc = lib.srtMatmulCheckStatus(_stream_ptr(dev), ctypes.byref(status))
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+    return status.value
+
+
+def launch_count() -> int:
+    return int(lib.srtMatmulLaunchCount())
