@@ -243,35 +243,52 @@ static void row_faithful(const mm_args* g, size_t n, size_t r)
     }
 }
 
-/* one output row, loop order k then c with a row of accumulators.  Every element still
- * receives its products in k = 0..K-1 order with the same two roundings, so the result is
- * bit-identical to row_faithful; only the memory access pattern differs. */
-static void row_fast(const mm_args* g, size_t n, size_t r, float* acc)
+/* A block of up to ORACLE_ROW_BLOCK output rows, loop order k, row, c with one row of
+ * accumulators per output row.  Every element still receives its products in k = 0..K-1 order
+ * with the same two roundings, so the result is bit-identical to row_faithful; only the memory
+ * access pattern differs (each row of B is read once per block of rows instead of once per row). */
+#define ORACLE_ROW_BLOCK 8
+#define ORACLE_COL_BLOCK 1024
+static void rows_fast(const mm_args* g, size_t n, size_t r0, size_t nrows, float* acc)
 {
-    for (size_t c = 0; c < g->N; ++c) acc[c] = 0.0f;
-    for (size_t k = 0; k < g->K; ++k) {
-        float x = load_value(g->dtype, g->a, n * g->a_b + r * g->a_m + k * g->a_k);
-        if (g->dtype == ORACLE_F32 && g->b_n == 1) {
-            const float* brow = (const float*)g->b + n * g->b_b + k * g->b_k;
-            for (size_t c = 0; c < g->N; ++c) { float p = x * brow[c]; acc[c] += p; }
-        } else if (g->dtype == ORACLE_BF16 && g->b_n == 1) {
-            const uint16_t* brow = (const uint16_t*)g->b + n * g->b_b + k * g->b_k;
-            for (size_t c = 0; c < g->N; ++c) { float p = x * bits2f((uint32_t)brow[c] << 16); acc[c] += p; }
-        } else {
-            for (size_t c = 0; c < g->N; ++c) {
-                float y = load_value(g->dtype, g->b, n * g->b_b + k * g->b_k + c * g->b_n);
-                float p = x * y;
-                acc[c] += p;
+    /* column blocks keep the accumulators (8 x 1024 floats) in the L1 cache */
+    for (size_t c0 = 0; c0 < g->N; c0 += ORACLE_COL_BLOCK) {
+        const size_t nc = g->N - c0 < ORACLE_COL_BLOCK ? g->N - c0 : ORACLE_COL_BLOCK;
+        for (size_t i = 0; i < nrows * ORACLE_COL_BLOCK; ++i) acc[i] = 0.0f;
+        for (size_t k = 0; k < g->K; ++k) {
+            float x[ORACLE_ROW_BLOCK];
+            for (size_t i = 0; i < nrows; ++i)
+                x[i] = load_value(g->dtype, g->a, n * g->a_b + (r0 + i) * g->a_m + k * g->a_k);
+            if (g->dtype == ORACLE_F32 && g->b_n == 1) {
+                const float* brow = (const float*)g->b + n * g->b_b + k * g->b_k + c0;
+                for (size_t i = 0; i < nrows; ++i) {
+                    float* ar = acc + i * ORACLE_COL_BLOCK;
+                    const float xi = x[i];
+                    for (size_t c = 0; c < nc; ++c) { float p = xi * brow[c]; ar[c] += p; }
+                }
+            } else if (g->dtype == ORACLE_BF16 && g->b_n == 1) {
+                const uint16_t* brow = (const uint16_t*)g->b + n * g->b_b + k * g->b_k + c0;
+                for (size_t i = 0; i < nrows; ++i) {
+                    float* ar = acc + i * ORACLE_COL_BLOCK;
+                    const float xi = x[i];
+                    for (size_t c = 0; c < nc; ++c) { float p = xi * bits2f((uint32_t)brow[c] << 16); ar[c] += p; }
+                }
+            } else {
+                for (size_t c = 0; c < nc; ++c) {
+                    float y = load_value(g->dtype, g->b, n * g->b_b + k * g->b_k + (c0 + c) * g->b_n);
+                    for (size_t i = 0; i < nrows; ++i) { float p = x[i] * y; acc[i * ORACLE_COL_BLOCK + c] += p; }
+                }
             }
         }
-    }
-    for (size_t c = 0; c < g->N; ++c) {
-        float v = acc[c];
-        if (g->has_epilogue) {
-            if (g->bias) v = v + load_value(g->dtype, g->bias, c * g->bias_s);
-            v = activate(g->act, v);
-        }
-        store_value(g->dtype, g->out, n * g->o_b + r * g->o_m + c * g->o_n, v);
+        for (size_t i = 0; i < nrows; ++i)
+            for (size_t c = 0; c < nc; ++c) {
+                float v = acc[i * ORACLE_COL_BLOCK + c];
+                if (g->has_epilogue) {
+                    if (g->bias) v = v + load_value(g->dtype, g->bias, (c0 + c) * g->bias_s);
+                    v = activate(g->act, v);
+                }
+                store_value(g->dtype, g->out, n * g->o_b + (r0 + i) * g->o_m + (c0 + c) * g->o_n, v);
+            }
     }
 }
 
@@ -281,8 +298,8 @@ static void row_fast(const mm_args* g, size_t n, size_t r, float* acc)
  * reference's srtTensorDescriptor.  A batch stride of 0 broadcasts that operand.
  * bias may be NULL; act is an ActivationType raw value; has_epilogue = 0 gives the plain
  * matmul (the reference's matmul(bias:) ignores the bias, Matmul.swift:57-72).
- * mode 0 = faithful loop order on one thread; mode 1 = k-outer loop order, `threads`
- * OpenMP threads over rows (bit-identical results).
+ * mode 0 = faithful loop order on one thread; mode 1 = k-outer loop order over blocks of rows,
+ * `threads` OpenMP threads over the blocks (bit-identical results).
  * row_begin/row_end restrict the computed output rows (for bounded samples); pass 0, M.
  * Returns 0, or a negative code on a shape error.
  */
@@ -326,15 +343,18 @@ int oracle_matmul(int dtype, int rank,
         return 0;
     }
     if (threads < 1) threads = 1;
-    long total = (long)(g.batch * (row_end - row_begin));
-    size_t rows = row_end - row_begin;
+    const size_t rows = row_end - row_begin;
+    const size_t blocks_per_item = (rows + ORACLE_ROW_BLOCK - 1) / ORACLE_ROW_BLOCK;
+    const long total = (long)(g.batch * blocks_per_item);
 #pragma omp parallel num_threads(threads)
     {
-        float* acc = (float*)malloc(sizeof(float) * (g.N ? g.N : 1));
-#pragma omp for schedule(dynamic, 4)
+        float* acc = (float*)malloc(sizeof(float) * ORACLE_ROW_BLOCK * ORACLE_COL_BLOCK);
+#pragma omp for schedule(dynamic, 1)
         for (long i = 0; i < total; ++i) {
-            size_t n = (size_t)i / rows, r = row_begin + (size_t)i % rows;
-            row_fast(&g, n, r, acc);
+            size_t n = (size_t)i / blocks_per_item;
+            size_t r0 = row_begin + ((size_t)i % blocks_per_item) * ORACLE_ROW_BLOCK;
+            size_t nr = row_end - r0 < ORACLE_ROW_BLOCK ? row_end - r0 : ORACLE_ROW_BLOCK;
+            rows_fast(&g, n, r0, nr, acc);
         }
         free(acc);
     }

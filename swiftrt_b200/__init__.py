@@ -9,3 +9,4 @@ from .matmul import (MatmulError, check_status, launch_count, matmul, matmul_gra
 from .tensor import ActivationType, DataType, Order, empty, order_of  # noqa: F401
 
 KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR = 1, 2, 3
+from .sharded import shard_range, sharded_matmul  # noqa: F401,E402

@@ -1,0 +1,120 @@
+"""Multi-GPU sharding of one matmul: one process per GPU, independent output blocks, no
+reduction, at most one exchange step (an all-gather of the output shards).
+
+This is the reference's only data-parallel idea -- pmap splits axis 0 into partitions whose
+results land in views of one shared output (Sources/SwiftRTCore/platform/common/pmap.swift:
+26-72, 77-86) -- moved from CPU threads to GPUs:
+
+  axis "batch": rank r multiplies batch items [b0, b1)            (batched matmul)
+  axis "m":     rank r multiplies rows [m0, m1) of op(lhs)          (tall-skinny matmul)
+  axis "n":     rank r multiplies columns [n0, n1) of op(rhs)       (large square matmul)
+
+Every rank passes the full logical operands (or at least the slices it owns: only the owned
+slices are read).  The local result is written straight into this rank's view of `out` when the
+full output is wanted, so the gather needs no staging copy for the batch and m axes.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+AXES = ("batch", "m", "n")
+
+
+def shard_range(total: int, world: int, rank: int, align: int = 1) -> tuple[int, int]:
+    """Contiguous, balanced [start, stop) of `total` items for `rank` of `world`.
+
+    Shard boundaries are multiples of `align` (the last shard takes the remainder), so that
+    column slices of 16-bit matrices stay 16-byte aligned for TMA."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank outside the world")
+    units = -(-total // align)
+    base, extra = divmod(units, world)
+    start_u = rank * base + min(rank, extra)
+    stop_u = start_u + base + (1 if rank < extra else 0)
+    return min(start_u * align, total), min(stop_u * align, total)
+
+
+def _slice_operands(lhs, transposed_lhs, rhs, transposed_rhs, axis, lo, hi):
+    if axis == "batch":
+        a = lhs[lo:hi] if lhs.dim() == 3 else lhs
+        b = rhs[lo:hi] if rhs.dim() == 3 else rhs
+        return a, b
+    if axis == "m":
+        # rows of op(lhs): dim -2 of lhs, or dim -1 when it is used transposed
+        a = lhs.narrow(-1 if transposed_lhs else -2, lo, hi - lo)
+        return a, rhs
+    b = rhs.narrow(-2 if transposed_rhs else -1, lo, hi - lo)
+    return lhs, b
+
+
+def sharded_matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False,
+                   transposed_rhs: bool = False, axis: str = "n", gather: bool = False,
+                   out: Optional[torch.Tensor] = None, group=None,
+                   matmul_into_fn: Optional[Callable] = None,
+                   rank: Optional[int] = None, world: Optional[int] = None) -> torch.Tensor:
+    """Computes this rank's block of op(lhs).op(rhs).
+
+    Returns the local block (a dense tensor) when `gather` is False, else the full result on
+    every rank.  `out`, if given, is the full-size result tensor to fill (gather) or the local
+    block.  `matmul_into_fn(out, lhs, tl, rhs, tr)` defaults to the CUDA operator; tests on CPU
+    ranks inject their own."""
+    if axis not in AXES:
+        raise ValueError(f"axis must be one of {AXES}")
+    if matmul_into_fn is None:
+        from .matmul import matmul_into as matmul_into_fn
+    if world is None:
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if rank is None:
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    a_rows = lhs.shape[-1] if transposed_lhs else lhs.shape[-2]
+    b_cols = rhs.shape[-2] if transposed_rhs else rhs.shape[-1]
+    batched = lhs.dim() == 3 or rhs.dim() == 3
+    nb = max(lhs.shape[0] if lhs.dim() == 3 else 1, rhs.shape[0] if rhs.dim() == 3 else 1)
+    if axis == "batch" and not batched:
+        raise ValueError("batch sharding needs a rank-3 operand")
+    total = {"batch": nb, "m": a_rows, "n": b_cols}[axis]
+    align = 8 if axis == "n" and lhs.element_size() == 2 else (4 if axis == "n" else 1)
+    lo, hi = shard_range(total, world, rank, align)
+    a, b = _slice_operands(lhs, transposed_lhs, rhs, transposed_rhs, axis, lo, hi)
+
+    full_shape = ((nb,) if batched else ()) + (a_rows, b_cols)
+    dim = {"batch": 0, "m": len(full_shape) - 2, "n": len(full_shape) - 1}[axis]
+    local_shape = list(full_shape)
+    local_shape[dim] = hi - lo
+
+    if not gather:
+        local = out if out is not None else torch.empty(local_shape, dtype=lhs.dtype, device=lhs.device)
+        if hi > lo:
+            matmul_into_fn(local, a, transposed_lhs, b, transposed_rhs)
+        return local
+
+    full = out if out is not None else torch.empty(full_shape, dtype=lhs.dtype, device=lhs.device)
+    if world == 1:
+        matmul_into_fn(full, a, transposed_lhs, b, transposed_rhs)
+        return full
+    if dim == 0 and full.is_contiguous() and total % world == 0 and (total // world) % align == 0:
+        # equal contiguous blocks along the outermost dim: compute in place, gather in place
+        if hi > lo:
+            matmul_into_fn(full.narrow(0, lo, hi - lo), a, transposed_lhs, b, transposed_rhs)
+        dist.all_gather_into_tensor(full, full.narrow(0, lo, hi - lo), group=group)
+        return full
+    # general case (inner-dim blocks, ragged shards): every rank contributes a dense block padded
+    # to the longest shard, the blocks are gathered into a staging tensor and placed
+    longest = max(shard_range(total, world, r, align)[1] - shard_range(total, world, r, align)[0]
+                  for r in range(world))
+    pad_shape = list(full_shape)
+    pad_shape[dim] = longest
+    staging = torch.empty([world] + pad_shape, dtype=lhs.dtype, device=lhs.device)
+    mine = staging[rank]
+    if hi > lo:
+        matmul_into_fn(mine.narrow(dim, 0, hi - lo), a, transposed_lhs, b, transposed_rhs)
+    dist.all_gather_into_tensor(staging.flatten(0, 1), mine, group=group)   # blocks concatenated along dim 0
+    for r in range(world):
+        r_lo, r_hi = shard_range(total, world, r, align)
+        if r_hi > r_lo:
+            full.narrow(dim, r_lo, r_hi - r_lo).copy_(staging[r].narrow(dim, 0, r_hi - r_lo))
+    return full

@@ -1,0 +1,329 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Bit-exact where the arithmetic order is the reference's (the strided SIMT kernel); within the
+path's tolerances (relative Frobenius error <= 1e-5 Float32, <= 1e-2 Float16 / BFloat16 with
+fp32 accumulation) on the tensor-core kernel, whose accumulation order differs."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from _gpu_util import BF16, F16, F32, TOL, TORCH_DTYPE, from_dev, random_bits, to_dev
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "matmul_kat.json")
+SIMT, TC = 1, 2
+TRANSPOSES = [(False, False), (False, True), (True, False), (True, True)]
+
+
+@pytest.fixture(scope="module")
+def srt():
+    import swiftrt_b200 as s
+    assert torch.cuda.is_available(), "these tests need a GPU"
+    yield s
+    s.set_tuning(0, 0, 0, 0)
+
+
+@pytest.fixture(autouse=True)
+def _reset_tuning_and_check_status(srt):
+    srt.set_tuning(0, 0, 0, 0)
+    yield
+    assert srt.check_status() == 0, "a pipeline wait of the tensor-core kernel timed out"
+    srt.set_tuning(0, 0, 0, 0)
+
+
+def _shapes(M, N, K, ta, tb, batch=0):
+    ash = (K, M) if ta else (M, K)
+    bsh = (N, K) if tb else (K, N)
+    if batch:
+        ash, bsh = (batch,) + ash, (batch,) + bsh
+    return ash, bsh
+
+
+def _run(srt, oracle, dtype, a, b, ta, tb, bias=None, act=None, expect_kernel=None, out=None, da=None, db=None):
+    """a, b, bias: numpy stored bits (any strides); da, db: the same operands already on the device
+    (for views whose base offset matters).  Returns (gpu bits, oracle bits)."""
+    ref = oracle.matmul(a, b, dtype, ta, tb, bias=bias, activation=act)
+    da = to_dev(a, dtype) if da is None else da
+    db = to_dev(b, dtype) if db is None else db
+    dbias = to_dev(bias, dtype) if bias is not None else None
+    activation = srt.ActivationType[act] if act else None
+    if out is None:
+        c = srt.matmul(da, db, ta, tb, bias=dbias, activation=activation)
+    else:
+        c = srt.matmul_into(out, da, ta, db, tb, dbias, activation)
+    if expect_kernel is not None:
+        assert srt.query_plan(da, db, c, ta, tb)["kernel"] == expect_kernel
+    torch.cuda.synchronize()
+    return from_dev(c, dtype), ref
+
+
+# ------------------------------------------------------------------ the reference's known answers
+def test_known_answers_on_gpu(srt):
+    cases = json.load(open(GOLDEN))["cases"]
+    dev = "cuda:0"
+    for name, case in cases.items():
+        a = torch.arange(int(np.prod(case["a_shape"])), dtype=torch.float32, device=dev).reshape(case["a_shape"])
+        b = torch.arange(int(np.prod(case["b_shape"])), dtype=torch.float32, device=dev).reshape(case["b_shape"])
+        c = srt.matmul(a, b)
+        if "c" in case:
+            assert c.cpu().tolist() == case["c"], name
+        else:
+            assert c[0].cpu().tolist() == case["c_first_item"], name
+    # gradients of test_matmul through matmulGradients' two extra matmul calls
+    case = cases["test_matmul"]
+    a = torch.arange(6.0, device=dev).reshape(3, 2)
+    b = torch.arange(8.0, device=dev).reshape(2, 4)
+    ga, gb = srt.matmul_gradients(torch.ones(3, 4, device=dev), a, False, b, False)
+    assert ga.cpu().tolist() == case["grad_a"] and gb.cpu().tolist() == case["grad_b"]
+    # batched gradients: per-item products, literal by literal
+    case = cases["test_batchMatmul"]
+    a = torch.arange(12.0, device=dev).reshape(2, 3, 2)
+    b = torch.arange(16.0, device=dev).reshape(2, 2, 4)
+    ones = torch.ones(2, 3, 4, device=dev)
+    assert srt.matmul(ones, b, False, True).cpu().tolist() == case["grad_a"]
+    assert srt.matmul(a, ones, True, False).cpu().tolist() == case["grad_b"]
+
+
+# ------------------------------------------------------------------ strided kernel: bit-exact
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("ta,tb", TRANSPOSES)
+@pytest.mark.parametrize("M,N,K,batch", [(1, 1, 1, 0), (3, 4, 2, 0), (65, 70, 33, 0), (64, 64, 64, 3), (130, 17, 257, 2), (1, 50, 300, 0), (40, 1, 77, 0)])
+def test_strided_kernel_is_bit_exact(srt, oracle, dtype, ta, tb, M, N, K, batch):
+    srt.set_tuning(SIMT, 0, 0, 0)
+    rng = np.random.default_rng(M * 1000 + N * 10 + K + dtype)
+    ash, bsh = _shapes(M, N, K, ta, tb, batch)
+    a, b = random_bits(oracle, rng, ash, dtype), random_bits(oracle, rng, bsh, dtype)
+    got, ref = _run(srt, oracle, dtype, a, b, ta, tb, expect_kernel=SIMT)
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+def test_strided_kernel_views_bias_relu_bit_exact(srt, oracle, dtype):
+    srt.set_tuning(SIMT, 0, 0, 0)
+    rng = np.random.default_rng(11 + dtype)
+    big_a, big_b = random_bits(oracle, rng, (70, 90), dtype), random_bits(oracle, rng, (90, 80), dtype)
+    a, b = big_a[3:63:2, 5:85:3], big_b[10:37, 1:61:4]          # no unit stride, odd offsets
+    bias = random_bits(oracle, rng, (30,), dtype)[::2]            # strided bias
+    got, ref = _run(srt, oracle, dtype, a, b, False, False, bias=bias, act="relu", expect_kernel=SIMT)
+    assert np.array_equal(got, ref)
+    got, ref = _run(srt, oracle, dtype, a, b, False, False, bias=bias, act="identity")
+    assert np.array_equal(got, ref)
+
+
+def test_output_view_is_honoured_and_nothing_else_is_written(srt, oracle):
+    rng = np.random.default_rng(12)
+    a, b = random_bits(oracle, rng, (33, 20), F32), random_bits(oracle, rng, (20, 15), F32)
+    canvas = torch.full((40, 64), 7.0, device="cuda:0")
+    view = canvas[2:35, 3:48:3]                                  # 33 x 15, column stride 3
+    got, ref = _run(srt, oracle, F32, a, b, False, False, out=view, expect_kernel=SIMT)
+    assert np.array_equal(got, ref)
+    mask = torch.ones_like(canvas, dtype=torch.bool)
+    mask[2:35, 3:48:3] = False
+    assert bool((canvas[mask] == 7.0).all())
+
+
+def test_broadcast_operands_left_and_right_batch(srt, oracle):
+    rng = np.random.default_rng(13)
+    a3, b2 = random_bits(oracle, rng, (4, 9, 6), F32), random_bits(oracle, rng, (6, 5), F32)
+    ref = oracle.matmul(a3, np.broadcast_to(b2, (4, 6, 5)), F32)
+    c = srt.matmul(to_dev(a3, F32), to_dev(b2, F32))
+    assert np.array_equal(from_dev(c, F32), ref)
+    a2, b3 = random_bits(oracle, rng, (9, 6), F32), random_bits(oracle, rng, (4, 6, 5), F32)
+    ref = oracle.matmul(np.broadcast_to(a2, (4, 9, 6)), b3, F32)
+    c = srt.matmul(to_dev(a2, F32), to_dev(b3, F32))
+    assert np.array_equal(from_dev(c, F32), ref)
+
+
+@pytest.mark.parametrize("act", ["sigmoid", "tanh", "gelu", "geluTanh"])
+def test_transcendental_activations(srt, oracle, act):
+    rng = np.random.default_rng(14)
+    a, b = random_bits(oracle, rng, (50, 40), F32, scale=2.0), random_bits(oracle, rng, (40, 30), F32)
+    bias = random_bits(oracle, rng, (30,), F32)
+    got, ref = _run(srt, oracle, F32, a, b, False, False, bias=bias, act=act)
+    assert oracle.rel_frobenius(got, ref) <= TOL[F32]
+
+
+# ------------------------------------------------------------------ tensor-core kernel
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("ta,tb", TRANSPOSES)
+@pytest.mark.parametrize("M,N,K,batch,tile_n", [
+    (128, 256, 64, 0, 0), (1000, 520, 200, 0, 0), (8, 8, 8, 0, 256), (136, 264, 72, 0, 128),
+    (512, 384, 1024, 0, 64), (256, 512, 64, 5, 0), (2048, 1024, 4096, 0, 0)])
+def test_tensor_core_kernel_within_tolerance(srt, oracle, dtype, ta, tb, M, N, K, batch, tile_n):
+    srt.set_tuning(TC, tile_n, 0, 0)
+    rng = np.random.default_rng(M + 3 * N + 7 * K + dtype + 2 * ta + tb)
+    ash, bsh = _shapes(M, N, K, ta, tb, batch)
+    a, b = random_bits(oracle, rng, ash, dtype), random_bits(oracle, rng, bsh, dtype)
+    got, ref = _run(srt, oracle, dtype, a, b, ta, tb, expect_kernel=TC)
+    err = oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype))
+    assert err <= TOL[dtype]
+    assert err <= 2e-3          # far inside the tolerance: only the final rounding can differ
+
+
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("act,with_bias", [("relu", True), ("identity", True), ("relu", False), ("gelu", True)])
+def test_tensor_core_fused_epilogue(srt, oracle, dtype, act, with_bias):
+    srt.set_tuning(TC, 0, 0, 0)
+    rng = np.random.default_rng(21 + dtype)
+    a = random_bits(oracle, rng, (300, 256), dtype, scale=0.05)
+    w = random_bits(oracle, rng, (256, 520), dtype, scale=0.05)
+    bias = random_bits(oracle, rng, (520,), dtype, scale=0.05) if with_bias else None
+    got, ref = _run(srt, oracle, dtype, a, w, False, False, bias=bias, act=act, expect_kernel=TC)
+    assert oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype)) <= 2e-3
+
+
+def test_tensor_core_views_alignment_decides_the_kernel(srt, oracle):
+    rng = np.random.default_rng(22)
+    big_a, big_b = random_bits(oracle, rng, (300, 512), BF16), random_bits(oracle, rng, (512, 400), BF16)
+    dev_a, dev_b = to_dev(big_a, BF16), to_dev(big_b, BF16)
+    # 16-byte aligned sub-views with legal strides stay on the tensor cores
+    got, ref = _run(srt, oracle, BF16, big_a[4:260, 64:448], big_b[64:448, 8:392], False, False, expect_kernel=TC,
+                    da=dev_a[4:260, 64:448], db=dev_b[64:448, 8:392])
+    assert oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16)) <= 2e-3
+    # an odd element offset breaks the 16-byte base alignment: strided kernel, bit-exact
+    got, ref = _run(srt, oracle, BF16, big_a[4:260, 63:447], big_b[63:447, 8:392], False, False, expect_kernel=SIMT,
+                    da=dev_a[4:260, 63:447], db=dev_b[63:447, 8:392])
+    assert np.array_equal(got, ref)
+
+
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_col_order_output_runs_transposed_problem_with_row_bias(srt, oracle, dtype):
+    """A col-order lhs gives a col-order result (Matmul.swift:36-38): computed as out^T = B^T . A^T."""
+    srt.set_tuning(TC, 0, 0, 0)
+    rng = np.random.default_rng(23)
+    a, b = random_bits(oracle, rng, (264, 200), dtype), random_bits(oracle, rng, (200, 136), dtype)
+    bias = random_bits(oracle, rng, (136,), dtype)
+    ref = oracle.matmul(a, b, dtype, bias=bias, activation="relu")
+    a_col = to_dev(np.asfortranarray(a), dtype)                  # logical [264 x 200], strides (1, 264)
+    assert srt.order_of(a_col) == srt.Order.col
+    c = srt.matmul(a_col, to_dev(b, dtype), bias=to_dev(bias, dtype), activation=srt.ActivationType.relu)
+    assert srt.order_of(c) == srt.Order.col and c.stride() == (1, 264)
+    plan = srt.query_plan(a_col, to_dev(b, dtype), c)
+    assert plan["kernel"] == TC and plan["swapped"] == 1
+    got = from_dev(c, dtype)
+    assert oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype)) <= 2e-3
+
+
+def test_identity_and_permutation_products_are_exact_at_full_size(srt):
+    """Size-independent property at the large-square configuration's size: A . I == A and
+    A . P permutes columns, bit for bit (every sum has one non-zero term)."""
+    n = 16384
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = (torch.rand((n, n), device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
+    eye = torch.eye(n, dtype=torch.bfloat16, device=dev)
+    c = srt.matmul(a, eye)
+    assert torch.equal(c, a)
+    perm = torch.randperm(n, device=dev, generator=g)
+    c = srt.matmul(a, eye[:, perm].contiguous())
+    assert torch.equal(c, a[:, perm])
+    c = srt.matmul(eye, a, False, True)                          # I . A^T
+    assert torch.equal(c, a.t())
+
+
+# ------------------------------------------------------------------ the five named configurations
+def _sample_rows(M, count, tile=128):
+    """Rows covering both matrix edges and every residue class of the tile height."""
+    rng = np.random.default_rng(0)
+    rows = {0, M - 1, tile - 1 if M >= tile else 0, min(M - 1, tile)}
+    while len(rows) < min(count, M):
+        rows.add(int(rng.integers(0, M)))
+    return sorted(rows)
+
+
+def test_config1_float32_256_cubed(srt, oracle):
+    rng = np.random.default_rng(0)
+    a, b = random_bits(oracle, rng, (256, 256), F32), random_bits(oracle, rng, (256, 256), F32)
+    got, ref = _run(srt, oracle, F32, a, b, False, False)
+    assert oracle.rel_frobenius(got, ref) <= TOL[F32]
+    assert np.array_equal(got, ref)           # the fp32 path keeps the reference's arithmetic order
+
+
+def test_config2_dense_bf16_bias_relu(srt, oracle):
+    rng = np.random.default_rng(0)
+    x = random_bits(oracle, rng, (1024, 4096), BF16, scale=0.05)
+    w = random_bits(oracle, rng, (4096, 4096), BF16, scale=0.05)
+    bias = random_bits(oracle, rng, (4096,), BF16, scale=0.05)
+    layer = srt.Dense(to_dev(w, BF16), to_dev(bias, BF16), srt.ActivationType.relu)
+    dx = to_dev(x, BF16)
+    y = layer(dx)
+    assert srt.query_plan(dx, layer.weight, y)["kernel"] == TC
+    ref = oracle.matmul(x, w, BF16, bias=bias, activation="relu")
+    got = from_dev(y, BF16)
+    err = oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16))
+    assert err <= TOL[BF16] and err <= 2e-3
+
+
+def test_config3_batched_fp16_attention_score_shape(srt, oracle):
+    rng = np.random.default_rng(0)
+    a = random_bits(oracle, rng, (64, 512, 64), F16, dist="normal")
+    b = random_bits(oracle, rng, (64, 512, 64), F16, dist="normal")
+    got, ref = _run(srt, oracle, F16, a, b, False, True, expect_kernel=TC)
+    err = oracle.rel_frobenius(oracle.decode(got, F16), oracle.decode(ref, F16))
+    assert err <= TOL[F16] and err <= 2e-3
+
+
+def test_config4_tall_skinny_float32(srt, oracle):
+    rng = np.random.default_rng(0)
+    a, b = random_bits(oracle, rng, (65536, 1024), F32), random_bits(oracle, rng, (1024, 256), F32)
+    da, db = to_dev(a, F32), to_dev(b, F32)
+    c = srt.matmul(da, db)
+    got = from_dev(c, F32)
+    rows = _sample_rows(65536, 2048)
+    ref = oracle.matmul(np.ascontiguousarray(a[rows]), b, F32)
+    assert oracle.rel_frobenius(got[rows], ref) <= TOL[F32]
+    # column checksums over ALL rows against float64: sum_i C_ij = (sum_i A_i.) . B_.j ; a lost or
+    # duplicated tile row would move a column sum by hundreds, rounding moves it by ~1e-2
+    want = a.astype(np.float64).sum(axis=0) @ b.astype(np.float64)
+    assert float(np.abs(got.astype(np.float64).sum(axis=0) - want).max()) < 1.0
+
+
+def test_config5_large_square_bf16(srt, oracle):
+    n = 16384
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = (torch.rand((n, n), device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
+    b = (torch.rand((n, n), device=dev, generator=g) * 2 - 1).to(torch.bfloat16)
+    c = srt.matmul(a, b)
+    assert srt.query_plan(a, b, c)["kernel"] in (TC, 3)
+    # sampled rows against the CPU oracle on the same stored bits
+    rows = _sample_rows(n, 24)
+    idx = torch.tensor(rows, device=dev)
+    a_rows = from_dev(a[idx], BF16)
+    b_host = from_dev(b, BF16)
+    ref = oracle.matmul(a_rows, b_host, BF16)
+    got = from_dev(c[idx], BF16)
+    err = oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16))
+    assert err <= TOL[BF16] and err <= 2e-3
+    # a band of 1024 full rows against the reference-ordered strided kernel (itself bit-exact with the oracle)
+    srt.set_tuning(SIMT, 0, 0, 0)
+    band = slice(7 * 1024 + 64, 8 * 1024 + 64)
+    exact = srt.matmul(a[band].contiguous(), b)
+    diff = (c[band].float() - exact.float()).norm() / exact.float().norm()
+    assert float(diff) <= 2e-3
+
+
+# ------------------------------------------------------------------ host buffers and bookkeeping
+def test_host_buffer_entry_and_launch_counter(srt, oracle):
+    rng = np.random.default_rng(31)
+    a, b = random_bits(oracle, rng, (256, 384), BF16), random_bits(oracle, rng, (384, 512), BF16)
+    ha = torch.from_numpy(a).view(torch.bfloat16).pin_memory()
+    hb = torch.from_numpy(b).view(torch.bfloat16).pin_memory()
+    before = srt.launch_count()
+    hc = srt.matmul_host(ha, hb)
+    assert srt.launch_count() == before + 1
+    assert not hc.is_cuda
+    ref = oracle.matmul(a, b, BF16)
+    got = hc.view(torch.uint16).numpy()
+    assert oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16)) <= 2e-3
+
+
+def test_unsupported_inputs_return_not_supported(srt):
+    a = torch.zeros((4, 4), dtype=torch.float64, device="cuda:0")
+    with pytest.raises(srt.MatmulError) as e:
+        srt.matmul(a, a)
+    assert e.value.code == 801
