@@ -161,6 +161,37 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier):
+    """End to end: host buffers in, host result out, copies inside the timed region."""
+    import torch
+    import torch.distributed as dist
+    tdt = a.dtype
+    flops = 2.0 * M * N * K
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    ha = a.cpu().pin_memory()
+    hb = b.contiguous().cpu().pin_memory()
+    hc = torch.empty((M, n_local), dtype=tdt).pin_memory()
+    srt.matmul_host(ha, hb, device=dev, out_host=hc)      # warm-up (allocator, pinned pages)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        srt.matmul_host(ha, hb, device=dev, out_host=hc)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+    h2d = (ha.numel() + hb.numel()) * ha.element_size()
+    d2h = hc.numel() * hc.element_size()
+    bytes_t = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(bytes_t, op=dist.ReduceOp.SUM)
+    return {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+            "h2d_bytes_per_step": int(bytes_t[0].item()), "d2h_bytes_per_step": int(bytes_t[1].item())}
+
+
 # ---------------------------------------------------------------------------------------------
 def run_ours(args):
     import torch
@@ -196,13 +227,15 @@ def run_ours(args):
     def step():
         srt.matmul_into(c, a, False, b, False)
 
+    if args.tune:
+        srt.set_tuning(*[int(x) for x in args.tune.split(",")])
     plan = srt.query_plan(a, b, c)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()          # nvidia-smi needs ~0.1 s to deliver its first sample: start it early
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = srt.launch_count()
     events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
@@ -226,28 +259,9 @@ def run_ours(args):
     flops = 2.0 * M * N * K
     value = flops / (ms_per_step * 1e-3) / 1e12
 
-    # end to end: host buffers in, host result out, copies inside the timed region
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    ha = a.cpu().pin_memory()
-    hb = b.contiguous().cpu().pin_memory()
-    hc = torch.empty((M, n_local), dtype=tdt).pin_memory()
-    srt.matmul_host(ha, hb, device=dev, out_host=hc)      # warm-up (allocator, pinned pages)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        srt.matmul_host(ha, hb, device=dev, out_host=hc)
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
-    h2d = (ha.numel() + hb.numel()) * ha.element_size()
-    d2h = hc.numel() * hc.element_size()
-    bytes_t = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(bytes_t, op=dist.ReduceOp.SUM)
+    e2e = None
+    if not args.no_e2e:
+        e2e = measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier)
 
     if rank == 0:
         pk, pk_kind = peaks()
@@ -266,9 +280,7 @@ def run_ours(args):
             "config": {"workload": desc, "M": M, "N": N, "K": K, "sharding": f"N over {world} rank(s), no collective",
                        "l2": "inputs (512 MiB each) larger than the 126 MB L2", "plan": plan},
             "roofline": roofline,
-            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "steps": e2e_steps, "h2d_bytes_per_step": int(bytes_t[0].item()),
-                    "d2h_bytes_per_step": int(bytes_t[1].item())},
+            "e2e": e2e,
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
@@ -291,6 +303,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--tune", default="", help="forceKernel,tileN,stages,maxCtas for srtMatmulSetTuning (0 = automatic)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

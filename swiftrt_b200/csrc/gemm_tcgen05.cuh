@@ -336,4 +336,216 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant (tcgen05 cta_group::2): a cluster of two CTAs computes one 256 x BN tile.
+// CTA r of the pair loads rows [m0 + 128 r, +128) of A and rows/columns [n0 + BN/2 r, +BN/2) of
+// B, so every byte of the tile's operands is fetched once per pair (2/3 of the shared-memory
+// fill traffic of two independent 128 x BN tiles).  One thread of CTA 0 issues the MMAs for
+// both CTAs; each CTA's TMEM receives its own 128 rows of the accumulator and its own epilogue
+// warps drain them.
+//
+// Synchronisation (stage s, accumulator buffer b):
+//   full[s]      CTA 0 only: its producer arms it with the bytes of BOTH CTAs' loads; the loads
+//                of CTA 1 complete their byte count on CTA 0's barrier (cta_group::2 form).
+//   empty[s]     both CTAs, signalled together by one multicast tcgen05.commit of CTA 0.
+//   tmem_full[b] both CTAs, multicast tcgen05.commit after the tile's last MMA.
+//   tmem_empty[b] CTA 0 only, count 8: the four epilogue warps of each CTA.
+// No TMA load is multicast; all loads are plain per-CTA tile loads.
+template <typename T, uint32_t BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ GemmParams p)
+{
+    constexpr uint32_t kBHalf = BN / 2;
+    constexpr uint32_t kBTileBytes = kBHalf * kRowBytes;
+    constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+    constexpr uint32_t kTmemCols = 2 * BN;
+    constexpr uint32_t kMaxStages = 8;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tmem_full_bar[2];
+    __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t stages = p.stages;
+    const uint32_t cta_rank = cluster_ctarank();          // 0 = leader
+    const uint32_t pair_id = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&tmem_full_bar[i]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[i]), 8);
+        }
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_cta2(smem_u32(&tmem_holder), kTmemCols);
+        tmem_relinquish_cta2();
+    }
+    tc_fence_before_sync();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+                uint32_t batch, m0, n0;
+                decode_tile(p, tile, BN, batch, m0, n0);
+                m0 = m0 * 2 + cta_rank * kTileM;            // decode_tile counts 128-row units; pair tiles are 256 rows
+                n0 += cta_rank * kBHalf;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    // every load of the pair reports to the leader's barrier
+                    const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+                    const int32_t k0 = static_cast<int32_t>(kb * p.kb_elems);
+                    if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * p.stage_tx_bytes);
+                    if (!p.a.mn_major) {
+                        tma_load_3d_pair(sa, &tmap_a, bar, k0, m0, batch * p.a.batch_mul);
+                    } else {
+                        for (uint32_t c = 0; c < p.a.chunks; ++c)
+                            tma_load_3d_pair(sa + c * p.a.chunk_bytes, &tmap_a, bar, m0 + c * p.a.chunk_elems, k0,
+                                             batch * p.a.batch_mul);
+                    }
+                    if (!p.b.mn_major) {
+                        tma_load_3d_pair(sb, &tmap_b, bar, k0, n0, batch * p.b.batch_mul);
+                    } else {
+                        for (uint32_t c = 0; c < p.b.chunks; ++c)
+                            tma_load_3d_pair(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0,
+                                             batch * p.b.batch_mul);
+                    }
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                abort_flag = 1;
+                atomicOr(&g_gemm_status, kStatusProducerTimeout);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool ok = true;
+            if (cta_rank == 0) {
+                // -------------------------------------------------------------- MMA issuer (leader)
+                for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
+                    const uint32_t buf = local & 1;
+                    const uint32_t acc_phase = (local >> 1) & 1;
+                    if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                        if (!mbar_wait_cluster(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t sa = smem_base + stage * kStageBytes;
+                        const uint32_t sb = sa + kATileBytes;
+                        const uint32_t a_lo = ((sa >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                        const uint32_t b_lo = ((sb >> 4) & 0x3fffu) | p.b.desc_lo_fixed;
+#pragma unroll
+                        for (uint32_t k = 0; k < kKStepsPerStage; ++k) {
+                            const uint64_t adesc = (static_cast<uint64_t>(p.a.desc_hi) << 32) | (a_lo + k * p.a.kstep);
+                            const uint64_t bdesc = (static_cast<uint64_t>(p.b.desc_hi) << 32) | (b_lo + k * p.b.kstep);
+                            if constexpr (sizeof(T) == 4) umma_tf32_cta2(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+                            else                          umma_f16_cta2(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+                        }
+                        umma_commit_cta2_mc(smem_u32(&empty_bar[stage]), 3);
+                        if (++stage == stages) { stage = 0; phase ^= 1; }
+                    }
+                    if (ok) umma_commit_cta2_mc(smem_u32(&tmem_full_bar[buf]), 3);
+                }
+                if (!ok) {
+                    abort_flag = 1;
+                    atomicOr(&g_gemm_status, kStatusMmaTimeout);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const uint32_t quarter = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        T* const out = static_cast<T*>(p.out);
+        const T* const bias = static_cast<const T*>(p.bias);
+        for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
+            uint32_t batch, m0, n0;
+            decode_tile(p, tile, BN, batch, m0, n0);
+            m0 = m0 * 2 + cta_rank * kTileM;
+            const uint32_t buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t row = m0 + quarter * 32 + lane;
+            T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
+            float row_bias = 0.0f;
+            if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                const uint32_t col0 = n0 + c * 32;
+                if (col0 >= p.N) break;
+                uint32_t raw[32];
+                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32, raw);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+                if (p.bias_mode == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) v[j] += to_float<T>(__ldg(bias + static_cast<long long>(col0 + j) * p.bias_stride));
+                } else if (p.bias_mode == 2) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += row_bias;
+                }
+                if (p.act != kActIdentity) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = apply_activation(p.act, v[j]);
+                }
+                if (row < p.M) store_row_chunk<T>(p, row_ptr, col0, v);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
+        }
+        if (!ok) {
+            abort_flag = 1;
+            if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    // no CTA may leave while its peer can still signal its barriers or read its shared memory
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        if (abort_flag != 0) __nanosleep(1000000);
+        tmem_dealloc_cta2(tmem_base, kTmemCols);
+    }
+    cluster_arrive_release();
+    cluster_wait_acquire();
+}
+
 }  // namespace srt

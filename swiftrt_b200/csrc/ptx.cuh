@@ -144,6 +144,28 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
         : "memory");
 }
 
+// Same load issued by one CTA of a cta_group::2 pair: the data lands in this CTA's shared
+// memory, the byte count is signalled on `bar_cluster`, a shared::cluster address that may
+// name the barrier of either CTA of the pair (see map_to_cta).  Not a multicast: one
+// destination CTA.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster,
+                                                 int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// shared::cluster address of the same shared-memory offset in CTA `cta_rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+    return r;
+}
+
 // ----------------------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc_cta1(uint32_t holder_smem, uint32_t ncols)
 {

@@ -9,6 +9,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -255,9 +256,9 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         if (Q.N > 1 && Q.o_m < (long long)Q.N && Q.M > 1) tc = false;   // overlapping output rows
     }
     // fp32 on the tensor cores is TF32 (10-bit mantissa): only on explicit request
-    if (tc && Q.type == real32F && force != srtMatmulKernelTcgen05) tc = false;
+    if (tc && Q.type == real32F && force != srtMatmulKernelTcgen05 && force != srtMatmulKernelTcgen05Pair) tc = false;
     // tiny problems are launch-bound either way; keep them on the exact kernel
-    if (tc && force != srtMatmulKernelTcgen05 && Q.M * Q.N * Q.K * Q.batch < (1ull << 18)) tc = false;
+    if (tc && force == 0 && Q.M * Q.N * Q.K * Q.batch < (1ull << 18)) tc = false;
 
     if (!tc) {
         plan.Q = P;
@@ -275,26 +276,37 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
 
     plan.Q = Q;
     uint32_t bn = (uint32_t)g_tuning.tile_n.load();
-    if (bn != 64 && bn != 128 && bn != 256) {
+    // CTA pairs (256 x BN tiles) when the problem has enough 256-row tiles to fill the device
+    bool pair = false;
+    if (force == srtMatmulKernelTcgen05Pair) pair = true;
+    else if (force == 0) pair = Q.M >= 256 && ((Q.M + 255) / 256) * ((Q.N + 255) / 256) * Q.batch >= (uint64_t)dev.sms;
+    const uint32_t tile_m = pair ? 2 * kTileM : kTileM;
+    if (pair) {
+        if (bn != 128 && bn != 256) bn = Q.N <= 128 ? 128 : 256;
+    } else if (bn != 64 && bn != 128 && bn != 256) {
         // widest tile that still gives every SM work; narrow tiles for narrow outputs
         const uint64_t tm = (Q.M + kTileM - 1) / kTileM;
         bn = 256;
         while (bn > 64 && (Q.N <= bn / 2 || tm * ((Q.N + bn - 1) / bn) * Q.batch < (uint64_t)dev.sms)) bn /= 2;
     }
-    const uint32_t stage_bytes = kATileBytes + bn * kRowBytes;
+    const uint32_t stage_bytes = kATileBytes + (pair ? bn / 2 : bn) * kRowBytes;
     uint32_t stages = (uint32_t)g_tuning.stages.load();
     const uint32_t max_stages = (227u * 1024u - 2048u) / stage_bytes;
-    if (stages < 2 || stages > 8) stages = 8;
+    // Four 32 KB stages keep the pair kernel's MMAs fed; deeper rings measured slower on a
+    // power-capped B200 (higher pipe utilisation, lower clock, lower L2 hit rate).
+    if (stages < 2 || stages > 8) stages = pair ? 4 : 8;
     if (stages > max_stages) stages = max_stages;
     const uint32_t kb_elems = kRowBytes / Q.elem;
-    const uint64_t tiles_m = (Q.M + kTileM - 1) / kTileM, tiles_n = (Q.N + bn - 1) / bn;
+    const uint64_t tiles_m = (Q.M + tile_m - 1) / tile_m, tiles_n = (Q.N + bn - 1) / bn;
     const uint64_t tiles = tiles_m * tiles_n * Q.batch;
-    uint32_t ctas = (uint32_t)(tiles < (uint64_t)dev.sms ? tiles : (uint64_t)dev.sms);
+    const uint64_t units = pair ? (uint64_t)dev.sms / 2 : (uint64_t)dev.sms;   // CTAs or CTA pairs
+    uint32_t ctas = (uint32_t)(tiles < units ? tiles : units);
     const int32_t cap = g_tuning.max_ctas.load();
     if (cap > 0 && ctas > (uint32_t)cap) ctas = (uint32_t)cap;
+    if (pair) ctas *= 2;
 
-    plan.pub.kernel = srtMatmulKernelTcgen05;
-    plan.pub.tileM = kTileM; plan.pub.tileN = (int32_t)bn; plan.pub.tileK = (int32_t)kb_elems;
+    plan.pub.kernel = pair ? srtMatmulKernelTcgen05Pair : srtMatmulKernelTcgen05;
+    plan.pub.tileM = (int32_t)tile_m; plan.pub.tileN = (int32_t)bn; plan.pub.tileK = (int32_t)kb_elems;
     plan.pub.stages = (int32_t)stages;
     plan.pub.ctas = (int32_t)ctas;
     plan.pub.tiles = (int32_t)tiles;
@@ -370,32 +382,77 @@ cudaError_t launch_tc_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& 
     }
 }
 
+template <typename T, uint32_t BN>
+cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas, size_t smem,
+                        cudaStream_t stream)
+{
+    auto kernel = gemm_tcgen05_pair_kernel<T, BN>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // SMs that cannot be paired inside their GPC stay idle: never ask for more pairs than fit at once
+    int max_clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+    if (e != cudaSuccess) return e;
+    if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
+    if (ctas / 2 > (uint32_t)max_clusters) cfg.gridDim.x = 2u * (uint32_t)max_clusters;
+    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, gp);
+}
+
+template <typename T>
+cudaError_t launch_pair_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp,
+                           uint32_t ctas, size_t smem, cudaStream_t stream)
+{
+    if (bn == 128) return launch_pair<T, 128>(ma, mb, gp, ctas, smem, stream);
+    return launch_pair<T, 256>(ma, mb, gp, ctas, smem, stream);
+}
+
 cudaError_t run_tc(const Plan& plan, cudaStream_t stream)
 {
     const Problem& Q = plan.Q;
+    const bool pair = plan.pub.kernel == srtMatmulKernelTcgen05Pair;
     const uint32_t bn = (uint32_t)plan.pub.tileN;
+    const uint32_t tile_m = (uint32_t)plan.pub.tileM;
+    const uint32_t b_rows = pair ? bn / 2 : bn;           // rows of B each CTA stages
     GemmParams gp;
     memset(&gp, 0, sizeof gp);
     CUtensorMap ma, mb;
     cudaError_t e = encode_operand(&ma, Q, Q.a, plan.ta, Q.M, Q.a_b, kTileM, gp.a);
     if (e != cudaSuccess) return e;
-    e = encode_operand(&mb, Q, Q.b, plan.tb, Q.N, Q.b_b, bn, gp.b);
+    e = encode_operand(&mb, Q, Q.b, plan.tb, Q.N, Q.b_b, b_rows, gp.b);
     if (e != cudaSuccess) return e;
 
     gp.M = (uint32_t)Q.M; gp.N = (uint32_t)Q.N; gp.K = (uint32_t)Q.K; gp.batch = (uint32_t)Q.batch;
-    gp.tiles_m = (uint32_t)((Q.M + kTileM - 1) / kTileM);
+    gp.tiles_m = (uint32_t)((Q.M + tile_m - 1) / tile_m);
     gp.tiles_n = (uint32_t)((Q.N + bn - 1) / bn);
     gp.tiles_per_batch = gp.tiles_m * gp.tiles_n;
     gp.num_tiles = (uint32_t)plan.pub.tiles;
     gp.kb_elems = kRowBytes / Q.elem;
     gp.k_blocks = (uint32_t)((Q.K + gp.kb_elems - 1) / gp.kb_elems);
-    gp.group_m = 16;
+    gp.group_m = pair ? 8 : 16;                           // 2048 rows of A per group either way
+    {
+        // experiment knob (not part of the ABI): rows of tiles per rasterisation group
+        static const int env_group = [] { const char* e = getenv("SRT_MATMUL_GROUP_M"); return e ? atoi(e) : 0; }();
+        if (env_group > 0) gp.group_m = (uint32_t)env_group;
+    }
     gp.stages = (uint32_t)plan.pub.stages;
-    gp.stage_tx_bytes = kATileBytes + bn * kRowBytes;
+    gp.stage_tx_bytes = kATileBytes + b_rows * kRowBytes;
     // instruction descriptor: fp32 accumulator, input format, majorness, N >> 3, M >> 4
     const uint32_t fmt = Q.type == real16F ? 0u : Q.type == real16BF ? 1u : 2u;
     gp.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)plan.ta.mn_major << 15) |
-               ((uint32_t)plan.tb.mn_major << 16) | ((bn >> 3) << 17) | ((kTileM >> 4) << 24);
+               ((uint32_t)plan.tb.mn_major << 16) | ((bn >> 3) << 17) | ((tile_m >> 4) << 24);
     gp.out = Q.out;
     gp.ldo = Q.N == 1 ? (Q.M == 1 ? 1 : Q.o_m) : (Q.M == 1 ? (long long)Q.N : Q.o_m);
     gp.out_batch_stride = Q.o_b;
@@ -408,10 +465,18 @@ cudaError_t run_tc(const Plan& plan, cudaStream_t stream)
 
     const size_t smem = plan.pub.dynamicSmemBytes;
     const uint32_t ctas = (uint32_t)plan.pub.ctas;
-    switch (Q.type) {
-    case real32F: e = launch_tc_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
-    case real16F: e = launch_tc_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
-    default: e = launch_tc_bn<__nv_bfloat16>(bn, ma, mb, gp, ctas, smem, stream); break;
+    if (pair) {
+        switch (Q.type) {
+        case real32F: e = launch_pair_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
+        case real16F: e = launch_pair_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
+        default: e = launch_pair_bn<__nv_bfloat16>(bn, ma, mb, gp, ctas, smem, stream); break;
+        }
+    } else {
+        switch (Q.type) {
+        case real32F: e = launch_tc_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
+        case real16F: e = launch_tc_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
+        default: e = launch_tc_bn<__nv_bfloat16>(bn, ma, mb, gp, ctas, smem, stream); break;
+        }
     }
     if (e == cudaSuccess) g_launches.fetch_add(1);
     return e;

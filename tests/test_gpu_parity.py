@@ -15,7 +15,7 @@ from _gpu_util import BF16, F16, F32, TOL, TORCH_DTYPE, from_dev, random_bits, t
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "matmul_kat.json")
-SIMT, TC = 1, 2
+SIMT, TC, PAIR = 1, 2, 3
 TRANSPOSES = [(False, False), (False, True), (True, False), (True, True)]
 
 
@@ -165,14 +165,30 @@ def test_tensor_core_kernel_within_tolerance(srt, oracle, dtype, ta, tb, M, N, K
 
 
 @pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("ta,tb", TRANSPOSES)
+@pytest.mark.parametrize("M,N,K,batch,tile_n", [
+    (256, 256, 64, 0, 0), (1000, 520, 200, 0, 0), (8, 8, 8, 0, 0), (264, 136, 72, 0, 128),
+    (512, 384, 1024, 0, 128), (512, 512, 64, 5, 0), (2048, 1024, 4096, 0, 0), (4096, 4096, 512, 0, 0)])
+def test_cta_pair_kernel_within_tolerance(srt, oracle, dtype, ta, tb, M, N, K, batch, tile_n):
+    srt.set_tuning(PAIR, tile_n, 0, 0)
+    rng = np.random.default_rng(M + 3 * N + 7 * K + dtype + 2 * ta + tb + 1)
+    ash, bsh = _shapes(M, N, K, ta, tb, batch)
+    a, b = random_bits(oracle, rng, ash, dtype), random_bits(oracle, rng, bsh, dtype)
+    got, ref = _run(srt, oracle, dtype, a, b, ta, tb, expect_kernel=PAIR)
+    err = oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype))
+    assert err <= TOL[dtype] and err <= 2e-3
+
+
+@pytest.mark.parametrize("kernel", [TC, PAIR])
+@pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("act,with_bias", [("relu", True), ("identity", True), ("relu", False), ("gelu", True)])
-def test_tensor_core_fused_epilogue(srt, oracle, dtype, act, with_bias):
-    srt.set_tuning(TC, 0, 0, 0)
+def test_tensor_core_fused_epilogue(srt, oracle, dtype, act, with_bias, kernel):
+    srt.set_tuning(kernel, 0, 0, 0)
     rng = np.random.default_rng(21 + dtype)
     a = random_bits(oracle, rng, (300, 256), dtype, scale=0.05)
     w = random_bits(oracle, rng, (256, 520), dtype, scale=0.05)
     bias = random_bits(oracle, rng, (520,), dtype, scale=0.05) if with_bias else None
-    got, ref = _run(srt, oracle, dtype, a, w, False, False, bias=bias, act=act, expect_kernel=TC)
+    got, ref = _run(srt, oracle, dtype, a, w, False, False, bias=bias, act=act, expect_kernel=kernel)
     assert oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype)) <= 2e-3
 
 
@@ -203,7 +219,7 @@ def test_col_order_output_runs_transposed_problem_with_row_bias(srt, oracle, dty
     c = srt.matmul(a_col, to_dev(b, dtype), bias=to_dev(bias, dtype), activation=srt.ActivationType.relu)
     assert srt.order_of(c) == srt.Order.col and c.stride() == (1, 264)
     plan = srt.query_plan(a_col, to_dev(b, dtype), c)
-    assert plan["kernel"] == TC and plan["swapped"] == 1
+    assert plan["kernel"] in (TC, PAIR) and plan["swapped"] == 1
     got = from_dev(c, dtype)
     assert oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype)) <= 2e-3
 
@@ -251,7 +267,7 @@ def test_config2_dense_bf16_bias_relu(srt, oracle):
     layer = srt.Dense(to_dev(w, BF16), to_dev(bias, BF16), srt.ActivationType.relu)
     dx = to_dev(x, BF16)
     y = layer(dx)
-    assert srt.query_plan(dx, layer.weight, y)["kernel"] == TC
+    assert srt.query_plan(dx, layer.weight, y)["kernel"] in (TC, PAIR)
     ref = oracle.matmul(x, w, BF16, bias=bias, activation="relu")
     got = from_dev(y, BF16)
     err = oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16))
@@ -262,7 +278,7 @@ def test_config3_batched_fp16_attention_score_shape(srt, oracle):
     rng = np.random.default_rng(0)
     a = random_bits(oracle, rng, (64, 512, 64), F16, dist="normal")
     b = random_bits(oracle, rng, (64, 512, 64), F16, dist="normal")
-    got, ref = _run(srt, oracle, F16, a, b, False, True, expect_kernel=TC)
+    got, ref = _run(srt, oracle, F16, a, b, False, True)
     err = oracle.rel_frobenius(oracle.decode(got, F16), oracle.decode(ref, F16))
     assert err <= TOL[F16] and err <= 2e-3
 
