@@ -140,9 +140,10 @@ cudaError_t srtMatmulBiasActivation(
  */
 typedef enum {
     srtMatmulKernelNone    = 0,
-    srtMatmulKernelSimt    = 1,   /* strided SIMT kernel, fp32 FMA */
+    srtMatmulKernelSimt    = 1,   /* strided SIMT kernel, fp32 multiply and add in the reference's order */
     srtMatmulKernelTcgen05 = 2,   /* TMA + tcgen05 tensor-core kernel, one CTA per tile */
-    srtMatmulKernelTcgen05Pair = 3 /* TMA + tcgen05 cta_group::2 kernel, CTA pair per tile */
+    srtMatmulKernelTcgen05Pair = 3, /* TMA + tcgen05 cta_group::2 kernel, CTA pair per tile */
+    srtMatmulKernelTcgen05Split = 4 /* Float32 as 3 x TF32 on the tensor cores (hi/lo split in shared memory) */
 } srtMatmulKernel;
 
 typedef struct {
@@ -167,7 +168,8 @@ cudaError_t srtMatmulQueryPlan(
     srtMatmulPlan* plan);
 
 /* Process-wide overrides, 0 = automatic.  forceKernel: an srtMatmulKernel value (a forced
- * tensor-core kernel still falls back to SIMT for views that TMA cannot address);
+ * tensor-core kernel still falls back to SIMT for views that TMA cannot address; Float32
+ * always takes the 3 x TF32 kernel when a tensor-core kernel is forced);
  * tileN: 64, 128 or 256; stages: 2..8; maxCtas: cap on the persistent grid. */
 cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas);
 

@@ -152,6 +152,50 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, OutT* row_p
     }
 }
 
+// Drains one finished 128-row accumulator (this warp's 32 TMEM lanes, BN columns starting at
+// TMEM address `acc`) to global memory: bias, activation, one rounding, stores.
+// With DUAL the tile's value is the sum of two accumulators (`acc` and `acc2`), added in fp32.
+template <typename T, uint32_t BN, bool DUAL = false>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t acc, uint32_t quarter, uint32_t lane,
+                                                  uint32_t batch, uint32_t m0, uint32_t n0, uint32_t acc2 = 0)
+{
+    T* const out = static_cast<T*>(p.out);
+    const T* const bias = static_cast<const T*>(p.bias);
+    const uint32_t row = m0 + quarter * 32 + lane;
+    T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
+    float row_bias = 0.0f;
+    if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
+    for (uint32_t c = 0; c < BN / 32; ++c) {
+        const uint32_t col0 = n0 + c * 32;
+        if (col0 >= p.N) break;                       // uniform over the warp
+        uint32_t raw[32];
+        tmem_ld_32x32(acc + ((quarter * 32u) << 16) + c * 32, raw);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        if constexpr (DUAL) {
+            tmem_ld_32x32(acc2 + ((quarter * 32u) << 16) + c * 32, raw);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(raw[j]);
+        }
+        if (p.bias_mode == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += to_float<T>(__ldg(bias + static_cast<long long>(col0 + j) * p.bias_stride));
+        } else if (p.bias_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += row_bias;
+        }
+        if (p.act != kActIdentity) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_activation(p.act, v[j]);
+        }
+        if (row < p.M) store_row_chunk<T>(p, row_ptr, col0, v);
+    }
+}
+
 // InT / OutT: element type of the inputs and of the output (float, __half, __nv_bfloat16).
 // BN: tile width (64, 128 or 256).  fp32 inputs are multiplied as TF32.
 template <typename T, uint32_t BN>
@@ -280,8 +324,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t quarter = warp & 3;       // TMEM lanes this warp may read
         uint32_t local = 0;
         bool ok = true;
-        T* const out = static_cast<T*>(p.out);
-        const T* const bias = static_cast<const T*>(p.bias);
         for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
             uint32_t batch, m0, n0;
             decode_tile(p, tile, BN, batch, m0, n0);
@@ -289,33 +331,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t row = m0 + quarter * 32 + lane;
-            T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
-            float row_bias = 0.0f;
-            if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
-            for (uint32_t c = 0; c < BN / 32; ++c) {
-                const uint32_t col0 = n0 + c * 32;
-                if (col0 >= p.N) break;                       // uniform over the warp
-                uint32_t raw[32];
-                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32, raw);
-                tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                if (p.bias_mode == 1) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) v[j] += to_float<T>(__ldg(bias + static_cast<long long>(col0 + j) * p.bias_stride));
-                } else if (p.bias_mode == 2) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += row_bias;
-                }
-                if (p.act != kActIdentity) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = apply_activation(p.act, v[j]);
-                }
-                if (row < p.M) store_row_chunk<T>(p, row_ptr, col0, v);
-            }
+            drain_accumulator<T, BN>(p, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
@@ -486,8 +502,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t quarter = warp & 3;
         uint32_t local = 0;
         bool ok = true;
-        T* const out = static_cast<T*>(p.out);
-        const T* const bias = static_cast<const T*>(p.bias);
         for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
             uint32_t batch, m0, n0;
             decode_tile(p, tile, BN, batch, m0, n0);
@@ -496,33 +510,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t row = m0 + quarter * 32 + lane;
-            T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
-            float row_bias = 0.0f;
-            if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
-            for (uint32_t c = 0; c < BN / 32; ++c) {
-                const uint32_t col0 = n0 + c * 32;
-                if (col0 >= p.N) break;
-                uint32_t raw[32];
-                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32, raw);
-                tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-                if (p.bias_mode == 1) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) v[j] += to_float<T>(__ldg(bias + static_cast<long long>(col0 + j) * p.bias_stride));
-                } else if (p.bias_mode == 2) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += row_bias;
-                }
-                if (p.act != kActIdentity) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = apply_activation(p.act, v[j]);
-                }
-                if (row < p.M) store_row_chunk<T>(p, row_ptr, col0, v);
-            }
+            drain_accumulator<T, BN>(p, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
@@ -546,6 +534,228 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     cluster_arrive_release();
     cluster_wait_acquire();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Float32 on the tensor cores: 3 x TF32.  A TF32 MMA reads fp32 words and uses the sign, the
+// exponent and the top 10 mantissa bits.  Each operand x is split as x = hi + lo with
+// hi = x with the low 13 mantissa bits cleared (exactly a TF32 value) and lo = x - hi (exact
+// in fp32, at most 13 significant bits), and the product is accumulated as
+//     hi_a.hi_b + hi_a.lo_b + lo_a.hi_b          (lo_a.lo_b ~ 2^-22 |a.b| is dropped)
+// in two fp32 TMEM accumulators (dominant products / correction terms) that the epilogue sums.
+// TMA delivers the raw fp32 tile; four transform warps rewrite
+// it in place as hi and write lo to a second buffer with the same (swizzled) layout, so the
+// same shared-memory descriptors address both.
+//   warp 0 producer, warp 1 MMA issuer, warps 2-5 epilogue, warps 6-9 transform.
+//   full[s]  TMA bytes landed -> transform warps;  ready[s] (count 4) transform done -> MMA;
+//   empty[s] MMAs done -> producer.
+constexpr uint32_t kSplitThreads = 320;
+
+template <uint32_t BN>
+__global__ void __launch_bounds__(kSplitThreads, 1)
+gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                          const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ GemmParams p)
+{
+    using T = float;
+    constexpr uint32_t kBTileBytes = BN * kRowBytes;
+    constexpr uint32_t kHalfBytes = kATileBytes + kBTileBytes;     // hi tiles; lo tiles follow
+    constexpr uint32_t kStageBytes = 2 * kHalfBytes;
+    // two accumulators per tile (dominant products / correction terms); tiles are double-buffered
+    // while 4 x BN columns fit in TMEM
+    constexpr uint32_t kAccBufs = BN == 256 ? 1 : 2;
+    constexpr uint32_t kTmemCols = kAccBufs * 2 * BN;
+    constexpr uint32_t kMaxStages = 4;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t ready_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t tmem_full_bar[2];
+    __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t stages = p.stages;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&ready_bar[s]), 4);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&tmem_full_bar[i]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[i]), 4);
+        }
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_cta1(smem_u32(&tmem_holder), kTmemCols);
+        tmem_relinquish_cta1();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                uint32_t batch, m0, n0;
+                decode_tile(p, tile, BN, batch, m0, n0);
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_bar[stage]);
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+                    const int32_t k0 = static_cast<int32_t>(kb * p.kb_elems);
+                    mbar_arrive_expect_tx(bar, p.stage_tx_bytes);
+                    if (!p.a.mn_major) {
+                        tma_load_3d(sa, &tmap_a, bar, k0, m0, batch * p.a.batch_mul);
+                    } else {
+                        for (uint32_t c = 0; c < p.a.chunks; ++c)
+                            tma_load_3d(sa + c * p.a.chunk_bytes, &tmap_a, bar, m0 + c * p.a.chunk_elems, k0,
+                                        batch * p.a.batch_mul);
+                    }
+                    if (!p.b.mn_major) {
+                        tma_load_3d(sb, &tmap_b, bar, k0, n0, batch * p.b.batch_mul);
+                    } else {
+                        for (uint32_t c = 0; c < p.b.chunks; ++c)
+                            tma_load_3d(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0,
+                                        batch * p.b.batch_mul);
+                    }
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                abort_flag = 1;
+                atomicOr(&g_gemm_status, kStatusProducerTimeout);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+                const uint32_t buf = local % kAccBufs;
+                const uint32_t acc_phase = (local / kAccBufs) & 1;
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_main = tmem_base + buf * 2 * BN;
+                const uint32_t d_small = d_main + BN;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&ready_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_base + stage * kStageBytes;
+                    const uint32_t sb = sa + kATileBytes;
+                    const uint32_t a_hi = ((sa >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t b_hi = ((sb >> 4) & 0x3fffu) | p.b.desc_lo_fixed;
+                    const uint32_t a_lo = (((sa + kHalfBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t b_lo = (((sb + kHalfBytes) >> 4) & 0x3fffu) | p.b.desc_lo_fixed;
+                    const uint64_t ahi64 = static_cast<uint64_t>(p.a.desc_hi) << 32;
+                    const uint64_t bhi64 = static_cast<uint64_t>(p.b.desc_hi) << 32;
+#pragma unroll
+                    for (uint32_t k = 0; k < kKStepsPerStage; ++k) {
+                        const uint32_t da = k * p.a.kstep, db = k * p.b.kstep;
+                        // The accumulator add truncates toward zero, a bias that grows with the number
+                        // of adds and with the accumulator's magnitude: the correction terms get their
+                        // own (2^-11 times smaller) accumulator and are added once, in the epilogue.
+                        umma_tf32_cta1(d_main, ahi64 | (a_hi + da), bhi64 | (b_hi + db), p.idesc, (kb | k) != 0);
+                        umma_tf32_cta1(d_small, ahi64 | (a_lo + da), bhi64 | (b_hi + db), p.idesc, (kb | k) != 0);
+                        umma_tf32_cta1(d_small, ahi64 | (a_hi + da), bhi64 | (b_lo + db), p.idesc, 1);
+                    }
+                    umma_commit_cta1(smem_u32(&empty_bar[stage]));
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit_cta1(smem_u32(&tmem_full_bar[buf]));
+            }
+            if (!ok) {
+                abort_flag = 1;
+                atomicOr(&g_gemm_status, kStatusMmaTimeout);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t quarter = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+            uint32_t batch, m0, n0;
+            decode_tile(p, tile, BN, batch, m0, n0);
+            const uint32_t buf = local % kAccBufs;
+            const uint32_t acc_phase = (local / kAccBufs) & 1;
+            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            drain_accumulator<T, BN, true>(p, tmem_base + buf * 2 * BN, quarter, lane, batch, m0, n0,
+                                           tmem_base + buf * 2 * BN + BN);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+        }
+        if (!ok) {
+            abort_flag = 1;
+            if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);
+        }
+    } else {
+        // ------------------------------------------------------------------ hi / lo transform
+        const uint32_t t = threadIdx.x - 6 * 32;              // 0 .. 127
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                const uint32_t hi_base = smem_base + stage * kStageBytes;
+#pragma unroll 4
+                for (uint32_t off = t * 16; off < kHalfBytes; off += 128 * 16) {
+                    uint32_t x0, x1, x2, x3;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(hi_base + off));
+                    uint32_t h[4] = {x0 & 0xffffe000u, x1 & 0xffffe000u, x2 & 0xffffe000u, x3 & 0xffffe000u};
+                    uint32_t x[4] = {x0, x1, x2, x3};
+                    uint32_t l[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float lo = __uint_as_float(x[j]) - __uint_as_float(h[j]);
+                        // infinities and NaNs stay in hi alone
+                        l[j] = ((x[j] & 0x7f800000u) == 0x7f800000u) ? 0u : __float_as_uint(lo);
+                    }
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(hi_base + off), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(hi_base + kHalfBytes + off), "r"(l[0]), "r"(l[1]), "r"(l[2]), "r"(l[3]) : "memory");
+                }
+                fence_proxy_async_smem();          // make the generic-proxy writes visible to the MMA
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ready_bar[stage]));
+                if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (!ok) {
+            abort_flag = 1;
+            if (lane == 0) atomicOr(&g_gemm_status, kStatusPairTimeout);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        if (abort_flag != 0) __nanosleep(1000000);
+        tmem_dealloc_cta1(tmem_base, kTmemCols);
+    }
 }
 
 }  // namespace srt

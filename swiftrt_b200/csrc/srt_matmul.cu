@@ -255,8 +255,13 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         if (!plan.ta.ok || !plan.tb.ok) tc = false;
         if (Q.N > 1 && Q.o_m < (long long)Q.N && Q.M > 1) tc = false;   // overlapping output rows
     }
-    // fp32 on the tensor cores is TF32 (10-bit mantissa): only on explicit request
-    if (tc && Q.type == real32F && force != srtMatmulKernelTcgen05 && force != srtMatmulKernelTcgen05Pair) tc = false;
+    // Float32 runs on the tensor cores as 3 x TF32 once the problem is large enough to pay for
+    // it; below that the strided kernel is as fast and keeps the reference's exact arithmetic
+    // The tensor cores add into the fp32 accumulator with truncation, an error that grows
+    // linearly with K (measured 9e-7 at K = 256, 2.6e-6 at K = 1024, relative Frobenius):
+    // beyond K = 2048 Float32 stays on the exact kernel to keep the 1e-5 tolerance.
+    const bool split = tc && Q.type == real32F;
+    if (split && force == 0 && (Q.M * Q.N * Q.K * Q.batch < (1ull << 26) || Q.K > 2048)) tc = false;
     // tiny problems are launch-bound either way; keep them on the exact kernel
     if (tc && force == 0 && Q.M * Q.N * Q.K * Q.batch < (1ull << 18)) tc = false;
 
@@ -278,7 +283,8 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     uint32_t bn = (uint32_t)g_tuning.tile_n.load();
     // CTA pairs (256 x BN tiles) when the problem has enough 256-row tiles to fill the device
     bool pair = false;
-    if (force == srtMatmulKernelTcgen05Pair) pair = true;
+    if (split) pair = false;
+    else if (force == srtMatmulKernelTcgen05Pair) pair = true;
     else if (force == 0) pair = Q.M >= 256 && ((Q.M + 255) / 256) * ((Q.N + 255) / 256) * Q.batch >= (uint64_t)dev.sms;
     const uint32_t tile_m = pair ? 2 * kTileM : kTileM;
     if (pair) {
@@ -289,9 +295,12 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         bn = 256;
         while (bn > 64 && (Q.N <= bn / 2 || tm * ((Q.N + bn - 1) / bn) * Q.batch < (uint64_t)dev.sms)) bn /= 2;
     }
-    const uint32_t stage_bytes = kATileBytes + (pair ? bn / 2 : bn) * kRowBytes;
+    static const bool tf32_single = getenv("SRT_MATMUL_TF32_SINGLE") != nullptr;   // experiment knob: 1 x TF32
+    const bool split3 = split && !tf32_single;
+    const uint32_t stage_bytes = (kATileBytes + (pair ? bn / 2 : bn) * kRowBytes) * (split3 ? 2 : 1);
     uint32_t stages = (uint32_t)g_tuning.stages.load();
-    const uint32_t max_stages = (227u * 1024u - 2048u) / stage_bytes;
+    uint32_t max_stages = (227u * 1024u - 2048u) / stage_bytes;
+    if (split3 && max_stages > 4) max_stages = 4;
     // Four 32 KB stages keep the pair kernel's MMAs fed; deeper rings measured slower on a
     // power-capped B200 (higher pipe utilisation, lower clock, lower L2 hit rate).
     if (stages < 2 || stages > 8) stages = pair ? 4 : 8;
@@ -305,14 +314,14 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     if (cap > 0 && ctas > (uint32_t)cap) ctas = (uint32_t)cap;
     if (pair) ctas *= 2;
 
-    plan.pub.kernel = pair ? srtMatmulKernelTcgen05Pair : srtMatmulKernelTcgen05;
+    plan.pub.kernel = split3 ? srtMatmulKernelTcgen05Split : pair ? srtMatmulKernelTcgen05Pair : srtMatmulKernelTcgen05;
     plan.pub.tileM = (int32_t)tile_m; plan.pub.tileN = (int32_t)bn; plan.pub.tileK = (int32_t)kb_elems;
     plan.pub.stages = (int32_t)stages;
     plan.pub.ctas = (int32_t)ctas;
     plan.pub.tiles = (int32_t)tiles;
     plan.pub.swapped = plan.swapped;
     plan.pub.aMajor = plan.ta.mn_major; plan.pub.bMajor = plan.tb.mn_major;
-    plan.pub.fp32Split = 0;
+    plan.pub.fp32Split = split3;
     plan.pub.workspaceBytes = 0;
     plan.pub.dynamicSmemBytes = (size_t)stages * stage_bytes + 1024;
 }
@@ -349,12 +358,19 @@ cudaError_t encode_operand(CUtensorMap* map, const Problem& Q, const char* ptr, 
     op.batch_mul = bcast ? 0 : 1;
     // stride offset 1024 bytes, descriptor version 1 (bit 46), 128-byte swizzle (bits 61-63 = 2)
     op.desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B;
+    if (t.mn_major && elem == 4) {
+        // M/N-contiguous 32-bit operands exist in one shared-memory layout only: 128-byte rows
+        // swizzled in 32-byte units (layout type 1), whose pattern repeats every 4 rows (512 bytes)
+        op.desc_hi = (512u >> 4) | (1u << 14) | (1u << 29);
+        swizzle = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    }
     gdim[2] = bcast ? 1 : Q.batch;
     gstride[0] = (cuuint64_t)t.ld * elem;
     gstride[1] = bcast ? gstride[0] * gdim[1] : (cuuint64_t)s_b * elem;
     box[2] = 1;
     CUresult r = g_encode(map, dt, 3, const_cast<char*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return cudaSuccess;
@@ -380,6 +396,17 @@ cudaError_t launch_tc_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& 
     case 128: return launch_tc<T, 128>(ma, mb, gp, ctas, smem, stream);
     default: return launch_tc<T, 256>(ma, mb, gp, ctas, smem, stream);
     }
+}
+
+template <uint32_t BN>
+cudaError_t launch_split(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas, size_t smem,
+                         cudaStream_t stream)
+{
+    auto kernel = gemm_tcgen05_split_kernel<BN>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<ctas, kSplitThreads, smem, stream>>>(ma, mb, gp);
+    return cudaGetLastError();
 }
 
 template <typename T, uint32_t BN>
@@ -465,7 +492,11 @@ cudaError_t run_tc(const Plan& plan, cudaStream_t stream)
 
     const size_t smem = plan.pub.dynamicSmemBytes;
     const uint32_t ctas = (uint32_t)plan.pub.ctas;
-    if (pair) {
+    if (plan.pub.kernel == srtMatmulKernelTcgen05Split) {
+        e = bn == 64    ? launch_split<64>(ma, mb, gp, ctas, smem, stream)
+            : bn == 128 ? launch_split<128>(ma, mb, gp, ctas, smem, stream)
+                        : launch_split<256>(ma, mb, gp, ctas, smem, stream);
+    } else if (pair) {
         switch (Q.type) {
         case real32F: e = launch_pair_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
         case real16F: e = launch_pair_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
@@ -567,7 +598,7 @@ cudaError_t srtMatmulQueryPlan(const void* a, const srtTensorDescriptor* aDesc, 
 
 cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas)
 {
-    if (forceKernel < 0 || forceKernel > srtMatmulKernelTcgen05Pair) return fail(cudaErrorInvalidValue, "unknown kernel id");
+    if (forceKernel < 0 || forceKernel > srtMatmulKernelTcgen05Split) return fail(cudaErrorInvalidValue, "unknown kernel id");
     if (tileN != 0 && tileN != 64 && tileN != 128 && tileN != 256) return fail(cudaErrorInvalidValue, "tileN must be 0, 64, 128 or 256");
     if (stages != 0 && (stages < 2 || stages > 8)) return fail(cudaErrorInvalidValue, "stages must be 0 or 2..8");
     if (maxCtas < 0) return fail(cudaErrorInvalidValue, "maxCtas must be >= 0");

@@ -15,7 +15,7 @@ from _gpu_util import BF16, F16, F32, TOL, TORCH_DTYPE, from_dev, random_bits, t
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "matmul_kat.json")
-SIMT, TC, PAIR = 1, 2, 3
+SIMT, TC, PAIR, SPLIT = 1, 2, 3, 4
 TRANSPOSES = [(False, False), (False, True), (True, False), (True, True)]
 
 
@@ -179,6 +179,50 @@ def test_cta_pair_kernel_within_tolerance(srt, oracle, dtype, ta, tb, M, N, K, b
     assert err <= TOL[dtype] and err <= 2e-3
 
 
+@pytest.mark.parametrize("ta,tb", TRANSPOSES)
+@pytest.mark.parametrize("M,N,K,batch,tile_n", [
+    (128, 256, 32, 0, 0), (1000, 520, 200, 0, 0), (4, 4, 4, 0, 256), (136, 264, 72, 0, 128),
+    (512, 384, 1024, 0, 64), (256, 512, 64, 5, 0), (2048, 512, 2048, 0, 0)])
+def test_float32_3xtf32_kernel_within_tolerance(srt, oracle, ta, tb, M, N, K, batch, tile_n):
+    """Float32 on the tensor cores (hi/lo split, three TF32 products) must stay within 1e-5."""
+    srt.set_tuning(SPLIT, tile_n, 0, 0)
+    rng = np.random.default_rng(M + 3 * N + 7 * K + 2 * ta + tb + 5)
+    ash, bsh = _shapes(M, N, K, ta, tb, batch)
+    a, b = random_bits(oracle, rng, ash, F32), random_bits(oracle, rng, bsh, F32)
+    got, ref = _run(srt, oracle, F32, a, b, ta, tb, expect_kernel=SPLIT)
+    assert oracle.rel_frobenius(got, ref) <= TOL[F32]
+
+
+def test_float32_3xtf32_epilogue_and_special_values(srt, oracle):
+    srt.set_tuning(SPLIT, 0, 0, 0)
+    rng = np.random.default_rng(41)
+    a, b = random_bits(oracle, rng, (300, 256), F32), random_bits(oracle, rng, (256, 520), F32)
+    bias = random_bits(oracle, rng, (520,), F32)
+    got, ref = _run(srt, oracle, F32, a, b, False, False, bias=bias, act="relu", expect_kernel=SPLIT)
+    assert oracle.rel_frobenius(got, ref) <= TOL[F32]
+    # values spanning many binades and a NaN: the NaN must poison exactly its row, like in the reference
+    # (an infinity times an operand whose low part is zero gives NaN instead of infinity on this
+    # kernel: the split evaluates inf . 0 for the missing low part)
+    a2 = a.copy()
+    a2[:, 0] *= 2.0 ** 60
+    a2[:, 1] *= 2.0 ** -60
+    a2[9, 5] = np.nan
+    got, ref = _run(srt, oracle, F32, a2, b, False, False, expect_kernel=SPLIT)
+    fin = np.isfinite(ref)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert oracle.rel_frobenius(got[fin], ref[fin]) <= TOL[F32]
+
+
+def test_float32_kernel_choice_follows_size_and_k(srt):
+    dev = "cuda:0"
+    small = torch.zeros((256, 256), device=dev)
+    assert srt.query_plan(small, small, small)["kernel"] == SIMT
+    a, b = torch.zeros((8192, 1024), device=dev), torch.zeros((1024, 256), device=dev)
+    assert srt.query_plan(a, b, torch.zeros((8192, 256), device=dev))["kernel"] == SPLIT
+    a, b = torch.zeros((1024, 4096), device=dev), torch.zeros((4096, 256), device=dev)
+    assert srt.query_plan(a, b, torch.zeros((1024, 256), device=dev))["kernel"] == SIMT    # K > 2048
+
+
 @pytest.mark.parametrize("kernel", [TC, PAIR])
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("act,with_bias", [("relu", True), ("identity", True), ("relu", False), ("gelu", True)])
@@ -288,6 +332,7 @@ def test_config4_tall_skinny_float32(srt, oracle):
     a, b = random_bits(oracle, rng, (65536, 1024), F32), random_bits(oracle, rng, (1024, 256), F32)
     da, db = to_dev(a, F32), to_dev(b, F32)
     c = srt.matmul(da, db)
+    assert srt.query_plan(da, db, c)["kernel"] == SPLIT
     got = from_dev(c, F32)
     rows = _sample_rows(65536, 2048)
     ref = oracle.matmul(np.ascontiguousarray(a[rows]), b, F32)
