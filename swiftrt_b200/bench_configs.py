@@ -1,0 +1,136 @@
+"""Times the five named configurations of the matmul path on one GPU and prints one JSON record
+per configuration (shape, kernel, ms, algorithmic TFLOP/s and GB/s, roofline fractions).
+
+    python -m swiftrt_b200.bench_configs [--iters 20] [--only c3]
+
+Inputs are seeded synthetic draws with the shapes and value distributions of the configurations;
+between timed launches a buffer larger than the L2 cache is read (not written: dirty lines would
+make the timed kernel pay for their write-back), so every launch starts with a cold, clean L2.
+Timing: CUDA events around each launch on the launching stream (the launch is a prepared
+MatmulOp, enqueued while the flush still runs, so host latency is not in the interval), median
+and best of `iters` after 3 warm-ups.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+import swiftrt_b200 as srt
+
+NOMINAL = {"bf16_tflops": 2250.0, "hbm_gbs": 8000.0}
+KERNEL_NAMES = {1: "gemm_simt_kernel", 2: "gemm_tcgen05_kernel", 3: "gemm_tcgen05_pair_kernel",
+                4: "gemm_tcgen05_split_kernel"}
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
+
+
+def _uniform(shape, dtype, dev, g, lo, hi):
+    return (torch.rand(shape, device=dev, generator=g) * (hi - lo) + lo).to(dtype)
+
+
+def configs(dev):
+    g = torch.Generator(device=dev).manual_seed(0)
+    f32, f16, bf16 = torch.float32, torch.float16, torch.bfloat16
+
+    def c1():
+        return dict(name="c1", desc="Float32 256^3 NN", a=_uniform((256, 256), f32, dev, g, -1, 1),
+                    b=_uniform((256, 256), f32, dev, g, -1, 1), bound="hbm")
+
+    def c2():
+        return dict(name="c2", desc="Dense bf16 [1024x4096].[4096x4096] + bias, ReLU",
+                    a=_uniform((1024, 4096), bf16, dev, g, -0.05, 0.05), b=_uniform((4096, 4096), bf16, dev, g, -0.05, 0.05),
+                    bias=_uniform((4096,), bf16, dev, g, -0.05, 0.05), act=srt.ActivationType.relu, bound="tensor")
+
+    def c3():
+        return dict(name="c3", desc="batched fp16 64 x [512x64].[512x64]^T",
+                    a=torch.randn((64, 512, 64), device=dev, generator=g).to(f16),
+                    b=torch.randn((64, 512, 64), device=dev, generator=g).to(f16), tb=True, bound="hbm")
+
+    def c4():
+        return dict(name="c4", desc="Float32 [65536x1024].[1024x256] NN", a=_uniform((65536, 1024), f32, dev, g, -1, 1),
+                    b=_uniform((1024, 256), f32, dev, g, -1, 1), bound="hbm")
+
+    def c5():
+        return dict(name="c5", desc="bf16 16384^3 NN", a=_uniform((16384, 16384), bf16, dev, g, -1, 1),
+                    b=_uniform((16384, 16384), bf16, dev, g, -1, 1), bound="tensor")
+
+    return [c1, c2, c3, c4, c5]
+
+
+def run(cfg: dict, iters: int, flush: torch.Tensor, peaks: dict) -> dict:
+    sink = torch.zeros((), dtype=torch.float32, device=flush.device)
+    a, b = cfg["a"], cfg["b"]
+    tb = cfg.get("tb", False)
+    bias, act = cfg.get("bias"), cfg.get("act")
+    out = srt.matmul(a, b, False, tb, bias=bias, activation=act)
+    plan = srt.query_plan(a, b, out, False, tb)
+    op = srt.MatmulOp(out, a, False, b, tb, bias, act)
+    for _ in range(3):
+        op()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        sink.copy_(flush.sum())                         # evicts L2 with clean lines: 256 MiB read
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        op()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    if srt.check_status() != 0:
+        raise RuntimeError("tensor-core kernel reported a pipeline timeout")
+    times.sort()
+    med, best = times[len(times) // 2], times[0]
+    batch = a.shape[0] if a.dim() == 3 else 1
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-2] if tb else b.shape[-1]
+    flops = 2.0 * batch * M * N * K
+    nbytes = (a.numel() + b.numel() + out.numel()) * a.element_size() + (bias.numel() * bias.element_size() if bias is not None else 0)
+    tf, gbs = flops / med / 1e9, nbytes / med / 1e6
+    rec = {"config": cfg["name"], "what": cfg["desc"], "kernel": KERNEL_NAMES[plan["kernel"]],
+           "tile": [plan["tileM"], plan["tileN"], plan["tileK"]], "stages": plan["stages"], "ctas": plan["ctas"],
+           "ms_median": med, "ms_best": best, "algorithmic_flops": flops, "algorithmic_bytes": nbytes,
+           "tflops": tf, "gbs": gbs, "bound": cfg["bound"]}
+    if cfg["bound"] == "tensor":
+        rec["frac_of_nominal"] = tf / NOMINAL["bf16_tflops"]
+        if "bf16_tflops" in peaks:
+            rec["frac_of_measured"] = tf / peaks["bf16_tflops"]
+    else:
+        rec["frac_of_nominal"] = gbs / NOMINAL["hbm_gbs"]
+        if "hbm_gbs" in peaks:
+            rec["frac_of_measured"] = gbs / peaks["hbm_gbs"]
+    return rec
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default="")
+    ap.add_argument("--tune", default="", help="forceKernel,tileN,stages,maxCtas")
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    if args.tune:
+        srt.set_tuning(*[int(x) for x in args.tune.split(",")])
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
+    peaks = measured_peaks()
+    for make in configs(dev):
+        if args.only and make.__name__ not in args.only.split(","):
+            continue
+        cfg = make()
+        print(json.dumps(run(cfg, args.iters, flush, peaks)), flush=True)
+        del cfg
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

@@ -6,8 +6,9 @@
 //               instruction) from the shared-memory descriptors into a TMEM accumulator;
 //               tcgen05.commit hands each stage back to the producer and each finished
 //               accumulator to the epilogue.  Also owns the TMEM allocation.
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (each warp its 32 TMEM lanes),
-//               add bias, apply the activation, round once to the output type, store.
+//   warps 2-9   epilogue: tcgen05.ld the fp32 accumulator (warp w reads TMEM lanes 32 (w mod 4) ..,
+//               two warps per lane quarter taking alternate 128-byte column segments), add bias,
+//               apply the activation, round once to the output type, store.
 //
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i
 // overlaps the main loop of tile i + 1.  Operands may be K-major (K contiguous) or
@@ -26,7 +27,7 @@ constexpr uint32_t kTileM = 128;        // rows of one MMA (all 128 TMEM lanes)
 constexpr uint32_t kRowBytes = 128;     // swizzle span = bytes of one shared-memory tile row
 constexpr uint32_t kATileBytes = kTileM * kRowBytes;
 constexpr uint32_t kKStepsPerStage = 4; // MMAs per stage: each consumes 32 bytes of K
-constexpr uint32_t kGemmThreads = 192;
+constexpr uint32_t kGemmThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
 
 enum : uint32_t {
     kStatusProducerTimeout = 1u,
@@ -37,6 +38,14 @@ enum : uint32_t {
 
 // Status word of the tensor-core kernels, one per device that loads the module.
 __device__ uint32_t g_gemm_status;
+
+// Development aid: with -DSRT_TRACE the epilogue of CTA 0 records clock64() at a few points.
+#ifdef SRT_TRACE
+__device__ long long g_trace[8192];
+#define SRT_TRACE_POINT(cond, idx) do { if ((cond) && blockIdx.x == 0 && (idx) < 8192) g_trace[(idx)] = clock64(); } while (0)
+#else
+#define SRT_TRACE_POINT(cond, idx) do { } while (0)
+#endif
 
 struct OperandParams {
     uint32_t mn_major;      // 0: K contiguous, 1: M/N contiguous
@@ -66,6 +75,7 @@ struct GemmParams {
     uint32_t bias_mode;          // 0 none, 1 one value per column, 2 one value per row
     uint32_t act;
     uint32_t out_vec_ok;         // 16-byte vector stores are aligned for every full chunk
+    uint32_t out_tma;            // the output view is TMA-addressable: bulk tensor stores from shared memory
 };
 
 enum : uint32_t { kActSigmoid = 0, kActRelu = 1, kActTanh = 2, kActIdentity = 5, kActGelu = 6, kActGeluTanh = 7 };
@@ -152,48 +162,134 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, OutT* row_p
     }
 }
 
+// Applies the activation to a chunk of 32 values; the selector is uniform, so the switch is
+// taken once per chunk and each case is a straight loop.
+__device__ __forceinline__ void activate_chunk(uint32_t act, float (&v)[32])
+{
+    switch (act) {
+    case kActIdentity: break;
+    case kActRelu:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = v[j] >= 0.0f ? v[j] : 0.0f;
+        break;
+    case kActSigmoid:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_activation(kActSigmoid, v[j]);
+        break;
+    case kActTanh:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_activation(kActTanh, v[j]);
+        break;
+    case kActGelu:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_activation(kActGelu, v[j]);
+        break;
+    case kActGeluTanh:
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_activation(kActGeluTanh, v[j]);
+        break;
+    default: break;
+    }
+}
+
 // Drains one finished 128-row accumulator (this warp's 32 TMEM lanes, BN columns starting at
 // TMEM address `acc`) to global memory: bias, activation, one rounding, stores.
 // With DUAL the tile's value is the sum of two accumulators (`acc` and `acc2`), added in fp32.
-template <typename T, uint32_t BN, bool DUAL = false>
-__device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t acc, uint32_t quarter, uint32_t lane,
+//
+// Two store paths.  When the output view is TMA-addressable (p.out_tma) each warp stages 128-byte
+// wide row segments of its 32 rows in shared memory (128-byte swizzle, one 4 KB buffer per warp)
+// and one lane issues a bulk tensor store per segment: full-line writes, clipped at the tensor's
+// edges by the hardware.  Otherwise every thread stores its own row with 16-byte or scalar stores.
+constexpr uint32_t kEpilogueStagingBytes = 8 * 4096;         // 8 warps x (32 rows x 128 B)
+
+// PARTS: how many warps share one lane quarter (1 or 2); warp `part` drains every PARTS-th
+// 128-byte column segment.  `staging` is this warp's own 4 KB buffer.
+template <typename T, uint32_t BN, bool DUAL = false, uint32_t PARTS = 1>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tmap_out, uint32_t staging,
+                                                  uint32_t part, uint32_t acc, uint32_t quarter, uint32_t lane,
                                                   uint32_t batch, uint32_t m0, uint32_t n0, uint32_t acc2 = 0)
 {
+    constexpr uint32_t kColsPerBox = 128 / sizeof(T);            // 64 (16-bit) or 32 (fp32)
+    constexpr uint32_t kLoadsPerBox = kColsPerBox / 32;
+    constexpr uint32_t kBoxes = BN / kColsPerBox;
     T* const out = static_cast<T*>(p.out);
     const T* const bias = static_cast<const T*>(p.bias);
     const uint32_t row = m0 + quarter * 32 + lane;
-    T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
+    const uint32_t lane_addr = (quarter * 32u) << 16;
     float row_bias = 0.0f;
     if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
-    for (uint32_t c = 0; c < BN / 32; ++c) {
-        const uint32_t col0 = n0 + c * 32;
-        if (col0 >= p.N) break;                       // uniform over the warp
-        uint32_t raw[32];
-        tmem_ld_32x32(acc + ((quarter * 32u) << 16) + c * 32, raw);
-        tmem_ld_wait();
-        float v[32];
+    T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
+
+    for (uint32_t bx = part; bx < kBoxes; bx += PARTS) {
+        const uint32_t box_col = n0 + bx * kColsPerBox;
+        if (box_col >= p.N) break;                              // uniform over the warp
+        SRT_TRACE_POINT(quarter == 2 && part == 0 && lane == 0, (bx + 0) * 8 + 0);
+        uint32_t packed[32];                                    // 128 bytes of this thread's output row
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-        if constexpr (DUAL) {
-            tmem_ld_32x32(acc2 + ((quarter * 32u) << 16) + c * 32, raw);
-            tmem_ld_wait();
+        for (uint32_t h = 0; h < kLoadsPerBox; ++h) {
+            const uint32_t col0 = box_col + h * 32;
+            uint32_t raw[32];
+            tmem_ld_32x32(acc + lane_addr + (bx * kLoadsPerBox + h) * 32, raw);
+            // one coalesced bias load per 32 columns, handed out by shuffle below
+            float my_bias = 0.0f;
+            if (p.bias_mode == 1 && col0 + lane < p.N)
+                my_bias = to_float<T>(__ldg(bias + static_cast<long long>(col0 + lane) * p.bias_stride));
+            tmem_ld_wait_regs(raw);
+            float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(raw[j]);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+            if constexpr (DUAL) {
+                tmem_ld_32x32(acc2 + lane_addr + (bx * kLoadsPerBox + h) * 32, raw);
+                tmem_ld_wait_regs(raw);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(raw[j]);
+            }
+            if (p.bias_mode == 1) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, my_bias, j);
+            } else if (p.bias_mode == 2) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += row_bias;
+            }
+            activate_chunk(p.act, v);
+            if (!p.out_tma) {
+                if (row < p.M && col0 < p.N) store_row_chunk<T>(p, row_ptr, col0, v);
+            } else if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) packed[j] = __float_as_uint(v[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) packed[h * 16 + j] = pack2<T>(v[2 * j], v[2 * j + 1]);
+            }
         }
-        if (p.bias_mode == 1) {
+        if (p.out_tma) {
+            // the previous store of this warp read the same buffer: it must have finished reading
+            if (lane == 0) bulk_wait_group_read<0>();
+            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) v[j] += to_float<T>(__ldg(bias + static_cast<long long>(col0 + j) * p.bias_stride));
-        } else if (p.bias_mode == 2) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += row_bias;
+            for (uint32_t q = 0; q < 8; ++q) {
+                const uint32_t addr = staging + lane * 128 + ((q ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(addr), "r"(packed[4 * q]), "r"(packed[4 * q + 1]), "r"(packed[4 * q + 2]),
+                               "r"(packed[4 * q + 3]) : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(tmap_out, staging, static_cast<int32_t>(box_col), static_cast<int32_t>(m0 + quarter * 32),
+                             static_cast<int32_t>(batch));
+                bulk_commit_group();
+            }
         }
-        if (p.act != kActIdentity) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = apply_activation(p.act, v[j]);
-        }
-        if (row < p.M) store_row_chunk<T>(p, row_ptr, col0, v);
     }
+}
+
+// Before a warp leaves the kernel (or shared memory is reused for something else) its lane 0
+// waits for all its bulk stores.
+__device__ __forceinline__ void drain_finish(uint32_t lane)
+{
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
 }
 
 // InT / OutT: element type of the inputs and of the output (float, __half, __nv_bfloat16).
@@ -202,6 +298,7 @@ template <typename T, uint32_t BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_out,
                     const __grid_constant__ GemmParams p)
 {
     constexpr uint32_t kBTileBytes = BN * kRowBytes;
@@ -232,11 +329,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&tmem_full_bar[i]), 1);
-            mbar_init(smem_u32(&tmem_empty_bar[i]), 4);   // one arrive per epilogue warp
+            mbar_init(smem_u32(&tmem_empty_bar[i]), 8);   // one arrive per epilogue warp
         }
         fence_mbar_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
+        if (p.out_tma) prefetch_tensormap(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc_cta1(smem_u32(&tmem_holder), kTmemCols);
@@ -331,11 +429,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            drain_accumulator<T, BN>(p, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
+            drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+                                               (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
         }
+        drain_finish(lane);
         if (!ok) {
             abort_flag = 1;
             if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);
@@ -365,12 +465,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 //                of CTA 1 complete their byte count on CTA 0's barrier (cta_group::2 form).
 //   empty[s]     both CTAs, signalled together by one multicast tcgen05.commit of CTA 0.
 //   tmem_full[b] both CTAs, multicast tcgen05.commit after the tile's last MMA.
-//   tmem_empty[b] CTA 0 only, count 8: the four epilogue warps of each CTA.
+//   tmem_empty[b] CTA 0 only, count 16: the eight epilogue warps of each CTA.
 // No TMA load is multicast; all loads are plain per-CTA tile loads.
 template <typename T, uint32_t BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_out,
                          const __grid_constant__ GemmParams p)
 {
     constexpr uint32_t kBHalf = BN / 2;
@@ -404,11 +505,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (uint32_t i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&tmem_full_bar[i]), 1);
-            mbar_init(smem_u32(&tmem_empty_bar[i]), 8);
+            mbar_init(smem_u32(&tmem_empty_bar[i]), 16);
         }
         fence_mbar_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
+        if (p.out_tma) prefetch_tensormap(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc_cta2(smem_u32(&tmem_holder), kTmemCols);
@@ -510,11 +612,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            drain_accumulator<T, BN>(p, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
+            drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+                                               (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
         }
+        drain_finish(lane);
         if (!ok) {
             abort_flag = 1;
             if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);
@@ -555,6 +659,7 @@ template <uint32_t BN>
 __global__ void __launch_bounds__(kSplitThreads, 1)
 gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                           const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_out,
                           const __grid_constant__ GemmParams p)
 {
     using T = float;
@@ -596,6 +701,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_mbar_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
+        if (p.out_tma) prefetch_tensormap(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc_cta1(smem_u32(&tmem_holder), kTmemCols);
@@ -698,12 +804,14 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local / kAccBufs) & 1;
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            drain_accumulator<T, BN, true>(p, tmem_base + buf * 2 * BN, quarter, lane, batch, m0, n0,
-                                           tmem_base + buf * 2 * BN + BN);
+            drain_accumulator<T, BN, true, 1>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096, 0,
+                                              tmem_base + buf * 2 * BN, quarter, lane, batch, m0, n0,
+                                              tmem_base + buf * 2 * BN + BN);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
         }
+        drain_finish(lane);
         if (!ok) {
             abort_flag = 1;
             if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);

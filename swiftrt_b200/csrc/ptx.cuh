@@ -68,15 +68,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                  : "memory");
 }
 
+// One try_wait with a suspend-time hint: the hardware parks the thread until the phase completes
+// or the hint (in nanoseconds) runs out, so a waiting role does not spin on the issue ports that
+// the epilogue warps need.
+constexpr uint32_t kSuspendHintNs = 200000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return done != 0;
 }
@@ -87,10 +92,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return done != 0;
 }
@@ -99,17 +104,17 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Waits for the phase with the given parity.  Returns false when the limit ran out or
-// when another role of this CTA already gave up (*abort_flag != 0).
+// when another role of this CTA already gave up (*abort_flag != 0).  Each failed try_wait has
+// already slept for up to kSuspendHintNs, so the bookkeeping below runs a few thousand times a
+// second at most.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
-    for (uint32_t spin = 1;; ++spin) {
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 0x3f) == 0) {
-            if (*abort_flag != 0) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) return false;
-        }
+        if (*abort_flag != 0) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
     }
 }
 
@@ -117,12 +122,10 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
-    for (uint32_t spin = 1;; ++spin) {
+    for (;;) {
         if (mbar_try_wait_cluster(bar, parity)) return true;
-        if ((spin & 0x3f) == 0) {
-            if (*abort_flag != 0) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) return false;
-        }
+        if (*abort_flag != 0) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
     }
 }
 
@@ -142,6 +145,32 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
         " [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
+}
+
+// 3-D tiled store shared -> global (bulk async group of the issuing thread).  Elements outside
+// the tensor are not written, so ragged tile edges need no masking.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// waits until at most N of this thread's bulk groups still READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// waits until at most N of this thread's bulk groups are incomplete (writes performed)
+template <int N>
+__device__ __forceinline__ void bulk_wait_group()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Same load issued by one CTA of a cta_group::2 pair: the data lands in this CTA's shared
@@ -281,6 +310,19 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Same wait, tied to the destination registers of an earlier load: the compiler may not read
+// (or move) them before this statement, which is when the hardware has written them.
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;"
+        : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+          "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+          "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+          "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+        :
+        : "memory");
 }
 
 // ----------------------------------------------------------------------------- cluster

@@ -281,25 +281,48 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
 
     plan.Q = Q;
     uint32_t bn = (uint32_t)g_tuning.tile_n.load();
-    // CTA pairs (256 x BN tiles) when the problem has enough 256-row tiles to fill the device
+    // Tile choice by a small cost model: time ~ waves x (time of one tile).  A 128 x BN tile costs
+    // BN / efficiency(BN) (narrow MMAs re-read A more often per flop); a CTA pair's 256 x BN tile
+    // costs about the same as one CTA's 128 x BN tile and fills the device with half as many tiles.
+    auto tile_cost = [](uint32_t n) { return n == 256 ? 256.0 : n == 128 ? 171.0 : 128.0; };
+    auto waves = [](uint64_t tiles, uint64_t units) { return (double)((tiles + units - 1) / units); };
+    auto tiles_for = [&](uint32_t tm, uint32_t n) { return ((Q.M + tm - 1) / tm) * ((Q.N + n - 1) / n) * Q.batch; };
+    const uint64_t sms = (uint64_t)dev.sms;
+    auto best_single = [&](uint32_t& n_out) {
+        double best = 1e300;
+        for (uint32_t n : {256u, 128u, 64u}) {
+            if (n > 64 && Q.N <= n / 2) continue;                       // mostly padding
+            const double c = waves(tiles_for(kTileM, n), sms) * tile_cost(n);
+            if (c < best) { best = c; n_out = n; }
+        }
+        return best;
+    };
     bool pair = false;
-    if (split) pair = false;
-    else if (force == srtMatmulKernelTcgen05Pair) pair = true;
-    else if (force == 0) pair = Q.M >= 256 && ((Q.M + 255) / 256) * ((Q.N + 255) / 256) * Q.batch >= (uint64_t)dev.sms;
-    const uint32_t tile_m = pair ? 2 * kTileM : kTileM;
-    if (pair) {
+    if (split) {
+        pair = false;
+        if (bn != 64 && bn != 128 && bn != 256) best_single(bn);
+    } else if (force == srtMatmulKernelTcgen05Pair) {
+        pair = true;
         if (bn != 128 && bn != 256) bn = Q.N <= 128 ? 128 : 256;
-    } else if (bn != 64 && bn != 128 && bn != 256) {
-        // widest tile that still gives every SM work; narrow tiles for narrow outputs
-        const uint64_t tm = (Q.M + kTileM - 1) / kTileM;
-        bn = 256;
-        while (bn > 64 && (Q.N <= bn / 2 || tm * ((Q.N + bn - 1) / bn) * Q.batch < (uint64_t)dev.sms)) bn /= 2;
+    } else if (bn == 64 || bn == 128 || bn == 256) {
+        pair = false;                                                   // explicit single-CTA tile width
+    } else {
+        uint32_t n1 = 256;
+        const double single = best_single(n1);
+        bn = n1;
+        // pairs pay off in long main loops; short ones are bound by the epilogue, where two
+        // independent CTAs drain faster
+        if (force == 0 && Q.M > kTileM && Q.K >= 1024 && Q.N > 128) {
+            const double paired = waves(tiles_for(2 * kTileM, 256), sms / 2) * tile_cost(256) / 1.05;
+            if (paired <= single) { pair = true; bn = 256; }
+        }
     }
+    const uint32_t tile_m = pair ? 2 * kTileM : kTileM;
     static const bool tf32_single = getenv("SRT_MATMUL_TF32_SINGLE") != nullptr;   // experiment knob: 1 x TF32
     const bool split3 = split && !tf32_single;
     const uint32_t stage_bytes = (kATileBytes + (pair ? bn / 2 : bn) * kRowBytes) * (split3 ? 2 : 1);
     uint32_t stages = (uint32_t)g_tuning.stages.load();
-    uint32_t max_stages = (227u * 1024u - 2048u) / stage_bytes;
+    uint32_t max_stages = (227u * 1024u - 2048u - kEpilogueStagingBytes) / stage_bytes;
     if (split3 && max_stages > 4) max_stages = 4;
     // Four 32 KB stages keep the pair kernel's MMAs fed; deeper rings measured slower on a
     // power-capped B200 (higher pipe utilisation, lower clock, lower L2 hit rate).
@@ -323,7 +346,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     plan.pub.aMajor = plan.ta.mn_major; plan.pub.bMajor = plan.tb.mn_major;
     plan.pub.fp32Split = split3;
     plan.pub.workspaceBytes = 0;
-    plan.pub.dynamicSmemBytes = (size_t)stages * stage_bytes + 1024;
+    plan.pub.dynamicSmemBytes = (size_t)stages * stage_bytes + kEpilogueStagingBytes + 1024;
 }
 
 // ------------------------------------------------------------------ tensor maps
@@ -376,45 +399,69 @@ cudaError_t encode_operand(CUtensorMap* map, const Problem& Q, const char* ptr, 
     return cudaSuccess;
 }
 
+// Opt-in to large dynamic shared memory once per (kernel instantiation, device); `done` is a
+// per-instantiation bit mask of devices.
+template <typename Kernel>
+cudaError_t ensure_smem_attr(Kernel kernel, std::atomic<uint64_t>& done, size_t smem)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
+    (void)smem;
+    if (e != cudaSuccess) return e;
+    done.fetch_or(bit, std::memory_order_release);
+    return cudaSuccess;
+}
+
 template <typename T, uint32_t BN>
-cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas, size_t smem,
+cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas, size_t smem,
                       cudaStream_t stream)
 {
     auto kernel = gemm_tcgen05_kernel<T, BN>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static std::atomic<uint64_t> attr_done{0};
+    cudaError_t e = ensure_smem_attr(kernel, attr_done, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<ctas, kGemmThreads, smem, stream>>>(ma, mb, gp);
+    kernel<<<ctas, kGemmThreads, smem, stream>>>(ma, mb, mo, gp);
     return cudaGetLastError();
 }
 
 template <typename T>
-cudaError_t launch_tc_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas,
+cudaError_t launch_tc_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas,
                          size_t smem, cudaStream_t stream)
 {
     switch (bn) {
-    case 64: return launch_tc<T, 64>(ma, mb, gp, ctas, smem, stream);
-    case 128: return launch_tc<T, 128>(ma, mb, gp, ctas, smem, stream);
-    default: return launch_tc<T, 256>(ma, mb, gp, ctas, smem, stream);
+    case 64: return launch_tc<T, 64>(ma, mb, mo, gp, ctas, smem, stream);
+    case 128: return launch_tc<T, 128>(ma, mb, mo, gp, ctas, smem, stream);
+    default: return launch_tc<T, 256>(ma, mb, mo, gp, ctas, smem, stream);
     }
 }
 
 template <uint32_t BN>
-cudaError_t launch_split(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas, size_t smem,
+cudaError_t launch_split(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas, size_t smem,
                          cudaStream_t stream)
 {
     auto kernel = gemm_tcgen05_split_kernel<BN>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static std::atomic<uint64_t> attr_done{0};
+    cudaError_t e = ensure_smem_attr(kernel, attr_done, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<ctas, kSplitThreads, smem, stream>>>(ma, mb, gp);
+    kernel<<<ctas, kSplitThreads, smem, stream>>>(ma, mb, mo, gp);
     return cudaGetLastError();
 }
 
 template <typename T, uint32_t BN>
-cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp, uint32_t ctas, size_t smem,
+cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas, size_t smem,
                         cudaStream_t stream)
 {
     auto kernel = gemm_tcgen05_pair_kernel<T, BN>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static std::atomic<uint64_t> attr_done{0};
+    static std::atomic<int> cluster_cache[64];           // max co-resident pairs per device, 0 = unknown
+    cudaError_t e = ensure_smem_attr(kernel, attr_done, smem);
+    if (e != cudaSuccess) return e;
+    int dev = 0;
+    e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
@@ -430,35 +477,52 @@ cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Gemm
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // SMs that cannot be paired inside their GPC stay idle: never ask for more pairs than fit at once
-    int max_clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
-    if (e != cudaSuccess) return e;
-    if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
+    int max_clusters = cluster_cache[dev & 63].load(std::memory_order_acquire);
+    if (max_clusters == 0) {
+        // queried once, with the largest shared-memory footprint the kernel may be launched with
+        cudaLaunchConfig_t q = cfg;
+        q.dynamicSmemBytes = 227 * 1024 - 1024;
+        e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &q);
+        if (e != cudaSuccess) return e;
+        if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
+        cluster_cache[dev & 63].store(max_clusters, std::memory_order_release);
+    }
     if (ctas / 2 > (uint32_t)max_clusters) cfg.gridDim.x = 2u * (uint32_t)max_clusters;
-    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, gp);
+    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, gp);
 }
 
 template <typename T>
-cudaError_t launch_pair_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& gp,
+cudaError_t launch_pair_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp,
                            uint32_t ctas, size_t smem, cudaStream_t stream)
 {
-    if (bn == 128) return launch_pair<T, 128>(ma, mb, gp, ctas, smem, stream);
-    return launch_pair<T, 256>(ma, mb, gp, ctas, smem, stream);
+    if (bn == 128) return launch_pair<T, 128>(ma, mb, mo, gp, ctas, smem, stream);
+    return launch_pair<T, 256>(ma, mb, mo, gp, ctas, smem, stream);
 }
 
-cudaError_t run_tc(const Plan& plan, cudaStream_t stream)
+// Everything a launch needs, computed once per distinct call signature (see the call cache).
+struct Prepared {
+    int32_t kernel = srtMatmulKernelNone;
+    srtDataType type = real32F;
+    uint32_t bn = 0, ctas = 0;
+    size_t smem = 0;
+    CUtensorMap ma, mb, mo;
+    GemmParams gp;
+    SimtParams sp;
+    dim3 grid;
+};
+
+cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
 {
     const Problem& Q = plan.Q;
     const bool pair = plan.pub.kernel == srtMatmulKernelTcgen05Pair;
     const uint32_t bn = (uint32_t)plan.pub.tileN;
     const uint32_t tile_m = (uint32_t)plan.pub.tileM;
     const uint32_t b_rows = pair ? bn / 2 : bn;           // rows of B each CTA stages
-    GemmParams gp;
+    GemmParams& gp = pr.gp;
     memset(&gp, 0, sizeof gp);
-    CUtensorMap ma, mb;
-    cudaError_t e = encode_operand(&ma, Q, Q.a, plan.ta, Q.M, Q.a_b, kTileM, gp.a);
+    cudaError_t e = encode_operand(&pr.ma, Q, Q.a, plan.ta, Q.M, Q.a_b, kTileM, gp.a);
     if (e != cudaSuccess) return e;
-    e = encode_operand(&mb, Q, Q.b, plan.tb, Q.N, Q.b_b, b_rows, gp.b);
+    e = encode_operand(&pr.mb, Q, Q.b, plan.tb, Q.N, Q.b_b, b_rows, gp.b);
     if (e != cudaSuccess) return e;
 
     gp.M = (uint32_t)Q.M; gp.N = (uint32_t)Q.N; gp.K = (uint32_t)Q.K; gp.batch = (uint32_t)Q.batch;
@@ -489,34 +553,34 @@ cudaError_t run_tc(const Plan& plan, cudaStream_t stream)
     gp.act = Q.act;
     gp.out_vec_ok = (reinterpret_cast<uintptr_t>(Q.out) % 16 == 0) && ((gp.ldo * (long long)Q.elem) % 16 == 0) &&
                     ((Q.o_b * (long long)Q.elem) % 16 == 0) && (Q.N > 1 ? Q.o_n == 1 : true);
-
-    const size_t smem = plan.pub.dynamicSmemBytes;
-    const uint32_t ctas = (uint32_t)plan.pub.ctas;
-    if (plan.pub.kernel == srtMatmulKernelTcgen05Split) {
-        e = bn == 64    ? launch_split<64>(ma, mb, gp, ctas, smem, stream)
-            : bn == 128 ? launch_split<128>(ma, mb, gp, ctas, smem, stream)
-                        : launch_split<256>(ma, mb, gp, ctas, smem, stream);
-    } else if (pair) {
-        switch (Q.type) {
-        case real32F: e = launch_pair_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
-        case real16F: e = launch_pair_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
-        default: e = launch_pair_bn<__nv_bfloat16>(bn, ma, mb, gp, ctas, smem, stream); break;
-        }
-    } else {
-        switch (Q.type) {
-        case real32F: e = launch_tc_bn<float>(bn, ma, mb, gp, ctas, smem, stream); break;
-        case real16F: e = launch_tc_bn<__half>(bn, ma, mb, gp, ctas, smem, stream); break;
-        default: e = launch_tc_bn<__nv_bfloat16>(bn, ma, mb, gp, ctas, smem, stream); break;
-        }
+    // bulk tensor stores need the same alignment as 16-byte vector stores
+    gp.out_tma = 0;
+    memset(&pr.mo, 0, sizeof pr.mo);
+    if (gp.out_vec_ok && Q.N > 1) {
+        const CUtensorMapDataType dt = Q.type == real32F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : Q.type == real16F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        const bool one = Q.batch == 1;
+        cuuint64_t gdim[3] = {Q.N, Q.M, one ? 1 : Q.batch};
+        cuuint64_t gstride[2] = {(cuuint64_t)gp.ldo * Q.elem, one ? (cuuint64_t)gp.ldo * Q.elem * Q.M : (cuuint64_t)Q.o_b * Q.elem};
+        cuuint32_t box[3] = {kRowBytes / Q.elem, 32, 1}, estr[3] = {1, 1, 1};
+        if (gstride[1] % 16 == 0 && gstride[0] < (1ull << 40) && gstride[1] < (1ull << 40) &&
+            g_encode(&pr.mo, dt, 3, Q.out, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            gp.out_tma = 1;
     }
-    if (e == cudaSuccess) g_launches.fetch_add(1);
-    return e;
+    pr.kernel = plan.pub.kernel;
+    pr.type = Q.type;
+    pr.bn = bn;
+    pr.smem = plan.pub.dynamicSmemBytes;
+    pr.ctas = (uint32_t)plan.pub.ctas;
+    return cudaSuccess;
 }
 
-cudaError_t run_simt(const Plan& plan, cudaStream_t stream)
+cudaError_t prepare_simt(const Plan& plan, Prepared& pr)
 {
     const Problem& P = plan.Q;
-    SimtParams sp;
+    SimtParams& sp = pr.sp;
     memset(&sp, 0, sizeof sp);
     sp.M = (uint32_t)P.M; sp.N = (uint32_t)P.N; sp.K = (uint32_t)P.K; sp.batch = (uint32_t)P.batch;
     sp.a = P.a; sp.b = P.b; sp.out = P.out; sp.bias = P.bias;
@@ -530,15 +594,73 @@ cudaError_t run_simt(const Plan& plan, cudaStream_t stream)
     sp.b_n_fast = (P.b_n == 1) || (P.b_k != 1);
     const uint64_t tm = (P.M + kSimtTile - 1) / kSimtTile, tn = (P.N + kSimtTile - 1) / kSimtTile;
     if (tm > 65535) return fail(cudaErrorNotSupported, "strided kernel: more than 65535 row tiles");
-    dim3 grid((unsigned)tn, (unsigned)tm, (unsigned)P.batch);
-    switch (P.type) {
-    case real32F: gemm_simt_kernel<float><<<grid, 256, 0, stream>>>(sp); break;
-    case real16F: gemm_simt_kernel<__half><<<grid, 256, 0, stream>>>(sp); break;
-    default: gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(sp); break;
+    pr.grid = dim3((unsigned)tn, (unsigned)tm, (unsigned)P.batch);
+    pr.kernel = srtMatmulKernelSimt;
+    pr.type = P.type;
+    return cudaSuccess;
+}
+
+cudaError_t launch_prepared(const Prepared& pr, cudaStream_t stream)
+{
+    cudaError_t e;
+    const uint32_t bn = pr.bn;
+    switch (pr.kernel) {
+    case srtMatmulKernelSimt:
+        switch (pr.type) {
+        case real32F: gemm_simt_kernel<float><<<pr.grid, 256, 0, stream>>>(pr.sp); break;
+        case real16F: gemm_simt_kernel<__half><<<pr.grid, 256, 0, stream>>>(pr.sp); break;
+        default: gemm_simt_kernel<__nv_bfloat16><<<pr.grid, 256, 0, stream>>>(pr.sp); break;
+        }
+        e = cudaGetLastError();
+        break;
+    case srtMatmulKernelTcgen05Split:
+        e = bn == 64    ? launch_split<64>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream)
+            : bn == 128 ? launch_split<128>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream)
+                        : launch_split<256>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
+        break;
+    case srtMatmulKernelTcgen05Pair:
+        switch (pr.type) {
+        case real32F: e = launch_pair_bn<float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        case real16F: e = launch_pair_bn<__half>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        default: e = launch_pair_bn<__nv_bfloat16>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        }
+        break;
+    default:
+        switch (pr.type) {
+        case real32F: e = launch_tc_bn<float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        case real16F: e = launch_tc_bn<__half>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        default: e = launch_tc_bn<__nv_bfloat16>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        }
+        break;
     }
-    cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) g_launches.fetch_add(1);
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return e;
+}
+
+// ------------------------------------------------------------------ call cache
+// Repeated calls with the same pointers, geometry and options (a training loop, a benchmark,
+// a layer applied to the same buffers) skip planning and tensor-map encoding.  The cache is
+// per host thread -- a SwiftRT queue is used by one thread only -- so it needs no lock.
+struct CallKey {
+    Problem P;
+    int32_t force, tile_n, stages, max_ctas;
+    int32_t device;
+};
+
+constexpr int kCallCacheSize = 64;
+struct CallCache {
+    bool valid[kCallCacheSize] = {};
+    CallKey key[kCallCacheSize];
+    Prepared value[kCallCacheSize];
+};
+thread_local CallCache* t_cache = nullptr;
+
+uint64_t hash_key(const CallKey& k)
+{
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(&k);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof k; ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return h;
 }
 
 cudaError_t plan_for(const Problem& P, Plan& plan)
@@ -564,13 +686,37 @@ cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aD
                                     const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
                                     const srtTensorDescriptor* oDesc, cudaStream_t stream)
 {
-    Problem P;
+    CallKey key;
+    memset(&key, 0, sizeof key);                 // padding bytes are part of the hashed key
+    Problem& P = key.P;
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
     if (e != cudaSuccess) return e;
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    key.force = g_tuning.force_kernel.load(std::memory_order_relaxed);
+    key.tile_n = g_tuning.tile_n.load(std::memory_order_relaxed);
+    key.stages = g_tuning.stages.load(std::memory_order_relaxed);
+    key.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
+    key.device = dev;
+    if (!t_cache) t_cache = new CallCache();
+    const int slot = (int)(hash_key(key) % kCallCacheSize);
+    if (t_cache->valid[slot] && memcmp(&t_cache->key[slot], &key, sizeof key) == 0)
+        return launch_prepared(t_cache->value[slot], stream);
+
     Plan plan;
     e = plan_for(P, plan);
     if (e != cudaSuccess) return e;
-    return plan.pub.kernel == srtMatmulKernelSimt ? run_simt(plan, stream) : run_tc(plan, stream);
+    Prepared& pr = t_cache->value[slot];
+    t_cache->valid[slot] = false;
+    e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, pr) : prepare_tc(plan, pr);
+    if (e != cudaSuccess) return e;
+    e = launch_prepared(pr, stream);
+    if (e == cudaSuccess) {
+        t_cache->key[slot] = key;
+        t_cache->valid[slot] = true;
+    }
+    return e;
 }
 
 cudaError_t srtMatmul(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
@@ -625,6 +771,10 @@ cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status)
     *status = v;
     return cudaSuccess;
 }
+
+#ifdef SRT_TRACE
+cudaError_t srtMatmulDebugTrace(long long* dst) { return cudaMemcpyFromSymbol(dst, srt::g_trace, sizeof(long long) * 8192); }
+#endif
 
 uint64_t srtMatmulLaunchCount(void) { return g_launches.load(); }
 

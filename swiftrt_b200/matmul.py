@@ -40,30 +40,72 @@ def _result_shape(lhs, transpose_lhs, rhs, transpose_rhs):
     return batch + (ls[0], rs[1])
 
 
+_DESC_CACHE: dict = {}
+_DESC_CACHE_MAX = 512
+
+
+def _descriptor(t: torch.Tensor) -> Descriptor:
+    """Descriptor for a tensor's geometry; built once per (shape, strides, dtype) and reused --
+    descriptors hold no pointer, so tensors with equal geometry share one."""
+    key = (t.dtype, tuple(t.shape), t.stride())
+    d = _DESC_CACHE.get(key)
+    if d is None:
+        if len(_DESC_CACHE) >= _DESC_CACHE_MAX:
+            _DESC_CACHE.clear()
+        d = _DESC_CACHE[key] = Descriptor(t)
+    return d
+
+
+class MatmulOp:
+    """A prepared call: descriptors and arguments are marshalled once, `op()` only enqueues.
+    The object form of the operator, as DeviceMatmul2 / CudaMatmul2 is in the reference
+    (cpu/functions/CpuMatmul.swift:21-58, cuda/functions/CudaMatmul.swift:71-120).  The tensors
+    must stay alive and keep their geometry while the op is used."""
+
+    def __init__(self, out: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
+                 transpose_rhs: bool, bias: torch.Tensor | None = None,
+                 activation: ActivationType | None = None):
+        if not (lhs.is_cuda and rhs.is_cuda and out.is_cuda):
+            raise ValueError("device tensors expected; use matmul_host for host buffers")
+        self.out = out
+        self._keep = (lhs, rhs, bias)
+        self._device = out.device
+        self._index = out.device.index if out.device.index is not None else torch.cuda.current_device()
+        da, db, do = _descriptor(lhs), _descriptor(rhs), _descriptor(out)
+        self._descs = (da, db, do)
+        if bias is None and activation is None:
+            self._fn = lib.srtMatmul
+            self._args = (lhs.data_ptr(), da.ref(), bool(transpose_lhs), rhs.data_ptr(), db.ref(), bool(transpose_rhs),
+                          out.data_ptr(), do.ref())
+        else:
+            dbias = _descriptor(bias) if bias is not None else None
+            self._descs += (dbias,)
+            self._fn = lib.srtMatmulBiasActivation
+            self._args = (lhs.data_ptr(), da.ref(), bool(transpose_lhs), rhs.data_ptr(), db.ref(), bool(transpose_rhs),
+                          bias.data_ptr() if bias is not None else None, dbias.ref() if dbias is not None else None,
+                          int(activation if activation is not None else ActivationType.identity),
+                          out.data_ptr(), do.ref())
+
+    def __call__(self) -> torch.Tensor:
+        """Enqueues the product on torch's current stream of the output's device."""
+        idx = self._index
+        if torch.cuda.current_device() != idx:
+            with torch.cuda.device(idx):
+                rc = self._fn(*self._args, torch.cuda.current_stream(idx).cuda_stream)
+        else:
+            rc = self._fn(*self._args, torch.cuda.current_stream(idx).cuda_stream)
+        if rc != _lib.cudaSuccess:
+            raise MatmulError(rc, _lib.last_error())
+        return self.out
+
+
 def matmul_into(out: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
                 transpose_rhs: bool, bias: torch.Tensor | None = None,
                 activation: ActivationType | None = None) -> torch.Tensor:
     """The queue-level call: writes op(lhs).op(rhs) [+ bias, activation] into `out`, which may be a
     strided view (CpuMath.swift:355-369 takes the result inout).  Asynchronous on torch's current
     stream of out's device."""
-    if not (lhs.is_cuda and rhs.is_cuda and out.is_cuda):
-        raise ValueError("device tensors expected; use matmul_host for host buffers")
-    da, db, do = Descriptor(lhs), Descriptor(rhs), Descriptor(out)
-    with torch.cuda.device(out.device):
-        stream = _stream_ptr(out.device)
-        if bias is None and activation is None:
-            rc = lib.srtMatmul(lhs.data_ptr(), da.ref(), transpose_lhs, rhs.data_ptr(), db.ref(), transpose_rhs,
-                               out.data_ptr(), do.ref(), stream)
-        else:
-            dbias = Descriptor(bias) if bias is not None else None
-            rc = lib.srtMatmulBiasActivation(
-                lhs.data_ptr(), da.ref(), transpose_lhs, rhs.data_ptr(), db.ref(), transpose_rhs,
-                bias.data_ptr() if bias is not None else None, dbias.ref() if dbias is not None else None,
-                int(activation if activation is not None else ActivationType.identity),
-                out.data_ptr(), do.ref(), stream)
-    if rc != _lib.cudaSuccess:
-        raise MatmulError(rc, _lib.last_error())
-    return out
+    return MatmulOp(out, lhs, transpose_lhs, rhs, transpose_rhs, bias, activation)()
 
 
 def matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,
