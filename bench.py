@@ -116,7 +116,8 @@ def cpu_sample(M, N, K, b, threads=None, target_s=12.0):
     import numpy as np
     from oracle import oracle
     if threads is None:
-        threads = oracle.lib().oracle_max_threads()
+        # every core this process may run on (torchrun sets OMP_NUM_THREADS=1, which is not the machine)
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else oracle.lib().oracle_max_threads()
     rng = np.random.default_rng(1)
     probe_rows = threads * 8                      # one block of 8 rows per thread
     a = oracle.encode(rng.random((probe_rows, K), dtype=np.float32) * 2.0 - 1.0, oracle.BF16)

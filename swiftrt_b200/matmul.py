@@ -133,22 +133,78 @@ def matmul_gradients(out_grad: torch.Tensor, lhs: torch.Tensor, transpose_lhs: b
     return (matmul(out_grad, rhs, True, True), matmul(lhs, out_grad, True, True))
 
 
+_HOST_STREAMS: dict = {}
+_HOST_CHUNK_BYTES = 32 << 20       # below this much of lhs + result, one copy each way is as fast
+
+
+def _side_streams(dev: torch.device):
+    """(copy-in stream, copy-out stream) of a device, created once."""
+    key = (dev.type, dev.index)
+    if key not in _HOST_STREAMS:
+        _HOST_STREAMS[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return _HOST_STREAMS[key]
+
+
 def matmul_host(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,
                 bias: torch.Tensor | None = None, activation: ActivationType | None = None,
-                device="cuda:0", out_host: torch.Tensor | None = None) -> torch.Tensor:
+                device="cuda:0", out_host: torch.Tensor | None = None, chunks: int = 8) -> torch.Tensor:
     """The same operator for HOST tensors: inputs are copied to `device`, multiplied there and the
-    result is copied back, all on the current stream, which is synchronised before returning.
-    This is what the reference's storage does around a queue call (host replicas migrate on
-    deviceRead, DiscreteStorage.swift:310-381).  Pinned host memory makes the copies asynchronous."""
+    result is copied back; the call returns when the result is in host memory.  This is what the
+    reference's storage does around a queue call (host replicas migrate on deviceRead,
+    DiscreteStorage.swift:310-381).  Pinned host memory makes the copies asynchronous.
+
+    Large rank-2 products with a row-major, untransposed lhs are pipelined over `chunks` blocks of
+    rows: rhs is copied first, then the copy-in of row block i + 1, the product of block i and the
+    copy-out of block i - 1 overlap (the two copy directions use separate DMA engines)."""
     dev = torch.device(device)
-    a = lhs.to(dev, non_blocking=True)
-    b = rhs.to(dev, non_blocking=True)
-    bz = bias.to(dev, non_blocking=True) if bias is not None else None
-    c = matmul(a, b, transposed_lhs, transposed_rhs, bz, activation)
+    M = lhs.shape[-1] if transposed_lhs else lhs.shape[-2]
+    N = rhs.shape[-2] if transposed_rhs else rhs.shape[-1]
+    pipelined = (lhs.dim() == 2 and rhs.dim() == 2 and not transposed_lhs and lhs.is_contiguous() and chunks > 1
+                 and M >= 128 * chunks
+                 and (lhs.numel() + M * N) * lhs.element_size() >= _HOST_CHUNK_BYTES
+                 and (out_host is None or out_host.is_contiguous()))
+    if not pipelined:
+        a = lhs.to(dev, non_blocking=True)
+        b = rhs.to(dev, non_blocking=True)
+        bz = bias.to(dev, non_blocking=True) if bias is not None else None
+        c = matmul(a, b, transposed_lhs, transposed_rhs, bz, activation)
+        if out_host is None:
+            out_host = torch.empty(c.shape, dtype=c.dtype, pin_memory=True)
+        out_host.copy_(c, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        return out_host
+
     if out_host is None:
-        out_host = torch.empty(c.shape, dtype=c.dtype, pin_memory=True)
-    out_host.copy_(c, non_blocking=True)
-    torch.cuda.current_stream(dev).synchronize()
+        out_host = torch.empty((M, N), dtype=lhs.dtype, pin_memory=True)
+    main = torch.cuda.current_stream(dev)
+    s_in, s_out = _side_streams(dev)
+    s_in.wait_stream(main)
+    s_out.wait_stream(main)
+    with torch.cuda.device(dev):
+        a = torch.empty(lhs.shape, dtype=lhs.dtype, device=dev)
+        c = torch.empty((M, N), dtype=lhs.dtype, device=dev)
+        with torch.cuda.stream(s_in):
+            b = rhs.to(dev, non_blocking=True)
+            bz = bias.to(dev, non_blocking=True) if bias is not None else None
+        rows = -(-M // chunks)
+        rows = -(-rows // 128) * 128                      # whole tiles per block
+        for r0 in range(0, M, rows):
+            r1 = min(M, r0 + rows)
+            with torch.cuda.stream(s_in):
+                a[r0:r1].copy_(lhs[r0:r1], non_blocking=True)
+                arrived = s_in.record_event()
+            main.wait_event(arrived)
+            matmul_into(c[r0:r1], a[r0:r1], False, b, transposed_rhs, bz, activation)
+            done = main.record_event()
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                out_host[r0:r1].copy_(c[r0:r1], non_blocking=True)
+        # the device buffers must outlive the side streams' work
+        for t in (a, b, c) + ((bz,) if bz is not None else ()):
+            t.record_stream(main)
+            t.record_stream(s_in)
+            t.record_stream(s_out)
+    s_out.synchronize()
     return out_host
 
 

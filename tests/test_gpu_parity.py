@@ -383,6 +383,26 @@ def test_host_buffer_entry_and_launch_counter(srt, oracle):
     assert oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16)) <= 2e-3
 
 
+def test_host_buffer_entry_pipelined_over_row_blocks(srt, oracle):
+    """Large host products are cut into row blocks whose copies overlap the math: same result."""
+    rng = np.random.default_rng(32)
+    M, K, N = 4096 + 200, 4096, 2048
+    a, b = random_bits(oracle, rng, (M, K), BF16), random_bits(oracle, rng, (K, N), BF16)
+    bias = random_bits(oracle, rng, (N,), BF16)
+    ha = torch.from_numpy(a).view(torch.bfloat16).pin_memory()
+    hb = torch.from_numpy(b).view(torch.bfloat16).pin_memory()
+    hbias = torch.from_numpy(bias).view(torch.bfloat16).pin_memory()
+    before = srt.launch_count()
+    hc = srt.matmul_host(ha, hb, bias=hbias, activation=srt.ActivationType.relu)
+    assert 2 <= srt.launch_count() - before <= 8         # one launch per row block
+    whole = srt.matmul_host(ha, hb, bias=hbias, activation=srt.ActivationType.relu, chunks=1)
+    assert torch.equal(hc, whole)
+    rows = _sample_rows(M, 48)
+    ref = oracle.matmul(np.ascontiguousarray(a[rows]), b, BF16, bias=bias, activation="relu")
+    got = hc.view(torch.uint16).numpy()[rows]
+    assert oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16)) <= 2e-3
+
+
 def test_unsupported_inputs_return_not_supported(srt):
     a = torch.zeros((4, 4), dtype=torch.float64, device="cuda:0")
     with pytest.raises(srt.MatmulError) as e:
