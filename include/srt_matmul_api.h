@@ -155,7 +155,8 @@ typedef struct {
     int32_t swapped;       /* 1 when computed as out^T = op(b)^T . op(a)^T (col-order out) */
     int32_t aMajor, bMajor;/* 0 = K-major, 1 = MN-major operand as the kernel sees it */
     int32_t fp32Split;     /* 1 when fp32 runs as 3 x TF32 on the tensor cores */
-    size_t  workspaceBytes;/* device scratch the call needs: always 0 */
+    int32_t splitK;        /* > 1: the reduction is cut into this many parts, summed by a second kernel */
+    size_t  workspaceBytes;/* device scratch of a split-K call (fp32 partial sums), else 0 */
     size_t  dynamicSmemBytes;
 } srtMatmulPlan;
 
@@ -172,6 +173,12 @@ cudaError_t srtMatmulQueryPlan(
  * always takes the 3 x TF32 kernel when a tensor-core kernel is forced);
  * tileN: 64, 128 or 256; stages: 2..8; maxCtas: cap on the persistent grid. */
 cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas);
+
+/* Split-K override, process-wide: 0 = automatic (Float32 with K > 2048; few tiles with a long
+ * reduction), 1 = never, n > 1 = cut the reduction into (up to) n parts whenever the tensor-core
+ * kernel for one CTA per tile runs.  The fp32 partial sums live in a workspace that the library
+ * keeps per (device, stream) and grows on demand with cudaMalloc. */
+cudaError_t srtMatmulSetSplitK(int32_t splits);
 
 /* Device-side status of the last tensor-core launches on the current device: 0 = all
  * pipeline waits completed; non-zero = a bounded wait gave up (the code says which) and

@@ -33,18 +33,18 @@ class MatmulPlan(ctypes.Structure):
                 ("tileM", ctypes.c_int32), ("tileN", ctypes.c_int32), ("tileK", ctypes.c_int32),
                 ("stages", ctypes.c_int32), ("ctas", ctypes.c_int32), ("tiles", ctypes.c_int32),
                 ("swapped", ctypes.c_int32), ("aMajor", ctypes.c_int32), ("bMajor", ctypes.c_int32),
-                ("fp32Split", ctypes.c_int32),
+                ("fp32Split", ctypes.c_int32), ("splitK", ctypes.c_int32),
                 ("workspaceBytes", ctypes.c_size_t), ("dynamicSmemBytes", ctypes.c_size_t)]
 
 
 # every symbol include/srt_matmul_api.h declares
-EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning",
+EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString"]
 
 if not os.path.exists(SO):
     raise ImportError(
         f"{SO} is missing: the CUDA library has not been built. Run "
-        "`python -m swiftrt_b200.build` (needs nvcc); there is no CPU or PyTorch fallback.")
+        "`python swiftrt_b200/build.py` (needs nvcc); there is no CPU or PyTorch fallback.")
 
 lib = ctypes.CDLL(SO)
 
@@ -58,6 +58,8 @@ lib.srtMatmulQueryPlan.restype = ctypes.c_int
 lib.srtMatmulQueryPlan.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.POINTER(MatmulPlan)]
 lib.srtMatmulSetTuning.restype = ctypes.c_int
 lib.srtMatmulSetTuning.argtypes = [ctypes.c_int32] * 4
+lib.srtMatmulSetSplitK.restype = ctypes.c_int
+lib.srtMatmulSetSplitK.argtypes = [ctypes.c_int32]
 lib.srtMatmulCheckStatus.restype = ctypes.c_int
 lib.srtMatmulCheckStatus.argtypes = [_P, ctypes.POINTER(ctypes.c_uint32)]
 lib.srtMatmulLaunchCount.restype = ctypes.c_uint64

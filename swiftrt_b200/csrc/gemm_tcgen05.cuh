@@ -62,6 +62,8 @@ struct GemmParams {
     uint32_t M, N, K, batch;
     uint32_t tiles_m, tiles_n, tiles_per_batch, num_tiles;
     uint32_t k_blocks, kb_elems, group_m;
+    uint32_t k_splits, kb_per_split;   // split-K: work unit = (tile, split); num_tiles counts units
+    uint32_t tiles_total;              // output tiles over all batch items (= num_tiles / k_splits)
     OperandParams a, b;
     uint32_t idesc;
     uint32_t stage_tx_bytes;
@@ -117,20 +119,32 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// tile index -> (batch, first row, first column); m-tiles are visited in groups of group_m
-// so that the CTAs running at the same time share A and B tiles in L2.
-__device__ __forceinline__ void decode_tile(const GemmParams& p, uint32_t tile, uint32_t bn,
-                                            uint32_t& batch, uint32_t& m0, uint32_t& n0)
+// work unit -> tile coordinates; m-tiles are visited in groups of group_m so that the CTAs running
+// at the same time share A and B tiles in L2.  With split-K, unit u is split u / tiles_total of
+// tile u % tiles_total: it reduces k-blocks [kb0, kb1) and writes partial sums to the slice
+// `obatch` of an fp32 workspace laid out [split][batch][M][N].
+struct TileCoord {
+    uint32_t batch, obatch, m0, n0, kb0, kb1;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, uint32_t unit, uint32_t bn)
 {
-    batch = tile / p.tiles_per_batch;
-    uint32_t t = tile - batch * p.tiles_per_batch;
+    TileCoord c;
+    const uint32_t split = unit / p.tiles_total;
+    const uint32_t tile = unit - split * p.tiles_total;
+    c.batch = tile / p.tiles_per_batch;
+    uint32_t t = tile - c.batch * p.tiles_per_batch;
     uint32_t per_group = p.group_m * p.tiles_n;
     uint32_t group = t / per_group;
     uint32_t first_m = group * p.group_m;
     uint32_t gm = min(p.group_m, p.tiles_m - first_m);
     uint32_t r = t - group * per_group;
-    m0 = (first_m + r % gm) * kTileM;
-    n0 = (r / gm) * bn;
+    c.m0 = (first_m + r % gm) * kTileM;
+    c.n0 = (r / gm) * bn;
+    c.obatch = split * p.batch + c.batch;
+    c.kb0 = split * p.kb_per_split;
+    c.kb1 = min(p.k_blocks, c.kb0 + p.kb_per_split);
+    return c;
 }
 
 // Stores 32 consecutive columns of one output row held as fp32 in v[].
@@ -294,7 +308,8 @@ __device__ __forceinline__ void drain_finish(uint32_t lane)
 
 // InT / OutT: element type of the inputs and of the output (float, __half, __nv_bfloat16).
 // BN: tile width (64, 128 or 256).  fp32 inputs are multiplied as TF32.
-template <typename T, uint32_t BN>
+// OutT differs from T only for split-K partial sums (16-bit inputs, fp32 workspace).
+template <typename T, uint32_t BN, typename OutT = T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
@@ -351,9 +366,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                uint32_t batch, m0, n0;
-                decode_tile(p, tile, BN, batch, m0, n0);
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                const TileCoord tc = decode_tile(p, tile, BN);
+                uint32_t batch = tc.batch, m0 = tc.m0, n0 = tc.n0;
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     const uint32_t sa = smem_base + stage * kStageBytes;
@@ -393,7 +408,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                const TileCoord tc = decode_tile(p, tile, BN);
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + stage * kStageBytes;
@@ -404,8 +420,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (uint32_t k = 0; k < kKStepsPerStage; ++k) {
                         const uint64_t adesc = (static_cast<uint64_t>(p.a.desc_hi) << 32) | (a_lo + k * p.a.kstep);
                         const uint64_t bdesc = (static_cast<uint64_t>(p.b.desc_hi) << 32) | (b_lo + k * p.b.kstep);
-                        if constexpr (sizeof(T) == 4) umma_tf32_cta1(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
-                        else                          umma_f16_cta1(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+                        if constexpr (sizeof(T) == 4) umma_tf32_cta1(d_tmem, adesc, bdesc, p.idesc, (kb != tc.kb0 || k != 0));
+                        else                          umma_f16_cta1(d_tmem, adesc, bdesc, p.idesc, (kb != tc.kb0 || k != 0));
                     }
                     umma_commit_cta1(smem_u32(&empty_bar[stage]));
                     if (++stage == stages) { stage = 0; phase ^= 1; }
@@ -423,13 +439,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t local = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
-            uint32_t batch, m0, n0;
-            decode_tile(p, tile, BN, batch, m0, n0);
+            const TileCoord tc = decode_tile(p, tile, BN);
+            uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             const uint32_t buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+            drain_accumulator<OutT, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
@@ -528,11 +544,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
-                uint32_t batch, m0, n0;
-                decode_tile(p, tile, BN, batch, m0, n0);
+                const TileCoord tc = decode_tile(p, tile, BN);
+                uint32_t batch = tc.batch, m0 = tc.m0, n0 = tc.n0;
                 m0 = m0 * 2 + cta_rank * kTileM;            // decode_tile counts 128-row units; pair tiles are 256 rows
                 n0 += cta_rank * kBHalf;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
                     // every load of the pair reports to the leader's barrier
                     const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
@@ -574,7 +590,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * BN;
-                    for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    const TileCoord tc = decode_tile(p, tile, BN);
+                    for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                         if (!mbar_wait_cluster(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t sa = smem_base + stage * kStageBytes;
@@ -585,8 +602,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         for (uint32_t k = 0; k < kKStepsPerStage; ++k) {
                             const uint64_t adesc = (static_cast<uint64_t>(p.a.desc_hi) << 32) | (a_lo + k * p.a.kstep);
                             const uint64_t bdesc = (static_cast<uint64_t>(p.b.desc_hi) << 32) | (b_lo + k * p.b.kstep);
-                            if constexpr (sizeof(T) == 4) umma_tf32_cta2(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
-                            else                          umma_f16_cta2(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+                            if constexpr (sizeof(T) == 4) umma_tf32_cta2(d_tmem, adesc, bdesc, p.idesc, (kb != tc.kb0 || k != 0));
+                            else                          umma_f16_cta2(d_tmem, adesc, bdesc, p.idesc, (kb != tc.kb0 || k != 0));
                         }
                         umma_commit_cta2_mc(smem_u32(&empty_bar[stage]), 3);
                         if (++stage == stages) { stage = 0; phase ^= 1; }
@@ -605,8 +622,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t local = 0;
         bool ok = true;
         for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
-            uint32_t batch, m0, n0;
-            decode_tile(p, tile, BN, batch, m0, n0);
+            const TileCoord tc = decode_tile(p, tile, BN);
+            uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             m0 = m0 * 2 + cta_rank * kTileM;
             const uint32_t buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
@@ -718,9 +735,9 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                uint32_t batch, m0, n0;
-                decode_tile(p, tile, BN, batch, m0, n0);
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                const TileCoord tc = decode_tile(p, tile, BN);
+                uint32_t batch = tc.batch, m0 = tc.m0, n0 = tc.n0;
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     const uint32_t sa = smem_base + stage * kStageBytes;
@@ -761,7 +778,8 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tc_fence_after_sync();
                 const uint32_t d_main = tmem_base + buf * 2 * BN;
                 const uint32_t d_small = d_main + BN;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                const TileCoord tc = decode_tile(p, tile, BN);
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&ready_bar[stage]), phase, &abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + stage * kStageBytes;
@@ -778,8 +796,8 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         // The accumulator add truncates toward zero, a bias that grows with the number
                         // of adds and with the accumulator's magnitude: the correction terms get their
                         // own (2^-11 times smaller) accumulator and are added once, in the epilogue.
-                        umma_tf32_cta1(d_main, ahi64 | (a_hi + da), bhi64 | (b_hi + db), p.idesc, (kb | k) != 0);
-                        umma_tf32_cta1(d_small, ahi64 | (a_lo + da), bhi64 | (b_hi + db), p.idesc, (kb | k) != 0);
+                        umma_tf32_cta1(d_main, ahi64 | (a_hi + da), bhi64 | (b_hi + db), p.idesc, (kb != tc.kb0 || k != 0));
+                        umma_tf32_cta1(d_small, ahi64 | (a_lo + da), bhi64 | (b_hi + db), p.idesc, (kb != tc.kb0 || k != 0));
                         umma_tf32_cta1(d_small, ahi64 | (a_hi + da), bhi64 | (b_lo + db), p.idesc, 1);
                     }
                     umma_commit_cta1(smem_u32(&empty_bar[stage]));
@@ -798,8 +816,8 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t local = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
-            uint32_t batch, m0, n0;
-            decode_tile(p, tile, BN, batch, m0, n0);
+            const TileCoord tc = decode_tile(p, tile, BN);
+            uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             const uint32_t buf = local % kAccBufs;
             const uint32_t acc_phase = (local / kAccBufs) & 1;
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
@@ -822,7 +840,8 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-            for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+            const TileCoord tc = decode_tile(p, tile, BN);
+            for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
                 if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
                 const uint32_t hi_base = smem_base + stage * kStageBytes;
 #pragma unroll 4

@@ -12,8 +12,10 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "gemm_simt.cuh"
+#include "gemm_splitk.cuh"
 #include "gemm_tcgen05.cuh"
 
 namespace {
@@ -24,7 +26,7 @@ thread_local char g_error[512] = "";
 std::atomic<uint64_t> g_launches{0};
 
 struct Tuning {
-    std::atomic<int32_t> force_kernel{0}, tile_n{0}, stages{0}, max_ctas{0};
+    std::atomic<int32_t> force_kernel{0}, tile_n{0}, stages{0}, max_ctas{0}, split_k{0};
 } g_tuning;
 
 cudaError_t fail(cudaError_t code, const char* fmt, ...)
@@ -221,6 +223,7 @@ struct Plan {
     Problem Q;                 // the problem as the kernel sees it (after a possible swap)
     TcOperand ta, tb;
     uint32_t bias_mode = 0;
+    uint32_t splits = 1, kb_per_split = 0;   // split-K: partial sums in an fp32 workspace + a reduce pass
 };
 
 void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
@@ -259,9 +262,10 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     // it; below that the strided kernel is as fast and keeps the reference's exact arithmetic
     // The tensor cores add into the fp32 accumulator with truncation, an error that grows
     // linearly with K (measured 9e-7 at K = 256, 2.6e-6 at K = 1024, relative Frobenius):
-    // beyond K = 2048 Float32 stays on the exact kernel to keep the 1e-5 tolerance.
+    // beyond K = 2048 the reduction is cut into chunks of 2048 whose fp32 partial sums are added
+    // in a second pass (split-K), which keeps the 1e-5 tolerance for any K.
     const bool split = tc && Q.type == real32F;
-    if (split && force == 0 && (Q.M * Q.N * Q.K * Q.batch < (1ull << 26) || Q.K > 2048)) tc = false;
+    if (split && force == 0 && Q.M * Q.N * Q.K * Q.batch < (1ull << 26)) tc = false;
     // tiny problems are launch-bound either way; keep them on the exact kernel
     if (tc && force == 0 && Q.M * Q.N * Q.K * Q.batch < (1ull << 18)) tc = false;
 
@@ -331,8 +335,48 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     const uint32_t kb_elems = kRowBytes / Q.elem;
     const uint64_t tiles_m = (Q.M + tile_m - 1) / tile_m, tiles_n = (Q.N + bn - 1) / bn;
     const uint64_t tiles = tiles_m * tiles_n * Q.batch;
+    // split-K: (1) Float32 beyond K = 2048, for accuracy; (2) few tiles and a long reduction, to
+    // give every SM work.  Partial sums go to an fp32 workspace [split][batch][M][N].
+    const uint32_t k_blocks = (uint32_t)((Q.K + kb_elems - 1) / kb_elems);
+    uint32_t splits = 1, kb_per_split = k_blocks;
+    const int32_t want_split = g_tuning.split_k.load();
+    if (!pair && want_split != 1) {
+        uint32_t target = 1;
+        if (want_split > 1) target = (uint32_t)want_split;
+        else {
+            if (split3 && Q.K > 2048) target = (uint32_t)((Q.K + 2047) / 2048);
+            if (tiles * 2 <= sms && k_blocks >= 32) {
+                uint32_t occ = (uint32_t)(sms / tiles);
+                if (occ > k_blocks / 16) occ = k_blocks / 16;
+                if (occ > 32) occ = 32;
+                if (occ > target) target = occ;
+            }
+        }
+        if (target > k_blocks) target = k_blocks;
+        if (target > 1) {
+            kb_per_split = (k_blocks + target - 1) / target;
+            if (split3 && kb_per_split * kb_elems > 2048) kb_per_split = 2048 / kb_elems;
+            splits = (k_blocks + kb_per_split - 1) / kb_per_split;
+        }
+        const uint64_t ws_bytes = (uint64_t)splits * Q.batch * Q.M * Q.N * 4;
+        if (splits > 1 && ws_bytes > (2ull << 30)) {
+            if (split3 && Q.K > 2048 && want_split == 0) {       // cannot hold the tolerance without it
+                plan.Q = P; plan.swapped = false; plan.bias_mode = P.bias ? 1 : 0;
+                plan.pub.kernel = srtMatmulKernelSimt;
+                plan.pub.tileM = kSimtTile; plan.pub.tileN = kSimtTile; plan.pub.tileK = kSimtK;
+                plan.pub.stages = 1;
+                plan.pub.tiles = (int32_t)(((P.M + kSimtTile - 1) / kSimtTile) * ((P.N + kSimtTile - 1) / kSimtTile) * P.batch);
+                plan.pub.ctas = plan.pub.tiles;
+                return;
+            }
+            splits = 1; kb_per_split = k_blocks;
+        }
+    }
+    plan.splits = splits;
+    plan.kb_per_split = kb_per_split;
+    const uint64_t work_units = tiles * splits;
     const uint64_t units = pair ? (uint64_t)dev.sms / 2 : (uint64_t)dev.sms;   // CTAs or CTA pairs
-    uint32_t ctas = (uint32_t)(tiles < units ? tiles : units);
+    uint32_t ctas = (uint32_t)(work_units < units ? work_units : units);
     const int32_t cap = g_tuning.max_ctas.load();
     if (cap > 0 && ctas > (uint32_t)cap) ctas = (uint32_t)cap;
     if (pair) ctas *= 2;
@@ -345,7 +389,8 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     plan.pub.swapped = plan.swapped;
     plan.pub.aMajor = plan.ta.mn_major; plan.pub.bMajor = plan.tb.mn_major;
     plan.pub.fp32Split = split3;
-    plan.pub.workspaceBytes = 0;
+    plan.pub.splitK = (int32_t)splits;
+    plan.pub.workspaceBytes = splits > 1 ? (size_t)splits * Q.batch * Q.M * Q.N * 4 : 0;
     plan.pub.dynamicSmemBytes = (size_t)stages * stage_bytes + kEpilogueStagingBytes + 1024;
 }
 
@@ -416,11 +461,11 @@ cudaError_t ensure_smem_attr(Kernel kernel, std::atomic<uint64_t>& done, size_t 
     return cudaSuccess;
 }
 
-template <typename T, uint32_t BN>
+template <typename T, uint32_t BN, typename OutT = T>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas, size_t smem,
                       cudaStream_t stream)
 {
-    auto kernel = gemm_tcgen05_kernel<T, BN>;
+    auto kernel = gemm_tcgen05_kernel<T, BN, OutT>;
     static std::atomic<uint64_t> attr_done{0};
     cudaError_t e = ensure_smem_attr(kernel, attr_done, smem);
     if (e != cudaSuccess) return e;
@@ -428,14 +473,14 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     return cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, typename OutT = T>
 cudaError_t launch_tc_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas,
                          size_t smem, cudaStream_t stream)
 {
     switch (bn) {
-    case 64: return launch_tc<T, 64>(ma, mb, mo, gp, ctas, smem, stream);
-    case 128: return launch_tc<T, 128>(ma, mb, mo, gp, ctas, smem, stream);
-    default: return launch_tc<T, 256>(ma, mb, mo, gp, ctas, smem, stream);
+    case 64: return launch_tc<T, 64, OutT>(ma, mb, mo, gp, ctas, smem, stream);
+    case 128: return launch_tc<T, 128, OutT>(ma, mb, mo, gp, ctas, smem, stream);
+    default: return launch_tc<T, 256, OutT>(ma, mb, mo, gp, ctas, smem, stream);
     }
 }
 
@@ -509,6 +554,12 @@ struct Prepared {
     GemmParams gp;
     SimtParams sp;
     dim3 grid;
+    // split-K only
+    uint32_t splits = 1;
+    size_t ws_bytes = 0;
+    void* ws_bound = nullptr;        // workspace the output tensor map and gp.out currently point at
+    ReduceParams rp;
+    uint32_t reduce_vec = 1, reduce_blocks = 0;
 };
 
 cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
@@ -529,9 +580,12 @@ cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
     gp.tiles_m = (uint32_t)((Q.M + tile_m - 1) / tile_m);
     gp.tiles_n = (uint32_t)((Q.N + bn - 1) / bn);
     gp.tiles_per_batch = gp.tiles_m * gp.tiles_n;
-    gp.num_tiles = (uint32_t)plan.pub.tiles;
+    gp.tiles_total = (uint32_t)plan.pub.tiles;
+    gp.k_splits = plan.splits;
+    gp.num_tiles = gp.tiles_total * plan.splits;          // work units
     gp.kb_elems = kRowBytes / Q.elem;
     gp.k_blocks = (uint32_t)((Q.K + gp.kb_elems - 1) / gp.kb_elems);
+    gp.kb_per_split = plan.splits > 1 ? plan.kb_per_split : gp.k_blocks;
     gp.group_m = pair ? 8 : 16;                           // 2048 rows of A per group either way
     {
         // experiment knob (not part of the ABI): rows of tiles per rasterisation group
@@ -574,6 +628,85 @@ cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
     pr.bn = bn;
     pr.smem = plan.pub.dynamicSmemBytes;
     pr.ctas = (uint32_t)plan.pub.ctas;
+    pr.splits = plan.splits;
+    pr.ws_bytes = 0;
+    pr.ws_bound = nullptr;
+    if (plan.splits > 1) {
+        // first pass: raw fp32 partial sums into the workspace (bound at launch); bias,
+        // activation, rounding and the output view belong to the reduce pass
+        pr.ws_bytes = plan.pub.workspaceBytes;
+        ReduceParams& rp = pr.rp;
+        memset(&rp, 0, sizeof rp);
+        rp.splits = plan.splits;
+        rp.slice = (unsigned long long)Q.batch * Q.M * Q.N;
+        rp.M = (uint32_t)Q.M; rp.N = (uint32_t)Q.N; rp.batch = (uint32_t)Q.batch;
+        rp.out = Q.out;
+        rp.o_b = Q.o_b; rp.o_m = Q.o_m; rp.o_n = Q.o_n;
+        rp.bias = Q.bias; rp.bias_stride = Q.bias_stride; rp.bias_mode = plan.bias_mode; rp.act = Q.act;
+        pr.reduce_vec = (Q.N % 4 == 0) ? 4 : 1;
+        const unsigned long long groups = rp.slice / pr.reduce_vec;
+        unsigned long long blocks = (groups + 255) / 256;
+        if (blocks > 148ull * 16) blocks = 148ull * 16;
+        pr.reduce_blocks = (uint32_t)blocks;
+        gp.out = nullptr;
+        gp.ldo = (long long)Q.N;
+        gp.out_batch_stride = (long long)(Q.M * Q.N);
+        gp.bias = nullptr; gp.bias_mode = 0; gp.act = kActIdentity;
+        gp.out_vec_ok = (Q.N % 4 == 0);
+        gp.out_tma = 0;
+    }
+    return cudaSuccess;
+}
+
+// Points a split-K launch at its workspace: the partial-sum kernel's output pointer and
+// output tensor map, and the reduce pass' input.
+cudaError_t bind_workspace(Prepared& pr, void* ws)
+{
+    GemmParams& gp = pr.gp;
+    gp.out = ws;
+    pr.rp.ws = static_cast<const float*>(ws);
+    gp.out_tma = 0;
+    if (gp.out_vec_ok && gp.N > 1) {
+        cuuint64_t gdim[3] = {gp.N, gp.M, (cuuint64_t)gp.batch * pr.splits};
+        cuuint64_t gstride[2] = {(cuuint64_t)gp.N * 4, (cuuint64_t)gp.M * gp.N * 4};
+        cuuint32_t box[3] = {32, 32, 1}, estr[3] = {1, 1, 1};
+        if (g_encode(&pr.mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ws, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            gp.out_tma = 1;
+    }
+    pr.ws_bound = ws;
+    return cudaSuccess;
+}
+
+// Workspaces of split-K launches: one buffer per (device, stream), grown on demand, kept until
+// the process exits.  Kernels of one stream run in order, so a stream never races with itself.
+struct Workspace { int device; cudaStream_t stream; void* ptr; size_t bytes; };
+std::mutex g_ws_mutex;
+std::vector<Workspace> g_workspaces;
+
+cudaError_t workspace_for(int device, cudaStream_t stream, size_t bytes, void** out)
+{
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    for (Workspace& w : g_workspaces) {
+        if (w.device != device || w.stream != stream) continue;
+        if (w.bytes < bytes) {
+            cudaError_t e = cudaStreamSynchronize(stream);     // the old buffer may still be in use
+            if (e != cudaSuccess) return e;
+            cudaFree(w.ptr);
+            w.ptr = nullptr; w.bytes = 0;
+            e = cudaMalloc(&w.ptr, bytes);
+            if (e != cudaSuccess) return e;
+            w.bytes = bytes;
+        }
+        *out = w.ptr;
+        return cudaSuccess;
+    }
+    Workspace w{device, stream, nullptr, 0};
+    cudaError_t e = cudaMalloc(&w.ptr, bytes);
+    if (e != cudaSuccess) return e;
+    w.bytes = bytes;
+    g_workspaces.push_back(w);
+    *out = w.ptr;
     return cudaSuccess;
 }
 
@@ -600,10 +733,44 @@ cudaError_t prepare_simt(const Plan& plan, Prepared& pr)
     return cudaSuccess;
 }
 
-cudaError_t launch_prepared(const Prepared& pr, cudaStream_t stream)
+cudaError_t launch_reduce(const Prepared& pr, cudaStream_t stream)
+{
+    const ReduceParams& rp = pr.rp;
+    const unsigned blocks = pr.reduce_blocks;
+    switch (pr.type) {
+    case real32F:
+        if (pr.reduce_vec == 4) splitk_reduce_kernel<float, 4><<<blocks, 256, 0, stream>>>(rp);
+        else                    splitk_reduce_kernel<float, 1><<<blocks, 256, 0, stream>>>(rp);
+        break;
+    case real16F:
+        if (pr.reduce_vec == 4) splitk_reduce_kernel<__half, 4><<<blocks, 256, 0, stream>>>(rp);
+        else                    splitk_reduce_kernel<__half, 1><<<blocks, 256, 0, stream>>>(rp);
+        break;
+    default:
+        if (pr.reduce_vec == 4) splitk_reduce_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>(rp);
+        else                    splitk_reduce_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, stream>>>(rp);
+        break;
+    }
+    return cudaGetLastError();
+}
+
+// `pr` is mutable because a split-K launch may have to re-point it at a new workspace.
+cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
 {
     cudaError_t e;
     const uint32_t bn = pr.bn;
+    if (pr.splits > 1) {
+        int dev = 0;
+        e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        void* ws = nullptr;
+        e = workspace_for(dev, stream, pr.ws_bytes, &ws);
+        if (e != cudaSuccess) return e;
+        if (ws != pr.ws_bound) {
+            e = bind_workspace(pr, ws);
+            if (e != cudaSuccess) return e;
+        }
+    }
     switch (pr.kernel) {
     case srtMatmulKernelSimt:
         switch (pr.type) {
@@ -626,14 +793,27 @@ cudaError_t launch_prepared(const Prepared& pr, cudaStream_t stream)
         }
         break;
     default:
-        switch (pr.type) {
-        case real32F: e = launch_tc_bn<float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
-        case real16F: e = launch_tc_bn<__half>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
-        default: e = launch_tc_bn<__nv_bfloat16>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+        if (pr.splits > 1) {
+            switch (pr.type) {
+            case real32F: e = launch_tc_bn<float, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+            case real16F: e = launch_tc_bn<__half, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+            default: e = launch_tc_bn<__nv_bfloat16, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+            }
+        } else {
+            switch (pr.type) {
+            case real32F: e = launch_tc_bn<float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+            case real16F: e = launch_tc_bn<__half>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+            default: e = launch_tc_bn<__nv_bfloat16>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream); break;
+            }
         }
         break;
     }
-    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (e != cudaSuccess) return e;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (pr.splits > 1) {
+        e = launch_reduce(pr, stream);
+        if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
     return e;
 }
 
@@ -643,7 +823,7 @@ cudaError_t launch_prepared(const Prepared& pr, cudaStream_t stream)
 // per host thread -- a SwiftRT queue is used by one thread only -- so it needs no lock.
 struct CallKey {
     Problem P;
-    int32_t force, tile_n, stages, max_ctas;
+    int32_t force, tile_n, stages, max_ctas, split_k;
     int32_t device;
 };
 
@@ -698,6 +878,7 @@ cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aD
     key.tile_n = g_tuning.tile_n.load(std::memory_order_relaxed);
     key.stages = g_tuning.stages.load(std::memory_order_relaxed);
     key.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
+    key.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
     key.device = dev;
     if (!t_cache) t_cache = new CallCache();
     const int slot = (int)(hash_key(key) % kCallCacheSize);
@@ -752,6 +933,13 @@ cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stage
     g_tuning.tile_n = tileN;
     g_tuning.stages = stages;
     g_tuning.max_ctas = maxCtas;
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulSetSplitK(int32_t splits)
+{
+    if (splits < 0 || splits > 64) return fail(cudaErrorInvalidValue, "splits must be 0 (automatic) or 1..64");
+    g_tuning.split_k = splits;
     return cudaSuccess;
 }
 

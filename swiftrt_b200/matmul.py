@@ -228,6 +228,13 @@ def set_tuning(force_kernel: int = 0, tile_n: int = 0, stages: int = 0, max_ctas
         raise MatmulError(rc, _lib.last_error())
 
 
+def set_split_k(splits: int = 0) -> None:
+    """0 = automatic, 1 = never, n > 1 = cut the reduction into up to n parts (srtMatmulSetSplitK)."""
+    rc = lib.srtMatmulSetSplitK(splits)
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+
+
 def check_status(device=None) -> int:
     """Synchronises the current stream and returns the tensor-core kernels' status word
     (0 = every pipeline wait completed)."""

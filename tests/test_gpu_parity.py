@@ -30,7 +30,9 @@ def srt():
 @pytest.fixture(autouse=True)
 def _reset_tuning_and_check_status(srt):
     srt.set_tuning(0, 0, 0, 0)
+    srt.set_split_k(0)
     yield
+    srt.set_split_k(0)
     assert srt.check_status() == 0, "a pipeline wait of the tensor-core kernel timed out"
     srt.set_tuning(0, 0, 0, 0)
 
@@ -220,7 +222,8 @@ def test_float32_kernel_choice_follows_size_and_k(srt):
     a, b = torch.zeros((8192, 1024), device=dev), torch.zeros((1024, 256), device=dev)
     assert srt.query_plan(a, b, torch.zeros((8192, 256), device=dev))["kernel"] == SPLIT
     a, b = torch.zeros((1024, 4096), device=dev), torch.zeros((4096, 256), device=dev)
-    assert srt.query_plan(a, b, torch.zeros((1024, 256), device=dev))["kernel"] == SIMT    # K > 2048
+    plan = srt.query_plan(a, b, torch.zeros((1024, 256), device=dev))
+    assert plan["kernel"] == SPLIT and plan["splitK"] >= 2                                 # K > 2048
 
 
 @pytest.mark.parametrize("kernel", [TC, PAIR])
@@ -283,6 +286,68 @@ def test_identity_and_permutation_products_are_exact_at_full_size(srt):
     assert torch.equal(c, a[:, perm])
     c = srt.matmul(eye, a, False, True)                          # I . A^T
     assert torch.equal(c, a.t())
+
+
+# ------------------------------------------------------------------ split-K
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("M,N,K,batch,ta,tb,splits", [
+    (256, 256, 4096, 0, False, False, 4), (300, 200, 1000, 0, False, False, 3), (130, 203, 1024, 0, False, True, 8),
+    (128, 64, 2048, 3, True, False, 2), (64, 512, 8192, 0, False, True, 0), (128, 128, 8192, 0, False, False, 0)])
+def test_split_k_sixteen_bit(srt, oracle, dtype, M, N, K, batch, ta, tb, splits):
+    """Reduction cut into parts (forced, or chosen automatically for few tiles and a long K):
+    fp32 partial sums + reduce pass must give the same result within tolerance."""
+    srt.set_tuning(TC, 0, 0, 0)
+    srt.set_split_k(splits)
+    rng = np.random.default_rng(M + 3 * N + 7 * K + dtype + 11)
+    ash, bsh = _shapes(M, N, K, ta, tb, batch)
+    a, b = random_bits(oracle, rng, ash, dtype), random_bits(oracle, rng, bsh, dtype)
+    bias = random_bits(oracle, rng, (N,), dtype)
+    ref = oracle.matmul(a, b, dtype, ta, tb, bias=bias, activation="relu")
+    da, db, dbias = to_dev(a, dtype), to_dev(b, dtype), to_dev(bias, dtype)
+    c = srt.matmul(da, db, ta, tb, bias=dbias, activation=srt.ActivationType.relu)
+    plan = srt.query_plan(da, db, c, ta, tb)
+    assert plan["kernel"] == TC and plan["splitK"] > 1
+    assert plan["workspaceBytes"] == plan["splitK"] * max(batch, 1) * M * N * 4
+    got = from_dev(c, dtype)
+    assert oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype)) <= 2e-3
+
+
+def test_split_k_col_order_output_and_strided_view(srt, oracle):
+    srt.set_tuning(TC, 0, 0, 0)
+    srt.set_split_k(4)
+    rng = np.random.default_rng(51)
+    a, b = random_bits(oracle, rng, (264, 2048), BF16), random_bits(oracle, rng, (2048, 136), BF16)
+    bias = random_bits(oracle, rng, (136,), BF16)
+    ref = oracle.matmul(a, b, BF16, bias=bias, activation="relu")
+    a_col = to_dev(np.asfortranarray(a), BF16)
+    c = srt.matmul(a_col, to_dev(b, BF16), bias=to_dev(bias, BF16), activation=srt.ActivationType.relu)
+    plan = srt.query_plan(a_col, to_dev(b, BF16), c)
+    assert plan["swapped"] == 1 and plan["splitK"] > 1 and c.stride() == (1, 264)
+    assert oracle.rel_frobenius(oracle.decode(from_dev(c, BF16), BF16), oracle.decode(ref, BF16)) <= 2e-3
+    # a strided output view: only the view is written
+    canvas = torch.full((300, 512), 7.0, dtype=torch.bfloat16, device="cuda:0")
+    view = canvas[10:274, 64:200]
+    srt.matmul_into(view, to_dev(a, BF16), False, to_dev(b, BF16), False)
+    ref2 = oracle.matmul(a, b, BF16)
+    assert oracle.rel_frobenius(oracle.decode(from_dev(view, BF16), BF16), oracle.decode(ref2, BF16)) <= 2e-3
+    mask = torch.ones_like(canvas, dtype=torch.bool)
+    mask[10:274, 64:200] = False
+    assert bool((canvas[mask] == 7.0).all())
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", [(512, 256, 4096, False, False), (256, 384, 8192, False, True), (1000, 520, 2056, True, False)])
+def test_float32_large_k_uses_split_k_and_holds_tolerance(srt, oracle, M, N, K, ta, tb):
+    """Beyond K = 2048 the 3 x TF32 kernel sums chunks of 2048 separately (accumulator truncation
+    grows with K); the result must stay within 1e-5 for any K."""
+    rng = np.random.default_rng(M + N + K)
+    ash, bsh = _shapes(M, N, K, ta, tb)
+    a, b = random_bits(oracle, rng, ash, F32), random_bits(oracle, rng, bsh, F32)
+    ref = oracle.matmul(a, b, F32, ta, tb)
+    da, db = to_dev(a, F32), to_dev(b, F32)
+    c = srt.matmul(da, db, ta, tb)
+    plan = srt.query_plan(da, db, c, ta, tb)
+    assert plan["kernel"] == SPLIT and plan["splitK"] >= -(-K // 2048)
+    assert oracle.rel_frobenius(from_dev(c, F32), ref) <= TOL[F32]
 
 
 # ------------------------------------------------------------------ the five named configurations
