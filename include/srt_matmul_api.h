@@ -180,6 +180,34 @@ cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stage
  * keeps per (device, stream) and grows on demand with cudaMalloc. */
 cudaError_t srtMatmulSetSplitK(int32_t splits);
 
+/* srtMatmulNoAlloc: srtMatmul for callers that must not allocate device memory.
+ *
+ * This entry point has no counterpart in the reference.  It exists for hosts that cannot call
+ * cudaMalloc at the point where the product is needed: code that runs inside a region where the
+ * allocator is locked or forbidden (a real-time loop, a callback from another runtime that owns
+ * all device memory, a process whose memory pool was handed out in full at start-up).  srtMatmul
+ * itself allocates only for split-K products, whose fp32 partial sums need scratch; here that
+ * scratch is a 16 MiB array compiled into the library instead of a cudaMalloc'ed workspace, and
+ * the call performs no cudaMalloc, cudaFree or other allocating call.
+ *
+ * Same arguments, result and kernels as srtMatmul.  Differences:
+ *  - a split-K product whose partial sums (splitK x batch x M x N x 4 bytes, see
+ *    srtMatmulQueryPlan) exceed 16 MiB is refused with cudaErrorInvalidValue and an explanatory
+ *    srtMatmulGetLastErrorString(); nothing is launched.  Products that are not split need no
+ *    scratch and are never refused for their size;
+ *  - the first call on a device looks up the scratch array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call outside any stream
+ *    capture;
+ *  - all calls on a device share the one array: two split-K calls that overlap on the GPU (on
+ *    different streams) corrupt each other's partial sums.  Calls on one stream are safe.  The
+ *    array keeps what the last call wrote; no call depends on its previous contents.
+ */
+cudaError_t srtMatmulNoAlloc(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    void* out, const srtTensorDescriptor* oDesc,
+    cudaStream_t stream);
+
 /* Device-side status of the last tensor-core launches on the current device: 0 = all
  * pipeline waits completed; non-zero = a bounded wait gave up (the code says which) and
  * the result of that launch is invalid.  Synchronises `stream` and resets the status. */

@@ -960,6 +960,83 @@ cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status)
     return cudaSuccess;
 }
 
+// ------------------------------------------------------------------ srtMatmulNoAlloc
+// Scratch of the entry point below.  It is part of the library image: every device that loads
+// the library carries these 16 MiB from then until the process ends, whether or not the entry
+// point is ever called.  In host code the name is only a handle for cudaGetSymbolAddress; the
+// device address it yields is what the kernels receive.
+constexpr size_t kNoAllocScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[kNoAllocScratchBytes];
+
+std::mutex g_no_alloc_mutex;
+void* g_no_alloc_ptr[64] = {};
+
+// Device address of the scratch array on the current device, looked up once per device.
+cudaError_t no_alloc_scratch(int dev, void** out)
+{
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (dev < 0 || dev >= 64) return fail(cudaErrorInvalidDevice, "device ordinal %d out of range", dev);
+    if (!g_no_alloc_ptr[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+        if (e != cudaSuccess) return fail(e, "cudaGetSymbolAddress of the static scratch failed: %s", cudaGetErrorString(e));
+        g_no_alloc_ptr[dev] = ptr;
+    }
+    *out = g_no_alloc_ptr[dev];
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulNoAlloc(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                             const srtTensorDescriptor* bDesc, bool transB, void* out, const srtTensorDescriptor* oDesc,
+                             cudaStream_t stream)
+{
+    Problem P;
+    memset(&P, 0, sizeof P);
+    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out, oDesc, P);
+    if (e != cudaSuccess) return e;
+    Plan plan;
+    e = plan_for(P, plan);
+    if (e != cudaSuccess) return e;
+    Prepared pr;
+    e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, pr) : prepare_tc(plan, pr);
+    if (e != cudaSuccess) return e;
+    if (pr.splits <= 1) return launch_prepared(pr, stream);      // this plan has no scratch to place
+
+    if (pr.ws_bytes > kNoAllocScratchBytes)
+        return fail(cudaErrorInvalidValue,
+                    "srtMatmulNoAlloc: this product needs %zu bytes of scratch (%u partial results of %llu x %llu x %llu "
+                    "fp32 values) but the static scratch holds %zu; use srtMatmul, or srtMatmulSetSplitK(1)",
+                    pr.ws_bytes, pr.splits, (unsigned long long)plan.Q.batch, (unsigned long long)plan.Q.M,
+                    (unsigned long long)plan.Q.N, kNoAllocScratchBytes);
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    void* scratch = nullptr;
+    e = no_alloc_scratch(dev, &scratch);
+    if (e != cudaSuccess) return e;
+    e = bind_workspace(pr, scratch);
+    if (e != cudaSuccess) return e;
+    // first pass: every element of every partial-sum slice is written before the second pass reads
+    // it, so nothing in the scratch has to start at zero and what an earlier call left is harmless
+    const uint32_t bn = pr.bn;
+    if (pr.kernel == srtMatmulKernelTcgen05Split) {
+        e = bn == 64    ? launch_split<64>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream)
+            : bn == 128 ? launch_split<128>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream)
+                        : launch_split<256>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
+    } else if (pr.type == real16F) {
+        e = launch_tc_bn<__half, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
+    } else if (pr.type == real16BF) {
+        e = launch_tc_bn<__nv_bfloat16, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
+    } else {
+        e = launch_tc_bn<float, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
+    }
+    if (e != cudaSuccess) return e;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    e = launch_reduce(pr, stream);
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
 #ifdef SRT_TRACE
 cudaError_t srtMatmulDebugTrace(long long* dst) { return cudaMemcpyFromSymbol(dst, srt::g_trace, sizeof(long long) * 8192); }
 #endif
