@@ -664,13 +664,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // in fp32, at most 13 significant bits), and the product is accumulated as
 //     hi_a.hi_b + hi_a.lo_b + lo_a.hi_b          (lo_a.lo_b ~ 2^-22 |a.b| is dropped)
 // in two fp32 TMEM accumulators (dominant products / correction terms) that the epilogue sums.
-// TMA delivers the raw fp32 tile; four transform warps rewrite
-// it in place as hi and write lo to a second buffer with the same (swizzled) layout, so the
-// same shared-memory descriptors address both.
-//   warp 0 producer, warp 1 MMA issuer, warps 2-5 epilogue, warps 6-9 transform.
-//   full[s]  TMA bytes landed -> transform warps;  ready[s] (count 4) transform done -> MMA;
+// TMA delivers the raw fp32 tile, which serves as hi unchanged: the MMA ignores the low 13
+// mantissa bits (truncation, confirmed by the 1e-5 parity tests -- rounding would show as 5e-4).
+// Four transform warps write lo to a second buffer with the same (swizzled) layout, so the same
+// shared-memory descriptors address both.
+//   warp 0 producer, warp 1 MMA issuer, warps 2-5 epilogue, warps 6-13 transform.
+//   full[s]  TMA bytes landed -> transform warps;  ready[s] (count 8) transform done -> MMA;
 //   empty[s] MMAs done -> producer.
-constexpr uint32_t kSplitThreads = 320;
+constexpr uint32_t kSplitTransformWarps = 8;   // two per scheduler: one warp alone issues too slowly
+constexpr uint32_t kSplitThreads = (6 + kSplitTransformWarps) * 32;
 
 template <uint32_t BN>
 __global__ void __launch_bounds__(kSplitThreads, 1)
@@ -708,7 +710,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
         abort_flag = 0;
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
-            mbar_init(smem_u32(&ready_bar[s]), 4);
+            mbar_init(smem_u32(&ready_bar[s]), kSplitTransformWarps);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (uint32_t i = 0; i < 2; ++i) {
@@ -836,7 +838,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
     } else {
         // ------------------------------------------------------------------ hi / lo transform
-        const uint32_t t = threadIdx.x - 6 * 32;              // 0 .. 127
+        const uint32_t t = threadIdx.x - 6 * 32;              // 0 .. 32 * kSplitTransformWarps - 1
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -845,7 +847,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
                 const uint32_t hi_base = smem_base + stage * kStageBytes;
 #pragma unroll 4
-                for (uint32_t off = t * 16; off < kHalfBytes; off += 128 * 16) {
+                for (uint32_t off = t * 16; off < kHalfBytes; off += kSplitTransformWarps * 32 * 16) {
                     uint32_t x0, x1, x2, x3;
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                  : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(hi_base + off));
@@ -858,8 +860,6 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         // infinities and NaNs stay in hi alone
                         l[j] = ((x[j] & 0x7f800000u) == 0x7f800000u) ? 0u : __float_as_uint(lo);
                     }
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(hi_base + off), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(hi_base + kHalfBytes + off), "r"(l[0]), "r"(l[1]), "r"(l[2]), "r"(l[3]) : "memory");
                 }

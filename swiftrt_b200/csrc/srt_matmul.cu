@@ -288,7 +288,11 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     // Tile choice by a small cost model: time ~ waves x (time of one tile).  A 128 x BN tile costs
     // BN / efficiency(BN) (narrow MMAs re-read A more often per flop); a CTA pair's 256 x BN tile
     // costs about the same as one CTA's 128 x BN tile and fills the device with half as many tiles.
-    auto tile_cost = [](uint32_t n) { return n == 256 ? 256.0 : n == 128 ? 171.0 : 128.0; };
+    // (the 3 x TF32 kernel gets a third pipeline stage at BN = 128, which makes its narrow tile cheaper)
+    auto tile_cost = [&](uint32_t n) {
+        if (split) return n == 256 ? 256.0 : n == 128 ? 140.0 : 110.0;
+        return n == 256 ? 256.0 : n == 128 ? 171.0 : 128.0;
+    };
     auto waves = [](uint64_t tiles, uint64_t units) { return (double)((tiles + units - 1) / units); };
     auto tiles_for = [&](uint32_t tm, uint32_t n) { return ((Q.M + tm - 1) / tm) * ((Q.N + n - 1) / n) * Q.batch; };
     const uint64_t sms = (uint64_t)dev.sms;
