@@ -26,58 +26,74 @@ struct SimtParams {
     uint32_t a_k_fast, b_n_fast; // which index the loader walks fastest (coalescing only)
 };
 
-constexpr int kSimtTile = 64;
+constexpr int kSimtTile = 64;       // default tile edge; 32 when a 64-tile grid would leave most SMs idle
 constexpr int kSimtK = 16;
 
-template <typename T>
+// TILE x TILE outputs per 256-thread block, (TILE/16)^2 per thread.  The global loads of k-tile
+// t + 1 are issued into registers before k-tile t is multiplied, so their latency overlaps the math.
+template <typename T, int TILE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const SimtParams p)
 {
-    __shared__ float As[kSimtK][kSimtTile + 1];
-    __shared__ float Bs[kSimtK][kSimtTile + 1];
+    constexpr int R = TILE / 16;                   // outputs per thread along each axis
+    constexpr int LD = TILE * kSimtK / 256;        // elements of each operand tile a thread loads
+    __shared__ float As[kSimtK][TILE + 1];
+    __shared__ float Bs[kSimtK][TILE + 1];
 
     const uint32_t tid = threadIdx.x;
     const uint32_t tx = tid & 15, ty = tid >> 4;
     const uint32_t batch = blockIdx.z;
-    const uint32_t m0 = blockIdx.y * kSimtTile, n0 = blockIdx.x * kSimtTile;
+    const uint32_t m0 = blockIdx.y * TILE, n0 = blockIdx.x * TILE;
     const T* A = static_cast<const T*>(p.a) + static_cast<long long>(batch) * p.a_b;
     const T* B = static_cast<const T*>(p.b) + static_cast<long long>(batch) * p.b_b;
 
-    float acc[4][4];
+    float acc[R][R];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < R; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < R; ++j) acc[i][j] = 0.0f;
 
+    // element e of a tile -> (row/column, k) so that consecutive threads walk the contiguous index
+    uint32_t a_mm[LD], a_kk[LD], b_nn[LD], b_kk[LD];
+#pragma unroll
+    for (int i = 0; i < LD; ++i) {
+        const uint32_t e = tid + i * 256;
+        if (p.a_k_fast) { a_kk[i] = e & 15; a_mm[i] = e >> 4; } else { a_mm[i] = e % TILE; a_kk[i] = e / TILE; }
+        if (p.b_n_fast) { b_nn[i] = e % TILE; b_kk[i] = e / TILE; } else { b_kk[i] = e & 15; b_nn[i] = e >> 4; }
+    }
+    auto fetch = [&](uint32_t k0, float (&ra)[LD], float (&rb)[LD]) {
+#pragma unroll
+        for (int i = 0; i < LD; ++i) {
+            const uint32_t gm = m0 + a_mm[i], gk = k0 + a_kk[i];
+            ra[i] = (gm < p.M && gk < p.K)
+                        ? to_float<T>(A[static_cast<long long>(gm) * p.a_m + static_cast<long long>(gk) * p.a_k]) : 0.0f;
+            const uint32_t gn = n0 + b_nn[i], gk2 = k0 + b_kk[i];
+            rb[i] = (gn < p.N && gk2 < p.K)
+                        ? to_float<T>(B[static_cast<long long>(gk2) * p.b_k + static_cast<long long>(gn) * p.b_n]) : 0.0f;
+        }
+    };
+
+    float ra[LD], rb[LD];
+    fetch(0, ra, rb);
     for (uint32_t k0 = 0; k0 < p.K; k0 += kSimtK) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t e = tid + i * 256;          // 1024 elements per tile
-            uint32_t mm, kk;
-            if (p.a_k_fast) { kk = e & 15; mm = e >> 4; } else { mm = e & 63; kk = e >> 6; }
-            const uint32_t gm = m0 + mm, gk = k0 + kk;
-            As[kk][mm] = (gm < p.M && gk < p.K)
-                             ? to_float<T>(A[static_cast<long long>(gm) * p.a_m + static_cast<long long>(gk) * p.a_k])
-                             : 0.0f;
-            uint32_t nn, kb;
-            if (p.b_n_fast) { nn = e & 63; kb = e >> 6; } else { kb = e & 15; nn = e >> 4; }
-            const uint32_t gn = n0 + nn, gk2 = k0 + kb;
-            Bs[kb][nn] = (gn < p.N && gk2 < p.K)
-                             ? to_float<T>(B[static_cast<long long>(gk2) * p.b_k + static_cast<long long>(gn) * p.b_n])
-                             : 0.0f;
+        for (int i = 0; i < LD; ++i) {
+            As[a_kk[i]][a_mm[i]] = ra[i];
+            Bs[b_kk[i]][b_nn[i]] = rb[i];
         }
         __syncthreads();
+        if (k0 + kSimtK < p.K) fetch(k0 + kSimtK, ra, rb);
         const uint32_t kmax = min(static_cast<uint32_t>(kSimtK), p.K - k0);
         for (uint32_t kk = 0; kk < kmax; ++kk) {
-            float av[4], bv[4];
+            float av[R], bv[R];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) av[i] = As[kk][ty + 16 * i];
+            for (int i = 0; i < R; ++i) av[i] = As[kk][ty + 16 * i];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx + 16 * j];
+            for (int j = 0; j < R; ++j) bv[j] = Bs[kk][tx + 16 * j];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < R; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+                for (int j = 0; j < R; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
         }
         __syncthreads();
     }
@@ -85,11 +101,11 @@ gemm_simt_kernel(const SimtParams p)
     T* O = static_cast<T*>(p.out) + static_cast<long long>(batch) * p.o_b;
     const T* bias = static_cast<const T*>(p.bias);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < R; ++i) {
         const uint32_t gm = m0 + ty + 16 * i;
         if (gm >= p.M) continue;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < R; ++j) {
             const uint32_t gn = n0 + tx + 16 * j;
             if (gn >= p.N) continue;
             float v = acc[i][j];

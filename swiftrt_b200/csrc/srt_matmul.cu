@@ -217,6 +217,13 @@ TcOperand classify(const char* ptr, uint64_t rows, uint64_t K, uint64_t batch, l
     return r;
 }
 
+// 64 x 64 tiles unless such a grid would leave most SMs idle: then 32 x 32 (4x the blocks)
+uint32_t simt_tile_for(uint64_t M, uint64_t N, uint64_t batch, int sms)
+{
+    const uint64_t t64 = ((M + 63) / 64) * ((N + 63) / 64) * batch;
+    return t64 < (uint64_t)sms ? 32u : 64u;
+}
+
 struct Plan {
     srtMatmulPlan pub;
     bool swapped = false;
@@ -274,9 +281,10 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         plan.swapped = false;
         plan.bias_mode = P.bias ? 1 : 0;
         plan.pub.kernel = srtMatmulKernelSimt;
-        plan.pub.tileM = kSimtTile; plan.pub.tileN = kSimtTile; plan.pub.tileK = kSimtK;
+        const uint32_t st = simt_tile_for(P.M, P.N, P.batch, dev.sms);
+        plan.pub.tileM = (int32_t)st; plan.pub.tileN = (int32_t)st; plan.pub.tileK = kSimtK;
         plan.pub.stages = 1;
-        const uint64_t tm = (P.M + kSimtTile - 1) / kSimtTile, tn = (P.N + kSimtTile - 1) / kSimtTile;
+        const uint64_t tm = (P.M + st - 1) / st, tn = (P.N + st - 1) / st;
         plan.pub.tiles = (int32_t)(tm * tn * P.batch);
         plan.pub.ctas = plan.pub.tiles;
         plan.pub.dynamicSmemBytes = 0;
@@ -367,9 +375,10 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
             if (split3 && Q.K > 2048 && want_split == 0) {       // cannot hold the tolerance without it
                 plan.Q = P; plan.swapped = false; plan.bias_mode = P.bias ? 1 : 0;
                 plan.pub.kernel = srtMatmulKernelSimt;
-                plan.pub.tileM = kSimtTile; plan.pub.tileN = kSimtTile; plan.pub.tileK = kSimtK;
+                const uint32_t st = simt_tile_for(P.M, P.N, P.batch, dev.sms);
+                plan.pub.tileM = (int32_t)st; plan.pub.tileN = (int32_t)st; plan.pub.tileK = kSimtK;
                 plan.pub.stages = 1;
-                plan.pub.tiles = (int32_t)(((P.M + kSimtTile - 1) / kSimtTile) * ((P.N + kSimtTile - 1) / kSimtTile) * P.batch);
+                plan.pub.tiles = (int32_t)(((P.M + st - 1) / st) * ((P.N + st - 1) / st) * P.batch);
                 plan.pub.ctas = plan.pub.tiles;
                 return;
             }
@@ -558,6 +567,7 @@ struct Prepared {
     GemmParams gp;
     SimtParams sp;
     dim3 grid;
+    uint32_t simt_tile = kSimtTile;
     // split-K only
     uint32_t splits = 1;
     size_t ws_bytes = 0;
@@ -729,7 +739,9 @@ cudaError_t prepare_simt(const Plan& plan, Prepared& pr)
     sp.act = P.act;
     sp.a_k_fast = (P.a_k == 1) || (P.a_m != 1);
     sp.b_n_fast = (P.b_n == 1) || (P.b_k != 1);
-    const uint64_t tm = (P.M + kSimtTile - 1) / kSimtTile, tn = (P.N + kSimtTile - 1) / kSimtTile;
+    const uint32_t st = (uint32_t)plan.pub.tileM;
+    pr.simt_tile = st;
+    const uint64_t tm = (P.M + st - 1) / st, tn = (P.N + st - 1) / st;
     if (tm > 65535) return fail(cudaErrorNotSupported, "strided kernel: more than 65535 row tiles");
     pr.grid = dim3((unsigned)tn, (unsigned)tm, (unsigned)P.batch);
     pr.kernel = srtMatmulKernelSimt;
@@ -778,9 +790,18 @@ cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
     switch (pr.kernel) {
     case srtMatmulKernelSimt:
         switch (pr.type) {
-        case real32F: gemm_simt_kernel<float><<<pr.grid, 256, 0, stream>>>(pr.sp); break;
-        case real16F: gemm_simt_kernel<__half><<<pr.grid, 256, 0, stream>>>(pr.sp); break;
-        default: gemm_simt_kernel<__nv_bfloat16><<<pr.grid, 256, 0, stream>>>(pr.sp); break;
+        case real32F:
+            if (pr.simt_tile == 32) gemm_simt_kernel<float, 32><<<pr.grid, 256, 0, stream>>>(pr.sp);
+            else                    gemm_simt_kernel<float, 64><<<pr.grid, 256, 0, stream>>>(pr.sp);
+            break;
+        case real16F:
+            if (pr.simt_tile == 32) gemm_simt_kernel<__half, 32><<<pr.grid, 256, 0, stream>>>(pr.sp);
+            else                    gemm_simt_kernel<__half, 64><<<pr.grid, 256, 0, stream>>>(pr.sp);
+            break;
+        default:
+            if (pr.simt_tile == 32) gemm_simt_kernel<__nv_bfloat16, 32><<<pr.grid, 256, 0, stream>>>(pr.sp);
+            else                    gemm_simt_kernel<__nv_bfloat16, 64><<<pr.grid, 256, 0, stream>>>(pr.sp);
+            break;
         }
         e = cudaGetLastError();
         break;
