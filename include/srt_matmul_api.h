@@ -132,6 +132,28 @@ cudaError_t srtMatmulBiasActivation(
     void* out, const srtTensorDescriptor* oDesc,
     cudaStream_t stream);
 
+/* srtBiasActivationBackward: the backward of the fused epilogue of srtMatmulBiasActivation.
+ *     dz[.., m, n] = dy[.., m, n] * activation'(y[.., m, n])          (one rounding)
+ *     dbias[n]     = sum over batch and rows of dz[.., m, n]          (fp32 sum, one rounding)
+ * Supplies the derivatives that the reference leaves as fatalError() -- _vjpMatmul with bias
+ * (Sources/SwiftRTCore/differentiable/MathDerivatives.swift:520-554) -- in the form the reference's
+ * cuDNN activation backward uses (derivative from the forward OUTPUT y,
+ * platform/cuda/layers/CudaActivation.swift:101-127).  With dz the remaining gradients are two
+ * srtMatmul calls with transpose flags, exactly as matmulGradients composes them
+ * (MathDerivatives.swift:460-482): dX = dz . W^T, dW = X^T . dz.
+ * dy, y, dz: rank 2 [M x N] or rank 3 [batch x M x N], same type and shape, any strides.  y may
+ * be NULL for srtActivationIdentity; dz or dbias may be NULL when not wanted; dz may alias dy.
+ * identity, relu, sigmoid and tanh are computed; gelu and the coefficient activations return
+ * cudaErrorNotSupported.  The column sums use the library's per-(device, stream) workspace.
+ */
+cudaError_t srtBiasActivationBackward(
+    const void* dy, const srtTensorDescriptor* dyDesc,
+    const void* y, const srtTensorDescriptor* yDesc,
+    srtActivationType activation,
+    void* dz, const srtTensorDescriptor* dzDesc,
+    void* dbias, const srtTensorDescriptor* dbiasDesc,
+    cudaStream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * Plan query and tuning knobs.  Stand in for MatmulAlgorithm.query / .search
  * (platform/cuda/cublaslt/MatmulAlgorithmSearch.swift:51-100, 128-216), MatmulTile /

@@ -381,6 +381,53 @@ int oracle_bias_activation_unfused(int dtype, void* y, size_t rows, size_t cols,
     return 0;
 }
 
+/* ---------------------------------------------------------------- Dense backward helpers
+ * The reference leaves the bias / activation derivatives of matmul unimplemented
+ * (Sources/SwiftRTCore/differentiable/MathDerivatives.swift:520-554 are fatalError()), so
+ * there is nothing executable to follow; this restates what composing the reference's own
+ * pieces would compute:
+ *   dz = dy * act'(y)   elementwise in the Value type, stored in the element type, with the
+ *        derivative written in terms of the forward OUTPUT y, as cuDNN's activation backward
+ *        does (platform/cuda/layers/CudaActivation.swift:101-127): relu: y > 0 ? dy : 0,
+ *        sigmoid: dy*y*(1-y), tanh: dy*(1-y*y), identity: dy;
+ *   dbias[n] = sum over rows m = 0..M-1, in order, of dz[m][n]   -- cpu_sum along axis 0
+ *        (platform/cpu/functions/CpuReduce.swift:69-96).  The reference's loop keeps the running
+ *        sum in the OUTPUT tensor, i.e. rounds it to the element type after every row
+ *        (`stepwise` = 1); with `stepwise` = 0 the sum is kept in fp32 and rounded once, which is
+ *        the graded variant (same choice as fp32 accumulation for the 16-bit matmul).
+ * dy, y, dz are dense row-major [M x N]; dbias has N elements.  Returns 0.
+ */
+int oracle_bias_activation_backward(int dtype, const void* dy, const void* y, size_t M, size_t N, int act,
+                                    void* dz, void* dbias, int stepwise)
+{
+    if (dtype != ORACLE_F32 && dtype != ORACLE_F16 && dtype != ORACLE_BF16) return -2;
+    float* acc = (float*)malloc(sizeof(float) * (N ? N : 1));
+    for (size_t n = 0; n < N; ++n) acc[n] = 0.0f;
+    for (size_t m = 0; m < M; ++m)
+        for (size_t n = 0; n < N; ++n) {
+            const float g = load_value(dtype, dy, m * N + n);
+            const float o = load_value(dtype, y, m * N + n);
+            float d;
+            switch (act) {
+            case ORACLE_ACT_RELU: d = o > 0.0f ? g : 0.0f; break;
+            case ORACLE_ACT_SIGMOID: { float t = o * (1.0f - o); d = g * t; break; }
+            case ORACLE_ACT_TANH: { float t = o * o; t = 1.0f - t; d = g * t; break; }
+            default: d = g; break;
+            }
+            store_value(dtype, dz, m * N + n, d);
+            const float stored = load_value(dtype, dz, m * N + n);
+            if (stepwise) {
+                store_value(dtype, dbias, n, m == 0 ? stored : load_value(dtype, dbias, n) + stored);
+            } else {
+                acc[n] = acc[n] + stored;
+            }
+        }
+    if (!stepwise)
+        for (size_t n = 0; n < N; ++n) store_value(dtype, dbias, n, acc[n]);
+    free(acc);
+    return 0;
+}
+
 int oracle_max_threads(void)
 {
 #ifdef _OPENMP

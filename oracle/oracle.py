@@ -48,6 +48,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_convert_to_f32.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, sz]
         L.oracle_bias_activation_unfused.argtypes = [ctypes.c_int, ctypes.c_void_p, sz, sz,
                                                      ctypes.c_void_p, ctypes.c_int]
+        L.oracle_bias_activation_backward.restype = ctypes.c_int
+        L.oracle_bias_activation_backward.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, sz, sz, ctypes.c_int,
+                                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
         L.oracle_max_threads.restype = ctypes.c_int
         _LIB = L
     return _LIB
@@ -129,6 +132,23 @@ def matmul(a: np.ndarray, b: np.ndarray, dtype: int, trans_a: bool = False, tran
     if rc != 0:
         raise ValueError(f"oracle_matmul failed with code {rc}")
     return out
+
+
+def bias_activation_backward(dy: np.ndarray, y: np.ndarray, dtype: int, activation: str = "identity",
+                             stepwise: bool = False):
+    """(dz, dbias) for dense row-major [M x N] dy and forward output y: dz = dy * act'(y),
+    dbias = column sums of dz (fp32 running sum rounded once; `stepwise` rounds after every row as
+    the reference's cpu_sum does)."""
+    dy = np.ascontiguousarray(dy)
+    y = np.ascontiguousarray(y)
+    M, N = dy.shape
+    dz = np.empty_like(dy)
+    dbias = np.zeros((N,), dtype=dy.dtype)
+    rc = lib().oracle_bias_activation_backward(dtype, dy.ctypes.data, y.ctypes.data, M, N, ACT[activation],
+                                               dz.ctypes.data, dbias.ctypes.data, int(stepwise))
+    if rc != 0:
+        raise ValueError(f"oracle_bias_activation_backward failed with code {rc}")
+    return dz, dbias
 
 
 def rel_frobenius(x: np.ndarray, ref: np.ndarray) -> float:

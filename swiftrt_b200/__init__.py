@@ -3,7 +3,7 @@
 Importing the package loads the compiled CUDA library (swiftrt_b200/libsrt_b200.so) and
 raises if it has not been built: there is no CPU or PyTorch fallback."""
 from ._lib import EXPORTS, SO  # noqa: F401  (raises ImportError when the library is missing)
-from .dense import Dense  # noqa: F401
+from .dense import Dense, bias_activation_backward  # noqa: F401
 from .matmul import (MatmulError, MatmulOp, check_status, launch_count, matmul, matmul_gradients,  # noqa: F401
                      matmul_host, matmul_into, query_plan, set_split_k, set_tuning)
 from .tensor import ActivationType, DataType, Order, empty, order_of  # noqa: F401

@@ -38,7 +38,7 @@ class MatmulPlan(ctypes.Structure):
 
 
 # every symbol include/srt_matmul_api.h declares
-EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc",
+EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString"]
 
 if not os.path.exists(SO):
@@ -52,6 +52,8 @@ _D = ctypes.POINTER(TensorDescriptor)
 _P = ctypes.c_void_p
 lib.srtMatmul.restype = ctypes.c_int
 lib.srtMatmul.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, _P]
+lib.srtBiasActivationBackward.restype = ctypes.c_int
+lib.srtBiasActivationBackward.argtypes = [_P, _D, _P, _D, ctypes.c_int, _P, _D, _P, _D, _P]
 lib.srtMatmulNoAlloc.restype = ctypes.c_int
 lib.srtMatmulNoAlloc.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, _P]
 lib.srtMatmulBiasActivation.restype = ctypes.c_int

@@ -1,0 +1,115 @@
+// Backward of the Dense epilogue: dz = dy * act'(y) and dbias = column sums of dz, in one pass
+// over dy and y (HBM-bound: reads 2 and writes 1 element per output element).
+//
+//   pass 1  grid (column blocks, row chunks): each block walks its rows with 8 warps, a thread
+//           owning VEC consecutive columns; dz is rounded to the element type and stored, the
+//           ROUNDED values are summed per column in fp32; the block's column sums go to
+//           partial[chunk][N] (fp32 scratch).
+//   pass 2  dbias[n] = partial[0][n] + partial[1][n] + ... in chunk order (deterministic), one
+//           rounding to the element type.
+// The derivative uses the forward OUTPUT y (relu: y > 0, sigmoid: y (1 - y), tanh: 1 - y^2),
+// as cuDNN's activation backward does in the reference
+// (Sources/SwiftRTCore/platform/cuda/layers/CudaActivation.swift:101-127).
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace srt {
+
+struct DenseBackwardParams {
+    const void* dy; const void* y; void* dz;
+    long long dy_b, dy_m, dy_n;      // element strides (batch, row, column)
+    long long y_b, y_m, y_n;
+    long long dz_b, dz_m, dz_n;
+    uint32_t M, N, batch;            // rows per batch item, columns, batch items
+    uint32_t rows_per_chunk;         // over the flattened batch * M rows
+    uint32_t act;
+    float* partial;                  // [chunks][N]
+};
+
+__device__ __forceinline__ float activation_grad(uint32_t act, float g, float o)
+{
+    switch (act) {
+    case kActRelu: return o > 0.0f ? g : 0.0f;
+    case kActSigmoid: return __fmul_rn(g, __fmul_rn(o, __fsub_rn(1.0f, o)));
+    case kActTanh: return __fmul_rn(g, __fsub_rn(1.0f, __fmul_rn(o, o)));
+    default: return g;
+    }
+}
+
+// VEC consecutive columns per thread: 8 (16-bit) or 4 (fp32) with 16-byte accesses when every
+// tensor is column-contiguous and aligned, else 1.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+dense_backward_kernel(const DenseBackwardParams p)
+{
+    __shared__ float red[8][32 * VEC + 1];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t col0 = (blockIdx.x * 32 + lane) * VEC;
+    const unsigned long long total_rows = static_cast<unsigned long long>(p.batch) * p.M;
+    const unsigned long long r_begin = static_cast<unsigned long long>(blockIdx.y) * p.rows_per_chunk;
+    unsigned long long r_end = r_begin + p.rows_per_chunk;
+    if (r_end > total_rows) r_end = total_rows;
+    const T* dy = static_cast<const T*>(p.dy);
+    const T* y = static_cast<const T*>(p.y);
+    T* dz = static_cast<T*>(p.dz);
+
+    float sum[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) sum[j] = 0.0f;
+
+    if (col0 < p.N) {
+        for (unsigned long long r = r_begin + warp; r < r_end; r += 8) {
+            const uint32_t b = static_cast<uint32_t>(r / p.M), m = static_cast<uint32_t>(r % p.M);
+            const long long o_dy = b * p.dy_b + m * p.dy_m + static_cast<long long>(col0) * p.dy_n;
+            const long long o_y = b * p.y_b + m * p.y_m + static_cast<long long>(col0) * p.y_n;
+            const long long o_dz = b * p.dz_b + m * p.dz_m + static_cast<long long>(col0) * p.dz_n;
+            __align__(16) T g[VEC];
+            __align__(16) T o[VEC];
+            __align__(16) T d[VEC];
+            if constexpr (VEC > 1) {
+                *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(dy + o_dy);
+                if (y) *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(y + o_y);
+            } else {
+                g[0] = dy[o_dy];
+                if (y) o[0] = y[o_y];
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+                const float gf = to_float<T>(g[j]);
+                const float df = y ? activation_grad(p.act, gf, to_float<T>(o[j])) : gf;
+                d[j] = from_float<T>(df);
+                sum[j] = __fadd_rn(sum[j], to_float<T>(d[j]));
+            }
+            if (dz) {
+                if constexpr (VEC > 1) *reinterpret_cast<uint4*>(dz + o_dz) = *reinterpret_cast<const uint4*>(d);
+                else dz[o_dz] = d[0];
+            }
+        }
+    }
+    if (p.partial == nullptr) return;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) red[warp][lane * VEC + j] = sum[j];
+    __syncthreads();
+    // 8 warps x (32 * VEC) columns -> one sum per column, warps added in order
+    for (uint32_t c = threadIdx.x; c < 32 * VEC; c += 256) {
+        const uint32_t col = blockIdx.x * 32 * VEC + c;
+        if (col >= p.N) continue;
+        float s = red[0][c];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) s = __fadd_rn(s, red[w][c]);
+        p.partial[static_cast<unsigned long long>(blockIdx.y) * p.N + col] = s;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dense_backward_finish_kernel(const float* partial, uint32_t chunks, uint32_t N, T* dbias, long long dbias_stride)
+{
+    const uint32_t n = blockIdx.x * 256 + threadIdx.x;
+    if (n >= N) return;
+    float s = partial[n];
+    for (uint32_t c = 1; c < chunks; ++c) s = __fadd_rn(s, partial[static_cast<unsigned long long>(c) * N + n]);
+    dbias[static_cast<long long>(n) * dbias_stride] = from_float<T>(s);
+}
+
+}  // namespace srt

@@ -14,6 +14,7 @@
 #include <mutex>
 #include <vector>
 
+#include "dense_backward.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_splitk.cuh"
 #include "gemm_tcgen05.cuh"
@@ -881,6 +882,46 @@ cudaError_t plan_for(const Problem& P, Plan& plan)
     return cudaSuccess;
 }
 
+// ------------------------------------------------------------------ srtBiasActivationBackward
+struct View3 { uint64_t batch, M, N; long long s_b, s_m, s_n; };
+
+// rank 2 [M x N] or rank 3 [batch x M x N] descriptor -> sizes and element strides
+cudaError_t view3(const srtTensorDescriptor* d, const char* what, View3& v)
+{
+    if (!d || !d->shape || !d->strides) return fail(cudaErrorInvalidValue, "%s: missing descriptor", what);
+    if (d->rank != 2 && d->rank != 3) return fail(cudaErrorNotSupported, "%s must have rank 2 or 3", what);
+    const uint32_t q = d->rank - 2;
+    v.batch = d->rank == 3 ? d->shape[0] : 1;
+    v.M = d->shape[q]; v.N = d->shape[q + 1];
+    v.s_b = d->rank == 3 ? (long long)d->strides[0] : 0;
+    v.s_m = (long long)d->strides[q]; v.s_n = (long long)d->strides[q + 1];
+    return cudaSuccess;
+}
+
+template <typename T>
+cudaError_t launch_dense_backward(const DenseBackwardParams& bp, bool vec, uint32_t chunks, void* dbias, long long dbias_stride,
+                                  cudaStream_t stream)
+{
+    constexpr int kVec = 16 / sizeof(T);
+    if (vec) {
+        dim3 grid((bp.N + 32 * kVec - 1) / (32 * kVec), chunks, 1);
+        dense_backward_kernel<T, kVec><<<grid, 256, 0, stream>>>(bp);
+    } else {
+        dim3 grid((bp.N + 31) / 32, chunks, 1);
+        dense_backward_kernel<T, 1><<<grid, 256, 0, stream>>>(bp);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (dbias) {
+        dense_backward_finish_kernel<T><<<(bp.N + 255) / 256, 256, 0, stream>>>(bp.partial, chunks, bp.N, static_cast<T*>(dbias),
+                                                                                 dbias_stride);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return e;
+}
+
 }  // namespace
 
 // ===================================================================== exported entry points
@@ -983,6 +1024,93 @@ cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status)
     }
     *status = v;
     return cudaSuccess;
+}
+
+cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor* dyDesc, const void* y,
+                                      const srtTensorDescriptor* yDesc, srtActivationType activation, void* dz,
+                                      const srtTensorDescriptor* dzDesc, void* dbias, const srtTensorDescriptor* dbiasDesc,
+                                      cudaStream_t stream)
+{
+    if (!dy || !dyDesc) return fail(cudaErrorInvalidValue, "null dy");
+    if (!dz && !dbias) return fail(cudaErrorInvalidValue, "nothing to compute: dz and dbias are both null");
+    View3 vg, vy{}, vz{};
+    cudaError_t e = view3(dyDesc, "dy", vg);
+    if (e != cudaSuccess) return e;
+    const srtDataType type = dyDesc->type;
+    const uint32_t elem = elem_size(type);
+    if (elem == 0) return fail(cudaErrorNotSupported, "element type %d is not computed by this library", (int)type);
+    switch ((int)activation) {
+    case srtActivationIdentity: case srtActivationRelu: case srtActivationSigmoid: case srtActivationTanh: break;
+    case srtActivationGelu: case srtActivationGeluTanh: case srtActivationClippedRelu: case srtActivationElu:
+        return fail(cudaErrorNotSupported, "this activation's derivative needs the pre-activation values, which the forward pass does not keep");
+    default: return fail(cudaErrorInvalidValue, "unknown activation %d", (int)activation);
+    }
+    const bool need_y = activation != srtActivationIdentity;
+    if (need_y) {
+        if (!y) return fail(cudaErrorInvalidValue, "the forward output y is needed for this activation's derivative");
+        e = view3(yDesc, "y", vy);
+        if (e != cudaSuccess) return e;
+        if (yDesc->type != type || vy.batch != vg.batch || vy.M != vg.M || vy.N != vg.N)
+            return fail(cudaErrorInvalidValue, "y must have the type and shape of dy");
+    }
+    if (dz) {
+        e = view3(dzDesc, "dz", vz);
+        if (e != cudaSuccess) return e;
+        if (dzDesc->type != type || vz.batch != vg.batch || vz.M != vg.M || vz.N != vg.N)
+            return fail(cudaErrorInvalidValue, "dz must have the type and shape of dy");
+    }
+    long long dbias_stride = 1;
+    if (dbias) {
+        if (!dbiasDesc || !dbiasDesc->shape || !dbiasDesc->strides || dbiasDesc->rank != 1 || dbiasDesc->shape[0] != vg.N ||
+            dbiasDesc->type != type)
+            return fail(cudaErrorInvalidValue, "dbias must be rank 1 with %llu elements of dy's type", (unsigned long long)vg.N);
+        dbias_stride = (long long)dbiasDesc->strides[0];
+    }
+    if (vg.M == 0 || vg.N == 0 || vg.batch == 0 || vg.M > 0x7fffffffull || vg.N > 0x7fffffffull || vg.batch > 0x7fffffffull)
+        return fail(cudaErrorInvalidValue, "dimension outside the supported range");
+    g_error[0] = 0;
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    DeviceInfo info;
+    e = device_info(dev, info);
+    if (e != cudaSuccess) return e;
+
+    DenseBackwardParams bp;
+    memset(&bp, 0, sizeof bp);
+    bp.dy = dy; bp.y = need_y ? y : nullptr; bp.dz = dz;
+    bp.dy_b = vg.s_b; bp.dy_m = vg.s_m; bp.dy_n = vg.s_n;
+    bp.y_b = vy.s_b; bp.y_m = vy.s_m; bp.y_n = vy.s_n;
+    bp.dz_b = vz.s_b; bp.dz_m = vz.s_m; bp.dz_n = vz.s_n;
+    bp.M = (uint32_t)vg.M; bp.N = (uint32_t)vg.N; bp.batch = (uint32_t)vg.batch;
+    bp.act = (uint32_t)activation;
+    const uint32_t vecw = 16 / elem;
+    auto vec_ok = [&](const void* ptr, const View3& v) {
+        return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (v.s_n == 1 || v.N == 1) && (v.s_m * (long long)elem) % 16 == 0 &&
+               (v.s_b * (long long)elem) % 16 == 0;
+    };
+    const bool vec = vg.N % vecw == 0 && vec_ok(dy, vg) && (!need_y || vec_ok(y, vy)) && (!dz || vec_ok(dz, vz));
+    // enough blocks to fill the device a few times over, at least 8 rows (one per warp) per chunk
+    const uint64_t rows = vg.batch * vg.M;
+    const uint64_t col_blocks = (vg.N + 32 * (vec ? vecw : 1) - 1) / (32 * (vec ? vecw : 1));
+    uint64_t chunks = ((uint64_t)info.sms * 4 + col_blocks - 1) / col_blocks;
+    if (chunks > (rows + 7) / 8) chunks = (rows + 7) / 8;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 65535) chunks = 65535;
+    bp.rows_per_chunk = (uint32_t)((rows + chunks - 1) / chunks);
+    chunks = (rows + bp.rows_per_chunk - 1) / bp.rows_per_chunk;
+    bp.partial = nullptr;
+    if (dbias) {
+        void* ws = nullptr;
+        e = workspace_for(dev, stream, (size_t)chunks * vg.N * sizeof(float), &ws);
+        if (e != cudaSuccess) return e;
+        bp.partial = static_cast<float*>(ws);
+    }
+    switch (type) {
+    case real32F: return launch_dense_backward<float>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
+    case real16F: return launch_dense_backward<__half>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
+    default: return launch_dense_backward<__nv_bfloat16>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
+    }
 }
 
 // ------------------------------------------------------------------ srtMatmulNoAlloc

@@ -175,3 +175,26 @@ def test_row_window_leaves_other_rows_untouched(oracle):
     part = np.full((20, 5), 7.0, dtype=np.float32)
     oracle.matmul(a, b, F32, out=part, rows=(4, 9))
     assert np.array_equal(part[4:9], full[4:9]) and np.all(part[:4] == 7) and np.all(part[9:] == 7)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("act", ["identity", "relu", "sigmoid", "tanh"])
+def test_bias_activation_backward_restatement(oracle, dtype, act):
+    """dz = dy * act'(y) and dbias = column sums, against float64; the reference-style row-by-row
+    rounding of the running sum (cpu_sum keeps it in the output tensor) is recorded next to the
+    graded fp32 running sum."""
+    rng = np.random.default_rng(8)
+    y = oracle.encode(np.tanh(rng.standard_normal((300, 17))) if act != "sigmoid" else rng.uniform(0, 1, (300, 17)), dtype)
+    dy = oracle.encode(rng.standard_normal((300, 17)), dtype)
+    dz, db = oracle.bias_activation_backward(dy, y, dtype, act)
+    yf, gf = oracle.decode(y, dtype).astype(np.float64), oracle.decode(dy, dtype).astype(np.float64)
+    grad = {"identity": np.ones_like(yf), "relu": (yf > 0).astype(np.float64), "sigmoid": yf * (1 - yf),
+            "tanh": 1 - yf * yf}[act]
+    tol = 1e-6 if dtype == F32 else 1e-2
+    assert oracle.rel_frobenius(oracle.decode(dz, dtype), gf * grad) <= tol
+    assert oracle.rel_frobenius(oracle.decode(db, dtype), oracle.decode(dz, dtype).astype(np.float64).sum(axis=0)) <= tol
+    _, db_step = oracle.bias_activation_backward(dy, y, dtype, act, stepwise=True)
+    if dtype == F32:
+        assert np.array_equal(db_step, db)          # fp32 elements: rounding every row IS the fp32 running sum
+    else:
+        assert oracle.rel_frobenius(oracle.decode(db_step, dtype), oracle.decode(db, dtype)) < 0.1
