@@ -159,7 +159,7 @@ def run_reference(args):
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier):
@@ -288,10 +288,28 @@ def run_ours(args):
         if world == 1 and not args.no_cpu:
             tf, cores, sample, _ = cpu_sample(M, N, K, cpu_inputs(N, K), target_s=args.cpu_seconds)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries print to stdout too (NCCL writes its version banner there), and the one JSON line
+    must be the only thing on it: point fd 1 at stderr for the run and keep the real stdout aside."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    text = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, text)
 
 
 def main():
@@ -308,6 +326,7 @@ def main():
     ap.add_argument("--tune", default="", help="forceKernel,tileN,stages,maxCtas for srtMatmulSetTuning (0 = automatic)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    keep_stdout_for_the_result()
     if args.impl == "reference":
         run_reference(args)
     else:
