@@ -193,6 +193,54 @@ def measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier):
             "h2d_bytes_per_step": int(bytes_t[0].item()), "d2h_bytes_per_step": int(bytes_t[1].item())}
 
 
+def measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier):
+    """Full C on every GPU, two ways, same sharding (N over the ranks), device-timed, max over ranks:
+    fused  = srtMatmulAllGather: the product's epilogue stores each tile into every GPU's buffer
+             over NVLink, then a barrier orders the ranks;
+    nccl   = the product, an NCCL all-gather of the column blocks and the copy that places them."""
+    import torch
+    import torch.distributed as dist
+    steps = max(1, min(args.steps, 10))
+    flops = 2.0 * M * N * K
+    rank = dist.get_rank()
+    lo, hi = srt.shard_range(N, world, rank, 8)
+    buf = srt.PeerBuffer((M, N), a.dtype)
+    view = buf.tensor.narrow(1, lo, hi - lo)
+    fused = srt.MatmulOp(view, a, False, b_full[:, lo:hi], False, peer_pointers=buf.peer_pointers(view))
+    full = torch.empty((M, N), dtype=a.dtype, device=dev)
+
+    def fused_step():
+        fused()
+        buf.ranks_done()
+
+    def nccl_step():
+        srt.sharded_matmul(a, b_full, axis="n", gather=True, out=full)
+
+    out = {"steps": steps, "bytes_sent_per_rank": int((world - 1) * M * (hi - lo) * a.element_size())}
+    for name, fn in (("fused", fused_step), ("nccl", nccl_step)):
+        for _ in range(3):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item()) / steps
+        out[name + "_ms"] = ms
+        out[name + "_tflops"] = flops / (ms * 1e-3) / 1e12
+    status = srt.check_status()
+    same = torch.equal(buf.tensor, full)
+    flag = torch.tensor([1 if (same and status == 0) else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    out["results_identical"] = bool(int(flag.item()))
+    buf.close()
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 def run_ours(args):
     import torch
@@ -264,6 +312,10 @@ def run_ours(args):
     if not args.no_e2e:
         e2e = measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier)
 
+    gather = None
+    if world > 1 and not args.no_gather:
+        gather = measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier)
+
     if rank == 0:
         pk, pk_kind = peaks()
         avg_kernel_ms = sum(kernel_ms) / len(kernel_ms)
@@ -283,6 +335,7 @@ def run_ours(args):
             "roofline": roofline,
             "e2e": e2e,
             "gpu_launches": int(launches),
+            "gather": gather,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
@@ -323,6 +376,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the full-C-on-every-GPU comparison")
     ap.add_argument("--tune", default="", help="forceKernel,tileN,stages,maxCtas for srtMatmulSetTuning (0 = automatic)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -230,6 +230,49 @@ cudaError_t srtMatmulNoAlloc(
     void* out, const srtTensorDescriptor* oDesc,
     cudaStream_t stream);
 
+/* ---- several GPUs of one machine, one process per GPU -----------------------------------------
+ *
+ * The reference has no multi-GPU path: its only data-parallel construct partitions axis 0 of a
+ * CPU tensor over threads that write disjoint views of one shared output
+ * (Sources/SwiftRTCore/operators/pmap.swift:26-72).  The entry points below are that idea for
+ * GPUs: every rank computes one block of C (its columns, rows or batch items) and writes it into
+ * ITS view of a full-size C -- in its own buffer and in every peer's buffer. */
+
+/* A buffer that other processes can map (cudaIpcMemHandle_t, 64 bytes). */
+typedef struct { unsigned char bytes[64]; } srtPeerMemHandle;
+
+/* cudaMalloc + cudaIpcGetMemHandle on the current device.  Send `handle` to the other ranks. */
+cudaError_t srtPeerMemAlloc(size_t bytes, void** ptr, srtPeerMemHandle* handle);
+/* Maps another rank's buffer into this process (peer access is enabled on demand).  A process
+ * cannot open its own handle. */
+cudaError_t srtPeerMemOpen(const srtPeerMemHandle* handle, void** ptr);
+/* Unmaps a pointer obtained from srtPeerMemOpen. */
+cudaError_t srtPeerMemClose(void* ptr);
+/* Frees a buffer obtained from srtPeerMemAlloc (after every peer has closed its mapping). */
+cudaError_t srtPeerMemFree(void* ptr);
+
+/* srtMatmulAllGather: srtMatmulBiasActivation whose result block is also delivered to peers.
+ *
+ * `out`/`oDesc` is this rank's block of C as a view into its own full-size buffer.  peerOut[i]
+ * (0 <= i < peerCount <= 7) is the first element of the same view -- same shape, strides and
+ * offset -- in the buffer of another GPU, mapped with srtPeerMemOpen (an address in a buffer of
+ * the same GPU is accepted too).  For products that run on the CTA-pair tensor-core kernel with
+ * a 16-byte aligned, row-contiguous output view, the kernel's epilogue stores each finished tile
+ * to the local and to all peer buffers, so the transfer overlaps the product; every other product
+ * runs as srtMatmulBiasActivation followed by one strided copy per peer on `stream`.
+ *
+ * Completion: the peers' copies are complete when `stream` has drained on THIS rank.  No rank
+ * waits for another on the device; before reading blocks written by others, synchronise the
+ * ranks on the host (each rank: cudaStreamSynchronize, then a barrier). */
+cudaError_t srtMatmulAllGather(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* bias, const srtTensorDescriptor* biasDesc,
+    srtActivationType activation,
+    void* out, const srtTensorDescriptor* oDesc,
+    int32_t peerCount, void* const* peerOut,
+    cudaStream_t stream);
+
 /* Device-side status of the last tensor-core launches on the current device: 0 = all
  * pipeline waits completed; non-zero = a bounded wait gave up (the code says which) and
  * the result of that launch is invalid.  Synchronises `stream` and resets the status. */

@@ -39,7 +39,8 @@ class MatmulPlan(ctypes.Structure):
 
 # every symbol include/srt_matmul_api.h declares
 EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
-           "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString"]
+           "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString",
+           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -70,6 +71,25 @@ lib.srtMatmulLaunchCount.restype = ctypes.c_uint64
 lib.srtMatmulLaunchCount.argtypes = []
 lib.srtMatmulGetLastErrorString.restype = ctypes.c_char_p
 lib.srtMatmulGetLastErrorString.argtypes = []
+
+
+
+class PeerMemHandle(ctypes.Structure):
+    """srtPeerMemHandle (64 opaque bytes)."""
+    _fields_ = [("bytes", ctypes.c_ubyte * 64)]
+
+
+lib.srtMatmulAllGather.restype = ctypes.c_int
+lib.srtMatmulAllGather.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_int, _P, _D,
+                                   ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p), _P]
+lib.srtPeerMemAlloc.restype = ctypes.c_int
+lib.srtPeerMemAlloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(PeerMemHandle)]
+lib.srtPeerMemOpen.restype = ctypes.c_int
+lib.srtPeerMemOpen.argtypes = [ctypes.POINTER(PeerMemHandle), ctypes.POINTER(ctypes.c_void_p)]
+lib.srtPeerMemClose.restype = ctypes.c_int
+lib.srtPeerMemClose.argtypes = [_P]
+lib.srtPeerMemFree.restype = ctypes.c_int
+lib.srtPeerMemFree.argtypes = [_P]
 
 
 def last_error() -> str:

@@ -78,6 +78,7 @@ struct GemmParams {
     uint32_t act;
     uint32_t out_vec_ok;         // 16-byte vector stores are aligned for every full chunk
     uint32_t out_tma;            // the output view is TMA-addressable: bulk tensor stores from shared memory
+    uint32_t n_peers;            // gathering kernels only: peer copies of the output view (<= kMaxPeers)
 };
 
 enum : uint32_t { kActSigmoid = 0, kActRelu = 1, kActTanh = 2, kActIdentity = 5, kActGelu = 6, kActGeluTanh = 7 };
@@ -218,10 +219,22 @@ constexpr uint32_t kEpilogueStagingBytes = 8 * 4096;         // 8 warps x (32 ro
 
 // PARTS: how many warps share one lane quarter (1 or 2); warp `part` drains every PARTS-th
 // 128-byte column segment.  `staging` is this warp's own 4 KB buffer.
-template <typename T, uint32_t BN, bool DUAL = false, uint32_t PARTS = 1>
+//
+// GATHER: every staged segment is also stored through the tensor maps of `peers` (the same view
+// in the output buffers of other GPUs, mapped into this process), so that all of them hold the
+// tile when the kernel has finished.  Bulk tensor STORES to peer memory only; nothing is loaded
+// from a peer and no peer is waited for.
+constexpr uint32_t kMaxPeers = 7;
+struct PeerMaps { CUtensorMap m[kMaxPeers]; };
+struct NoPeers { uint32_t unused; };
+template <bool GATHER> struct PeerArgOf { using type = NoPeers; };
+template <> struct PeerArgOf<true> { using type = PeerMaps; };
+
+template <typename T, uint32_t BN, bool DUAL = false, uint32_t PARTS = 1, bool GATHER = false>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tmap_out, uint32_t staging,
                                                   uint32_t part, uint32_t acc, uint32_t quarter, uint32_t lane,
-                                                  uint32_t batch, uint32_t m0, uint32_t n0, uint32_t acc2 = 0)
+                                                  uint32_t batch, uint32_t m0, uint32_t n0, uint32_t acc2 = 0,
+                                                  const CUtensorMap* peers = nullptr)
 {
     constexpr uint32_t kColsPerBox = 128 / sizeof(T);            // 64 (16-bit) or 32 (fp32)
     constexpr uint32_t kLoadsPerBox = kColsPerBox / 32;
@@ -292,6 +305,11 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
             if (lane == 0) {
                 tma_store_3d(tmap_out, staging, static_cast<int32_t>(box_col), static_cast<int32_t>(m0 + quarter * 32),
                              static_cast<int32_t>(batch));
+                if constexpr (GATHER) {
+                    for (uint32_t i = 0; i < p.n_peers; ++i)
+                        tma_store_3d(peers + i, staging, static_cast<int32_t>(box_col),
+                                     static_cast<int32_t>(m0 + quarter * 32), static_cast<int32_t>(batch));
+                }
                 bulk_commit_group();
             }
         }
@@ -483,12 +501,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 //   tmem_full[b] both CTAs, multicast tcgen05.commit after the tile's last MMA.
 //   tmem_empty[b] CTA 0 only, count 16: the eight epilogue warps of each CTA.
 // No TMA load is multicast; all loads are plain per-CTA tile loads.
-template <typename T, uint32_t BN>
+//
+// GATHER: the epilogue also stores every tile into the peers' output buffers (product followed
+// by an all-gather of the shards, in one kernel; see drain_accumulator).
+template <typename T, uint32_t BN, bool GATHER = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_out,
-                         const __grid_constant__ GemmParams p)
+                         const __grid_constant__ GemmParams p,
+                         const __grid_constant__ typename PeerArgOf<GATHER>::type peer_maps)
 {
     constexpr uint32_t kBHalf = BN / 2;
     constexpr uint32_t kBTileBytes = kBHalf * kRowBytes;
@@ -629,8 +651,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
-                                               (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
+            if constexpr (GATHER)
+                drain_accumulator<T, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+                                                         (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
+                                                         0, peer_maps.m);
+            else
+                drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+                                                   (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);

@@ -510,11 +510,11 @@ cudaError_t launch_split(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     return cudaGetLastError();
 }
 
-template <typename T, uint32_t BN>
+template <typename T, uint32_t BN, bool GATHER = false>
 cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas, size_t smem,
-                        cudaStream_t stream)
+                        cudaStream_t stream, const typename PeerArgOf<GATHER>::type& peers = typename PeerArgOf<GATHER>::type())
 {
-    auto kernel = gemm_tcgen05_pair_kernel<T, BN>;
+    auto kernel = gemm_tcgen05_pair_kernel<T, BN, GATHER>;
     static std::atomic<uint64_t> attr_done{0};
     static std::atomic<int> cluster_cache[64];           // max co-resident pairs per device, 0 = unknown
     cudaError_t e = ensure_smem_attr(kernel, attr_done, smem);
@@ -547,7 +547,7 @@ cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUte
         cluster_cache[dev & 63].store(max_clusters, std::memory_order_release);
     }
     if (ctas / 2 > (uint32_t)max_clusters) cfg.gridDim.x = 2u * (uint32_t)max_clusters;
-    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, gp);
+    return cudaLaunchKernelEx(&cfg, kernel, ma, mb, mo, gp, peers);
 }
 
 template <typename T>
@@ -556,6 +556,15 @@ cudaError_t launch_pair_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap
 {
     if (bn == 128) return launch_pair<T, 128>(ma, mb, mo, gp, ctas, smem, stream);
     return launch_pair<T, 256>(ma, mb, mo, gp, ctas, smem, stream);
+}
+
+// The gathering form of the pair kernel (product + stores of every tile to the peers' buffers).
+template <typename T>
+cudaError_t launch_pair_gather_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp,
+                                  uint32_t ctas, size_t smem, cudaStream_t stream, const PeerMaps& peers)
+{
+    if (bn == 128) return launch_pair<T, 128, true>(ma, mb, mo, gp, ctas, smem, stream, peers);
+    return launch_pair<T, 256, true>(ma, mb, mo, gp, ctas, smem, stream, peers);
 }
 
 // Everything a launch needs, computed once per distinct call signature (see the call cache).
@@ -576,6 +585,24 @@ struct Prepared {
     ReduceParams rp;
     uint32_t reduce_vec = 1, reduce_blocks = 0;
 };
+
+// Tensor map of an output view for the epilogue's bulk stores: boxes of 32 rows x 128 bytes,
+// 128-byte swizzle.  `base` is the view's first element (the caller's buffer, or the same view
+// in a peer's buffer).  False when the view is not TMA-addressable.
+bool encode_out_map(CUtensorMap* map, const Problem& Q, long long ldo, void* base)
+{
+    const CUtensorMapDataType dt = Q.type == real32F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : Q.type == real16F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const bool one = Q.batch == 1;
+    cuuint64_t gdim[3] = {Q.N, Q.M, one ? 1 : Q.batch};
+    cuuint64_t gstride[2] = {(cuuint64_t)ldo * Q.elem, one ? (cuuint64_t)ldo * Q.elem * Q.M : (cuuint64_t)Q.o_b * Q.elem};
+    cuuint32_t box[3] = {kRowBytes / Q.elem, 32, 1}, estr[3] = {1, 1, 1};
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return false;
+    return gstride[1] % 16 == 0 && gstride[0] < (1ull << 40) && gstride[1] < (1ull << 40) &&
+           g_encode(map, dt, 3, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
 {
@@ -625,19 +652,7 @@ cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
     // bulk tensor stores need the same alignment as 16-byte vector stores
     gp.out_tma = 0;
     memset(&pr.mo, 0, sizeof pr.mo);
-    if (gp.out_vec_ok && Q.N > 1) {
-        const CUtensorMapDataType dt = Q.type == real32F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                       : Q.type == real16F ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-        const bool one = Q.batch == 1;
-        cuuint64_t gdim[3] = {Q.N, Q.M, one ? 1 : Q.batch};
-        cuuint64_t gstride[2] = {(cuuint64_t)gp.ldo * Q.elem, one ? (cuuint64_t)gp.ldo * Q.elem * Q.M : (cuuint64_t)Q.o_b * Q.elem};
-        cuuint32_t box[3] = {kRowBytes / Q.elem, 32, 1}, estr[3] = {1, 1, 1};
-        if (gstride[1] % 16 == 0 && gstride[0] < (1ull << 40) && gstride[1] < (1ull << 40) &&
-            g_encode(&pr.mo, dt, 3, Q.out, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
-            gp.out_tma = 1;
-    }
+    if (gp.out_vec_ok && Q.N > 1 && encode_out_map(&pr.mo, Q, gp.ldo, Q.out)) gp.out_tma = 1;
     pr.kernel = plan.pub.kernel;
     pr.type = Q.type;
     pr.bn = bn;
@@ -747,6 +762,10 @@ cudaError_t prepare_simt(const Plan& plan, Prepared& pr)
     pr.grid = dim3((unsigned)tn, (unsigned)tm, (unsigned)P.batch);
     pr.kernel = srtMatmulKernelSimt;
     pr.type = P.type;
+    // `pr` may be a recycled call-cache slot that last held a split-K launch
+    pr.splits = 1;
+    pr.ws_bytes = 0;
+    pr.ws_bound = nullptr;
     return cudaSuccess;
 }
 
@@ -1188,6 +1207,168 @@ cudaError_t srtMatmulNoAlloc(const void* a, const srtTensorDescriptor* aDesc, bo
     e = launch_reduce(pr, stream);
     if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return e;
+}
+
+// ------------------------------------------------------------------ srtMatmulAllGather
+// One rank's part of "every GPU computes a block of C, every GPU ends up with all of C".
+// `out` is this rank's block as a view into its own full-size buffer; peerOut[i] is the first
+// element of the SAME view in the buffer of another GPU, mapped into this process (see
+// srtPeerMemOpen).  When the plan is the CTA-pair kernel with bulk tensor stores, the epilogue
+// stores each finished tile to all buffers (one kernel: the transfers overlap the product tile by
+// tile).  Any other plan runs the ordinary product and then copies the block to each peer on the
+// same stream.  Nothing waits for another GPU: the peers' copies are complete when this stream
+// has drained, and the caller synchronises the ranks (a host barrier) before anyone reads.
+struct GatherKey {
+    CallKey call;
+    void* peers[kMaxPeers];
+    int32_t count;
+    int32_t pad;
+};
+struct GatherEntry {
+    bool valid = false;
+    bool fused = false;
+    GatherKey key;
+    Prepared pr;
+    PeerMaps maps;
+};
+constexpr int kGatherCacheSize = 8;
+static thread_local GatherEntry* t_gather = nullptr;
+
+static cudaError_t copy_view_to_peers(const Problem& P, const srtTensorDescriptor* oDesc, const void* out, int32_t count,
+                               void* const* peers, cudaStream_t stream)
+{
+    View3 v;
+    cudaError_t e = view3(oDesc, "out", v);
+    if (e != cudaSuccess) return e;
+    size_t width, height, pitch;
+    if (v.s_n == 1 || v.N == 1) { width = v.N * P.elem; height = v.M; pitch = (size_t)v.s_m * P.elem; }
+    else if (v.s_m == 1 || v.M == 1) { width = v.M * P.elem; height = v.N; pitch = (size_t)v.s_n * P.elem; }
+    else return fail(cudaErrorNotSupported, "srtMatmulAllGather: the output view has no contiguous dimension");
+    if (height <= 1) pitch = width;
+    if (pitch < width) return fail(cudaErrorNotSupported, "srtMatmulAllGather: overlapping output rows");
+    for (int32_t i = 0; i < count; ++i)
+        for (uint64_t bt = 0; bt < v.batch; ++bt) {
+            const size_t off = (size_t)bt * (size_t)v.s_b * P.elem;
+            e = cudaMemcpy2DAsync(static_cast<char*>(peers[i]) + off, pitch, static_cast<const char*>(out) + off, pitch, width,
+                                  height, cudaMemcpyDefault, stream);
+            if (e != cudaSuccess) return fail(e, "srtMatmulAllGather: copy to peer %d failed: %s", i, cudaGetErrorString(e));
+        }
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                               const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                               const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                               const srtTensorDescriptor* oDesc, int32_t peerCount, void* const* peerOut,
+                               cudaStream_t stream)
+{
+    if (peerCount < 0 || peerCount > (int32_t)kMaxPeers)
+        return fail(cudaErrorInvalidValue, "srtMatmulAllGather: peerCount %d outside 0..%u", peerCount, kMaxPeers);
+    if (peerCount > 0 && !peerOut) return fail(cudaErrorInvalidValue, "srtMatmulAllGather: null peerOut");
+    if (peerCount == 0)
+        return srtMatmulBiasActivation(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, activation, out, oDesc, stream);
+    GatherKey key;
+    memset(&key, 0, sizeof key);
+    Problem& P = key.call.P;
+    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
+    if (e != cudaSuccess) return e;
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    key.call.force = g_tuning.force_kernel.load(std::memory_order_relaxed);
+    key.call.tile_n = g_tuning.tile_n.load(std::memory_order_relaxed);
+    key.call.stages = g_tuning.stages.load(std::memory_order_relaxed);
+    key.call.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
+    key.call.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
+    key.call.device = dev;
+    key.count = peerCount;
+    for (int32_t i = 0; i < peerCount; ++i) {
+        if (!peerOut[i]) return fail(cudaErrorInvalidValue, "srtMatmulAllGather: peerOut[%d] is null", i);
+        key.peers[i] = peerOut[i];
+    }
+    if (!t_gather) t_gather = new GatherEntry[kGatherCacheSize];
+    GatherEntry& ent = t_gather[hash_key(key.call) % kGatherCacheSize];
+    if (!(ent.valid && memcmp(&ent.key, &key, sizeof key) == 0)) {
+        ent.valid = false;
+        Plan plan;
+        e = plan_for(P, plan);
+        if (e != cudaSuccess) return e;
+        e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, ent.pr) : prepare_tc(plan, ent.pr);
+        if (e != cudaSuccess) return e;
+        ent.fused = plan.pub.kernel == srtMatmulKernelTcgen05Pair && ent.pr.splits <= 1 && ent.pr.gp.out_tma;
+        if (ent.fused) {
+            // the planner may have transposed the problem (column-order output): peers hold the same view
+            memset(&ent.maps, 0, sizeof ent.maps);
+            for (int32_t i = 0; i < peerCount && ent.fused; ++i)
+                ent.fused = encode_out_map(&ent.maps.m[i], plan.Q, ent.pr.gp.ldo, peerOut[i]);
+        }
+        ent.pr.gp.n_peers = ent.fused ? (uint32_t)peerCount : 0u;
+        ent.key = key;
+        ent.valid = true;
+    }
+    if (!ent.fused) {
+        e = launch_prepared(ent.pr, stream);
+        if (e != cudaSuccess) return e;
+        return copy_view_to_peers(P, oDesc, out, peerCount, peerOut, stream);
+    }
+    const Prepared& pr = ent.pr;
+    switch (pr.type) {
+    case real32F: e = launch_pair_gather_bn<float>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+    case real16F: e = launch_pair_gather_bn<__half>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+    default: e = launch_pair_gather_bn<__nv_bfloat16>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+    }
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
+// ------------------------------------------------------------------ peer memory (one process per GPU)
+// Device buffers that other processes of the same machine can map: plain cudaMalloc memory and
+// CUDA IPC handles, no multicast objects.  The handle bytes travel over whatever channel the ranks
+// already have (an MPI or torch.distributed all-gather of 64 bytes per rank).
+cudaError_t srtPeerMemAlloc(size_t bytes, void** ptr, srtPeerMemHandle* handle)
+{
+    static_assert(sizeof(srtPeerMemHandle) == sizeof(cudaIpcMemHandle_t), "handle size");
+    if (!ptr || !handle || bytes == 0) return fail(cudaErrorInvalidValue, "srtPeerMemAlloc: null argument or zero size");
+    *ptr = nullptr;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return fail(e, "srtPeerMemAlloc: cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(e, "srtPeerMemAlloc: cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle->bytes, &h, sizeof h);
+    *ptr = p;
+    return cudaSuccess;
+}
+
+cudaError_t srtPeerMemOpen(const srtPeerMemHandle* handle, void** ptr)
+{
+    if (!ptr || !handle) return fail(cudaErrorInvalidValue, "srtPeerMemOpen: null argument");
+    *ptr = nullptr;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle->bytes, sizeof h);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(e, "srtPeerMemOpen: cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+    *ptr = p;
+    return cudaSuccess;
+}
+
+cudaError_t srtPeerMemClose(void* ptr)
+{
+    if (!ptr) return cudaSuccess;
+    cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    return e == cudaSuccess ? e : fail(e, "srtPeerMemClose: %s", cudaGetErrorString(e));
+}
+
+cudaError_t srtPeerMemFree(void* ptr)
+{
+    if (!ptr) return cudaSuccess;
+    cudaError_t e = cudaFree(ptr);
+    return e == cudaSuccess ? e : fail(e, "srtPeerMemFree: %s", cudaGetErrorString(e));
 }
 
 #ifdef SRT_TRACE

@@ -64,7 +64,10 @@ class MatmulOp:
 
     def __init__(self, out: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
                  transpose_rhs: bool, bias: torch.Tensor | None = None,
-                 activation: ActivationType | None = None):
+                 activation: ActivationType | None = None, peer_pointers=None):
+        """`peer_pointers`: device addresses of the same output view in other GPUs' buffers
+        (PeerBuffer.peer_pointers); the result block is then delivered to them as well
+        (srtMatmulAllGather)."""
         if not (lhs.is_cuda and rhs.is_cuda and out.is_cuda):
             raise ValueError("device tensors expected; use matmul_host for host buffers")
         self.out = out
@@ -73,7 +76,16 @@ class MatmulOp:
         self._index = out.device.index if out.device.index is not None else torch.cuda.current_device()
         da, db, do = _descriptor(lhs), _descriptor(rhs), _descriptor(out)
         self._descs = (da, db, do)
-        if bias is None and activation is None:
+        if peer_pointers:
+            dbias = _descriptor(bias) if bias is not None else None
+            self._descs += (dbias,)
+            self._peers = (ctypes.c_void_p * len(peer_pointers))(*peer_pointers)
+            self._fn = lib.srtMatmulAllGather
+            self._args = (lhs.data_ptr(), da.ref(), bool(transpose_lhs), rhs.data_ptr(), db.ref(), bool(transpose_rhs),
+                          bias.data_ptr() if bias is not None else None, dbias.ref() if dbias is not None else None,
+                          int(activation if activation is not None else ActivationType.identity),
+                          out.data_ptr(), do.ref(), len(peer_pointers), self._peers)
+        elif bias is None and activation is None:
             self._fn = lib.srtMatmul
             self._args = (lhs.data_ptr(), da.ref(), bool(transpose_lhs), rhs.data_ptr(), db.ref(), bool(transpose_rhs),
                           out.data_ptr(), do.ref())
@@ -106,6 +118,15 @@ def matmul_into(out: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: 
     strided view (CpuMath.swift:355-369 takes the result inout).  Asynchronous on torch's current
     stream of out's device."""
     return MatmulOp(out, lhs, transpose_lhs, rhs, transpose_rhs, bias, activation)()
+
+
+def matmul_all_gather_into(out: torch.Tensor, peer_pointers, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
+                           transpose_rhs: bool, bias: torch.Tensor | None = None,
+                           activation: ActivationType | None = None) -> torch.Tensor:
+    """matmul_into whose result block also lands at `peer_pointers` (the same view in the other
+    ranks' buffers).  The peers' copies are complete when this rank's stream has drained; order
+    the ranks (PeerBuffer.ranks_done) before reading blocks that others wrote."""
+    return MatmulOp(out, lhs, transpose_lhs, rhs, transpose_rhs, bias, activation, peer_pointers)()
 
 
 def matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,

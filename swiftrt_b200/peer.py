@@ -1,0 +1,108 @@
+"""Result buffers that every rank of one machine can write: the storage behind the fused
+product + all-gather (srtMatmulAllGather).
+
+One process per GPU.  Each rank allocates one full-size result with srtPeerMemAlloc, the 64-byte
+handles travel through torch.distributed, and each rank maps the others' buffers with
+srtPeerMemOpen.  The reference's pmap gives every partition a view of one shared output
+(Sources/SwiftRTCore/operators/pmap.swift:26-72); here "shared" is one buffer per GPU, all of
+them holding all blocks once every rank has finished.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import lib
+from .matmul import MatmulError
+
+
+def _check(rc: int) -> None:
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+
+
+class _RawDeviceMemory:
+    """Just enough of the CUDA array interface for torch to wrap a device pointer."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+class PeerBuffer:
+    """A dense tensor of `shape` on this rank's GPU plus the addresses of the same tensor on the
+    other ranks' GPUs.
+
+    tensor      this rank's buffer as a torch tensor (not owned by torch's allocator)
+    peer_base   {rank: device address of that rank's buffer, mapped into this process}
+    """
+
+    def __init__(self, shape: Sequence[int], dtype: torch.dtype, group=None, device: Optional[torch.device] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (7 peers)")
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = dtype
+        count = 1
+        for s in self.shape:
+            count *= s
+        self.nbytes = max(count * torch.empty((), dtype=dtype).element_size(), 16)
+        self._ptr = ctypes.c_void_p()
+        handle = _lib.PeerMemHandle()
+        with torch.cuda.device(self.device):
+            _check(lib.srtPeerMemAlloc(self.nbytes, ctypes.byref(self._ptr), ctypes.byref(handle)))
+        raw = torch.as_tensor(_RawDeviceMemory(self._ptr.value, self.nbytes), device=self.device)
+        self.tensor = raw[: count * raw.new_empty((), dtype=dtype).element_size()].view(dtype).reshape(self.shape)
+        self.peer_base: dict[int, int] = {}
+        if self.world > 1:
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.bytes), group=group)
+            with torch.cuda.device(self.device):
+                for r, blob in enumerate(handles):
+                    if r == self.rank:
+                        continue
+                    h = _lib.PeerMemHandle()
+                    ctypes.memmove(h.bytes, blob, 64)
+                    p = ctypes.c_void_p()
+                    _check(lib.srtPeerMemOpen(ctypes.byref(h), ctypes.byref(p)))
+                    self.peer_base[r] = p.value
+        self._open = True
+
+    def peer_pointers(self, view: torch.Tensor) -> list[int]:
+        """Addresses of `view` (a view of self.tensor) in every peer's buffer, by rank order."""
+        offset = view.data_ptr() - self.tensor.data_ptr()
+        if not 0 <= offset < self.nbytes:
+            raise ValueError("not a view of this buffer")
+        return [base + offset for _, base in sorted(self.peer_base.items())]
+
+    def ranks_done(self) -> None:
+        """Orders everything the ranks enqueued so far before what follows on this rank's current
+        stream: after it, blocks written by other ranks may be read."""
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' buffers, then frees this rank's."""
+        if not self._open:
+            return
+        self._open = False
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for p in self.peer_base.values():
+                _check(lib.srtPeerMemClose(p))
+        self.peer_base = {}
+        if self.world > 1:
+            dist.barrier(group=self.group)
+            torch.cuda.synchronize(self.device)
+        self.tensor = None
+        with torch.cuda.device(self.device):
+            _check(lib.srtPeerMemFree(self._ptr))

@@ -54,13 +54,21 @@ def sharded_matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = 
                    transposed_rhs: bool = False, axis: str = "n", gather: bool = False,
                    out: Optional[torch.Tensor] = None, group=None,
                    matmul_into_fn: Optional[Callable] = None,
-                   rank: Optional[int] = None, world: Optional[int] = None) -> torch.Tensor:
+                   rank: Optional[int] = None, world: Optional[int] = None,
+                   peer_buffer=None, gather_fn: Optional[Callable] = None) -> torch.Tensor:
     """Computes this rank's block of op(lhs).op(rhs).
 
     Returns the local block (a dense tensor) when `gather` is False, else the full result on
     every rank.  `out`, if given, is the full-size result tensor to fill (gather) or the local
     block.  `matmul_into_fn(out, lhs, tl, rhs, tr)` defaults to the CUDA operator; tests on CPU
-    ranks inject their own."""
+    ranks inject their own.
+
+    With `peer_buffer` (a swiftrt_b200.peer.PeerBuffer of the full result's shape) the gather is
+    fused into the product: this rank's block is written into its view of every rank's buffer
+    by the product's own kernel (srtMatmulAllGather), there is no collective and no staging copy
+    for any axis, and the call returns peer_buffer.tensor.  Blocks from other ranks are complete
+    after peer_buffer.ranks_done().  `gather_fn(out_view, peer_pointers, lhs, tl, rhs, tr)`
+    defaults to the CUDA operator."""
     if axis not in AXES:
         raise ValueError(f"axis must be one of {AXES}")
     if matmul_into_fn is None:
@@ -85,6 +93,16 @@ def sharded_matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = 
     dim = {"batch": 0, "m": len(full_shape) - 2, "n": len(full_shape) - 1}[axis]
     local_shape = list(full_shape)
     local_shape[dim] = hi - lo
+
+    if peer_buffer is not None:
+        if tuple(peer_buffer.tensor.shape) != tuple(full_shape):
+            raise ValueError(f"peer buffer of shape {tuple(peer_buffer.tensor.shape)}, result is {tuple(full_shape)}")
+        if gather_fn is None:
+            from .matmul import matmul_all_gather_into as gather_fn
+        if hi > lo:
+            view = peer_buffer.tensor.narrow(dim, lo, hi - lo)
+            gather_fn(view, peer_buffer.peer_pointers(view), a, transposed_lhs, b, transposed_rhs)
+        return peer_buffer.tensor
 
     if not gather:
         local = out if out is not None else torch.empty(local_shape, dtype=lhs.dtype, device=lhs.device)

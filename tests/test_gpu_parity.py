@@ -312,6 +312,29 @@ def test_split_k_sixteen_bit(srt, oracle, dtype, M, N, K, batch, ta, tb, splits)
     assert oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype)) <= 2e-3
 
 
+def test_call_cache_slot_reused_by_another_kernel(srt):
+    """The per-thread call cache has 64 slots.  Fill them with split-K launches, then run many
+    distinct strided-kernel calls that land in the same slots: each must behave like a fresh call
+    (no reduce pass of the slot's previous owner)."""
+    torch.manual_seed(3)
+    srt.set_tuning(TC, 0, 0, 0)
+    srt.set_split_k(4)
+    keep = []
+    for i in range(96):
+        a = torch.randn(128, 1024 + 64 * (i % 8), device="cuda:0", dtype=torch.bfloat16)
+        b = torch.randn(a.shape[1], 64 + 8 * (i // 8), device="cuda:0", dtype=torch.bfloat16)
+        keep.append((a, b, srt.matmul(a, b)))
+    srt.set_tuning(SIMT, 0, 0, 0)
+    srt.set_split_k(0)
+    for i in range(192):
+        a = torch.randn(1 + i % 7, 30 + i, device="cuda:0")
+        b = torch.randn(30 + i, 5 + i % 11, device="cuda:0")
+        c = srt.matmul(a, b)
+        ref = a.double() @ b.double()
+        assert torch.allclose(c.double(), ref, rtol=1e-4, atol=1e-4), i
+    torch.cuda.synchronize()
+
+
 def test_split_k_col_order_output_and_strided_view(srt, oracle):
     srt.set_tuning(TC, 0, 0, 0)
     srt.set_split_k(4)

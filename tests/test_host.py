@@ -62,3 +62,52 @@ def test_shard_ranges_partition_the_axis(total, world, align):
     assert all(lo % align == 0 for lo, _ in ranges)
     sizes = [hi - lo for lo, hi in ranges]
     assert max(sizes) - min(s for s in sizes if s or True) <= 2 * align or min(sizes) == 0
+
+
+class _FakePeerBuffer:
+    """The part of PeerBuffer that sharded_matmul uses, over host tensors of one process: the
+    'addresses' of the peers' buffers are the data pointers of the other ranks' tensors."""
+
+    def __init__(self, tensors, rank):
+        self.tensor = tensors[rank]
+        self.peer_base = {r: t.data_ptr() for r, t in enumerate(tensors) if r != rank}
+        self.nbytes = self.tensor.numel() * self.tensor.element_size()
+
+    peer_pointers = __import__("swiftrt_b200").PeerBuffer.peer_pointers
+
+
+@pytest.mark.parametrize("axis,ash,bsh,tl,tr", [("n", (24, 16), (16, 40), False, False),
+                                                 ("m", (26, 16), (16, 12), False, False),
+                                                 ("m", (16, 26), (12, 16), True, True),
+                                                 ("batch", (6, 8, 5), (6, 5, 7), False, False)])
+def test_sharded_matmul_with_peer_buffers_fills_every_rank(axis, ash, bsh, tl, tr):
+    """Every rank's block must land at the same place in every rank's buffer: the view offsets
+    handed to the gathering product are checked by writing through them."""
+    import ctypes
+    import swiftrt_b200 as srt
+    g = torch.Generator().manual_seed(1)
+    a = torch.rand(ash, generator=g)
+    b = torch.rand(bsh, generator=g)
+    want = torch.matmul(a.transpose(-1, -2) if tl else a, b.transpose(-1, -2) if tr else b)
+    world = 3
+    buffers = [torch.full(want.shape, -1.0) for _ in range(world)]
+
+    def gather_fn(view, peer_ptrs, lhs, tl_, rhs, tr_):
+        block = torch.matmul(lhs.transpose(-1, -2) if tl_ else lhs, rhs.transpose(-1, -2) if tr_ else rhs)
+        view.copy_(block)
+        assert len(peer_ptrs) == world - 1
+        for ptr in peer_ptrs:                       # the same view, re-based on a peer's buffer
+            span = 1 + sum((n - 1) * s for n, s in zip(view.shape, view.stride()))
+            raw = (ctypes.c_float * span).from_address(ptr)
+            peer = torch.as_strided(torch.frombuffer(raw, dtype=torch.float32), view.shape, view.stride())
+            peer.copy_(block)
+
+    for rank in range(world):
+        got = srt.sharded_matmul(a, b, tl, tr, axis=axis, rank=rank, world=world,
+                                 peer_buffer=_FakePeerBuffer(buffers, rank), gather_fn=gather_fn)
+        assert got is buffers[rank]
+    for buf in buffers:
+        assert torch.allclose(buf, want, rtol=1e-6, atol=1e-6)
+    with pytest.raises(ValueError):
+        srt.sharded_matmul(a, b, tl, tr, axis=axis, rank=0, world=world,
+                           peer_buffer=_FakePeerBuffer([torch.zeros(2, 2)] * 2, 0), gather_fn=gather_fn)
