@@ -73,6 +73,7 @@ class PeerBuffer:
                     p = ctypes.c_void_p()
                     _check(lib.srtPeerMemOpen(ctypes.byref(h), ctypes.byref(p)))
                     self.peer_base[r] = p.value
+        self._token = None
         self._open = True
 
     def peer_pointers(self, view: torch.Tensor) -> list[int]:
@@ -86,7 +87,11 @@ class PeerBuffer:
         """Orders everything the ranks enqueued so far before what follows on this rank's current
         stream: after it, blocks written by other ranks may be read."""
         if self.world > 1:
-            dist.barrier(group=self.group)
+            # a one-element all-reduce on the current stream: every rank's kernel precedes its
+            # contribution, so what follows on this stream sees all blocks; the host is not blocked
+            if self._token is None:
+                self._token = torch.zeros(1, device=self.device)
+            dist.all_reduce(self._token, group=self.group)
 
     def close(self) -> None:
         """Collective: unmaps the peers' buffers, then frees this rank's."""
