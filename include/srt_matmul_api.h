@@ -230,6 +230,30 @@ cudaError_t srtMatmulNoAlloc(
     void* out, const srtTensorDescriptor* oDesc,
     cudaStream_t stream);
 
+/* srtLstmCell: one time step of an LSTM cell, a caller of the fused product.
+ *
+ * Computes what LSTMCell.callAsFunction composes from separate operators
+ * (Sources/SwiftRTLayers/Recurrent.swift:255-266):
+ *     fused   = matmul(concatenate(input, hidden, axis: 1), fusedWeight, bias: fusedBias)
+ *     i, u, f, o = sigmoid, tanh, sigmoid, sigmoid of the column blocks 0..3 of fused (Part: input,
+ *               update, forget, output; Recurrent.swift:173)
+ *     newCell   = cell * f + i * u
+ *     newHidden = tanh(newCell) * o
+ * input [batch x inputSize], hidden / cell / newCell / newHidden [batch x hiddenSize], fusedWeight
+ * [(inputSize + hiddenSize) x 4 hiddenSize], fusedBias [4 hiddenSize] (may be NULL); all of one element
+ * type, rank 2 (bias rank 1), any strides.  newCell may alias cell and newHidden may alias hidden.
+ * Three launches on `stream`: a concatenation, the product (srtMatmulBiasActivation) and the gate
+ * pass; the two intermediates live in the library's per-(device, stream) workspace. */
+cudaError_t srtLstmCell(
+    const void* input, const srtTensorDescriptor* inputDesc,
+    const void* hidden, const srtTensorDescriptor* hiddenDesc,
+    const void* cell, const srtTensorDescriptor* cellDesc,
+    const void* fusedWeight, const srtTensorDescriptor* weightDesc,
+    const void* fusedBias, const srtTensorDescriptor* biasDesc,
+    void* newCell, const srtTensorDescriptor* newCellDesc,
+    void* newHidden, const srtTensorDescriptor* newHiddenDesc,
+    cudaStream_t stream);
+
 /* ---- several GPUs of one machine, one process per GPU -----------------------------------------
  *
  * The reference has no multi-GPU path: its only data-parallel construct partitions axis 0 of a

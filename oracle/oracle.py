@@ -151,6 +151,36 @@ def bias_activation_backward(dy: np.ndarray, y: np.ndarray, dtype: int, activati
     return dz, dbias
 
 
+def _sigmoid32(x: np.ndarray) -> np.ndarray:
+    """1 / (1 + exp(-x)) in Float32, the reference's definition (cpu/functions/CpuMath.swift:1369-1377)."""
+    x = x.astype(np.float32)
+    return (np.float32(1) / (np.float32(1) + np.exp(-x, dtype=np.float32))).astype(np.float32)
+
+
+def lstm_cell(x: np.ndarray, hidden: np.ndarray, cell: np.ndarray, fused_weight: np.ndarray,
+              fused_bias: np.ndarray | None, dtype: int, stepwise: bool = False):
+    """One step of LSTMCell.callAsFunction (Sources/SwiftRTLayers/Recurrent.swift:255-266) on stored
+    bits: fused = matmul(concatenate(x, hidden), fusedWeight, bias:) through the restated CPU loop,
+    gates i, u, f, o = sigmoid, tanh, sigmoid, sigmoid of its four column blocks, cell' = cell * f +
+    i * u, hidden' = tanh(cell') * o.  Returns (cell', hidden') as stored bits.
+
+    stepwise=False rounds only the tensors the step stores (fused, cell', hidden'); stepwise=True
+    rounds every intermediate tensor to the element type, which is what composing the reference's
+    separate operators does for 16-bit elements (identical for Float32)."""
+    H = hidden.shape[1]
+    gate_in = np.ascontiguousarray(np.concatenate([x, hidden], axis=1))
+    fused = decode(matmul(gate_in, np.ascontiguousarray(fused_weight), dtype, bias=fused_bias), dtype)
+    rnd = (lambda v: decode(encode(v, dtype), dtype)) if stepwise else (lambda v: v.astype(np.float32))
+    gi = rnd(_sigmoid32(fused[:, 0:H]))
+    gu = rnd(np.tanh(fused[:, H:2 * H], dtype=np.float32))
+    gf = rnd(_sigmoid32(fused[:, 2 * H:3 * H]))
+    go = rnd(_sigmoid32(fused[:, 3 * H:4 * H]))
+    c = decode(cell, dtype)
+    new_cell = encode(rnd(c * gf) + rnd(gi * gu), dtype)
+    new_hidden = encode(rnd(np.tanh(decode(new_cell, dtype), dtype=np.float32)) * go, dtype)
+    return new_cell, new_hidden
+
+
 def rel_frobenius(x: np.ndarray, ref: np.ndarray) -> float:
     """||x - ref||_F / ||ref||_F in float64."""
     x = np.asarray(x, dtype=np.float64)

@@ -40,7 +40,7 @@ class MatmulPlan(ctypes.Structure):
 # every symbol include/srt_matmul_api.h declares
 EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString",
-           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree"]
+           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -90,6 +90,9 @@ lib.srtPeerMemClose.restype = ctypes.c_int
 lib.srtPeerMemClose.argtypes = [_P]
 lib.srtPeerMemFree.restype = ctypes.c_int
 lib.srtPeerMemFree.argtypes = [_P]
+
+lib.srtLstmCell.restype = ctypes.c_int
+lib.srtLstmCell.argtypes = [_P, _D] * 7 + [_P]
 
 
 def last_error() -> str:

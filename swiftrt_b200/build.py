@@ -15,7 +15,7 @@ ROOT = os.path.dirname(PKG)
 SO = os.path.join(PKG, "libsrt_b200.so")
 SOURCES = [os.path.join(PKG, "csrc", "srt_matmul.cu")]
 HEADERS = [os.path.join(PKG, "csrc", h) for h in ("ptx.cuh", "gemm_tcgen05.cuh", "gemm_simt.cuh", "gemm_splitk.cuh",
-                                                  "dense_backward.cuh")] + [
+                                                  "dense_backward.cuh", "lstm_cell.cuh")] + [
     os.path.join(ROOT, "include", "srt_matmul_api.h")]
 
 # the explicit -gencode form is required: a bare -arch=sm_100a does not enable tcgen05

@@ -18,6 +18,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_splitk.cuh"
 #include "gemm_tcgen05.cuh"
+#include "lstm_cell.cuh"
 
 namespace {
 
@@ -710,15 +711,17 @@ cudaError_t bind_workspace(Prepared& pr, void* ws)
 
 // Workspaces of split-K launches: one buffer per (device, stream), grown on demand, kept until
 // the process exits.  Kernels of one stream run in order, so a stream never races with itself.
-struct Workspace { int device; cudaStream_t stream; void* ptr; size_t bytes; };
+// `slot` separates buffers that are alive at the same time on one stream (slot 0: split-K partial
+// sums and column-sum partials; slot 1: the LSTM cell's gate input and fused product).
+struct Workspace { int device; cudaStream_t stream; int slot; void* ptr; size_t bytes; };
 std::mutex g_ws_mutex;
 std::vector<Workspace> g_workspaces;
 
-cudaError_t workspace_for(int device, cudaStream_t stream, size_t bytes, void** out)
+cudaError_t workspace_for(int device, cudaStream_t stream, size_t bytes, void** out, int slot = 0)
 {
     std::lock_guard<std::mutex> lock(g_ws_mutex);
     for (Workspace& w : g_workspaces) {
-        if (w.device != device || w.stream != stream) continue;
+        if (w.device != device || w.stream != stream || w.slot != slot) continue;
         if (w.bytes < bytes) {
             cudaError_t e = cudaStreamSynchronize(stream);     // the old buffer may still be in use
             if (e != cudaSuccess) return e;
@@ -731,7 +734,7 @@ cudaError_t workspace_for(int device, cudaStream_t stream, size_t bytes, void** 
         *out = w.ptr;
         return cudaSuccess;
     }
-    Workspace w{device, stream, nullptr, 0};
+    Workspace w{device, stream, slot, nullptr, 0};
     cudaError_t e = cudaMalloc(&w.ptr, bytes);
     if (e != cudaSuccess) return e;
     w.bytes = bytes;
@@ -941,6 +944,37 @@ cudaError_t launch_dense_backward(const DenseBackwardParams& bp, bool vec, uint3
     return e;
 }
 
+// ------------------------------------------------------------------ srtLstmCell helpers
+cudaError_t view2(const srtTensorDescriptor* d, const char* what, srtDataType type, uint64_t& rows, uint64_t& cols,
+                         long long& s_m, long long& s_n)
+{
+    if (!d || !d->shape || !d->strides) return fail(cudaErrorInvalidValue, "srtLstmCell: %s: missing descriptor", what);
+    if (d->rank != 2) return fail(cudaErrorInvalidValue, "srtLstmCell: %s must have rank 2", what);
+    if (d->type != type) return fail(cudaErrorInvalidValue, "srtLstmCell: %s has a different element type", what);
+    rows = d->shape[0]; cols = d->shape[1];
+    s_m = (long long)d->strides[0]; s_n = (long long)d->strides[1];
+    return cudaSuccess;
+}
+
+template <typename T>
+cudaError_t launch_lstm_elementwise(const ConcatParams* cp, const LstmGateParams* gp, cudaStream_t stream)
+{
+    if (cp) {
+        const unsigned long long total = (unsigned long long)cp->rows * (cp->nx + cp->nh);
+        unsigned long long blocks = (total + 255) / 256;
+        if (blocks > 148ull * 8) blocks = 148ull * 8;
+        concat_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(*cp);
+    } else {
+        const unsigned long long total = (unsigned long long)gp->rows * gp->hidden;
+        unsigned long long blocks = (total + 255) / 256;
+        if (blocks > 148ull * 8) blocks = 148ull * 8;
+        lstm_gates_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(*gp);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
 }  // namespace
 
 // ===================================================================== exported entry points
@@ -1130,6 +1164,80 @@ cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor*
     case real16F: return launch_dense_backward<__half>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
     default: return launch_dense_backward<__nv_bfloat16>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
     }
+}
+
+// ------------------------------------------------------------------ srtLstmCell
+cudaError_t srtLstmCell(const void* input, const srtTensorDescriptor* inputDesc, const void* hidden,
+                        const srtTensorDescriptor* hiddenDesc, const void* cell, const srtTensorDescriptor* cellDesc,
+                        const void* fusedWeight, const srtTensorDescriptor* weightDesc, const void* fusedBias,
+                        const srtTensorDescriptor* biasDesc, void* newCell, const srtTensorDescriptor* newCellDesc,
+                        void* newHidden, const srtTensorDescriptor* newHiddenDesc, cudaStream_t stream)
+{
+    if (!input || !hidden || !cell || !fusedWeight || !newCell || !newHidden || !inputDesc)
+        return fail(cudaErrorInvalidValue, "srtLstmCell: null tensor");
+    const srtDataType type = inputDesc->type;
+    if (type != real32F && type != real16F && type != real16BF)
+        return fail(cudaErrorNotSupported, "srtLstmCell: element type %d is outside this library", (int)type);
+    uint64_t rows, nx, r2, nh, r3, c3, wk, wn, r4, c4, r5, c5;
+    long long x_m, x_n, h_m, h_n, c_m, c_n, w_m, w_n, nc_m, nc_n, nh_m, nh_n;
+    cudaError_t e;
+    if ((e = view2(inputDesc, "input", type, rows, nx, x_m, x_n)) != cudaSuccess) return e;
+    if ((e = view2(hiddenDesc, "hidden", type, r2, nh, h_m, h_n)) != cudaSuccess) return e;
+    if ((e = view2(cellDesc, "cell", type, r3, c3, c_m, c_n)) != cudaSuccess) return e;
+    if ((e = view2(weightDesc, "fusedWeight", type, wk, wn, w_m, w_n)) != cudaSuccess) return e;
+    if ((e = view2(newCellDesc, "newCell", type, r4, c4, nc_m, nc_n)) != cudaSuccess) return e;
+    if ((e = view2(newHiddenDesc, "newHidden", type, r5, c5, nh_m, nh_n)) != cudaSuccess) return e;
+    if (r2 != rows || r3 != rows || r4 != rows || r5 != rows || c3 != nh || c4 != nh || c5 != nh)
+        return fail(cudaErrorInvalidValue, "srtLstmCell: state tensors must be [batch x hiddenSize]");
+    if (wk != nx + nh || wn != 4 * nh)
+        return fail(cudaErrorInvalidValue, "srtLstmCell: fusedWeight must be [(inputSize + hiddenSize) x 4 hiddenSize], got %llu x %llu",
+                    (unsigned long long)wk, (unsigned long long)wn);
+    if (fusedBias && (!biasDesc || biasDesc->rank != 1 || biasDesc->shape[0] != 4 * nh || biasDesc->type != type))
+        return fail(cudaErrorInvalidValue, "srtLstmCell: fusedBias must be rank 1 with 4 hiddenSize elements");
+    if (rows == 0 || nh == 0) return cudaSuccess;
+    if (rows > 0xffffffffull || nx + nh > 0xffffffffull || 4 * nh > 0xffffffffull)
+        return fail(cudaErrorNotSupported, "srtLstmCell: extents beyond 32 bits");
+
+    const size_t elem = type == real32F ? 4 : 2;
+    const size_t gate_bytes = ((size_t)rows * (nx + nh) * elem + 255) & ~(size_t)255;
+    const size_t fused_bytes = (size_t)rows * 4 * nh * elem;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    void* ws = nullptr;
+    if ((e = workspace_for(dev, stream, gate_bytes + fused_bytes, &ws, 1)) != cudaSuccess) return e;
+    void* gate_in = ws;
+    void* fused = static_cast<char*>(ws) + gate_bytes;
+
+    ConcatParams cp;
+    cp.x = input; cp.h = hidden; cp.out = gate_in;
+    cp.x_m = x_m; cp.x_n = x_n; cp.h_m = h_m; cp.h_n = h_n;
+    cp.rows = (uint32_t)rows; cp.nx = (uint32_t)nx; cp.nh = (uint32_t)nh;
+    e = type == real32F ? launch_lstm_elementwise<float>(&cp, nullptr, stream)
+        : type == real16F ? launch_lstm_elementwise<__half>(&cp, nullptr, stream)
+                          : launch_lstm_elementwise<__nv_bfloat16>(&cp, nullptr, stream);
+    if (e != cudaSuccess) return e;
+
+    // fused = gateInput . fusedWeight + fusedBias, rounded to the element type (what matmul(bias:) returns)
+    size_t g_shape[2] = {(size_t)rows, (size_t)(nx + nh)}, g_strides[2] = {(size_t)(nx + nh), 1};
+    size_t f_shape[2] = {(size_t)rows, (size_t)(4 * nh)}, f_strides[2] = {(size_t)(4 * nh), 1};
+    srtTensorDescriptor gd, fd;
+    memset(&gd, 0, sizeof gd);
+    gd.type = type; gd.rank = 2; gd.order = srtOrderRow; gd.count = g_shape[0] * g_shape[1]; gd.spanCount = gd.count;
+    gd.shape = g_shape; gd.strides = g_strides; gd.logicalStrides = g_strides;
+    fd = gd;
+    fd.count = f_shape[0] * f_shape[1]; fd.spanCount = fd.count;
+    fd.shape = f_shape; fd.strides = f_strides; fd.logicalStrides = f_strides;
+    e = srtMatmulBiasActivation(gate_in, &gd, false, fusedWeight, weightDesc, false, fusedBias, biasDesc, srtActivationIdentity,
+                                fused, &fd, stream);
+    if (e != cudaSuccess) return e;
+
+    LstmGateParams gp;
+    gp.fused = fused; gp.cell = cell; gp.new_cell = newCell; gp.new_hidden = newHidden;
+    gp.c_m = c_m; gp.c_n = c_n; gp.nc_m = nc_m; gp.nc_n = nc_n; gp.nh_m = nh_m; gp.nh_n = nh_n;
+    gp.rows = (uint32_t)rows; gp.hidden = (uint32_t)nh;
+    return type == real32F ? launch_lstm_elementwise<float>(nullptr, &gp, stream)
+           : type == real16F ? launch_lstm_elementwise<__half>(nullptr, &gp, stream)
+                             : launch_lstm_elementwise<__nv_bfloat16>(nullptr, &gp, stream);
 }
 
 // ------------------------------------------------------------------ srtMatmulNoAlloc

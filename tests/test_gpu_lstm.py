@@ -1,0 +1,130 @@
+"""The LSTM cell step on a B200 (srtLstmCell: concatenation, fused product with bias, gate pass)
+against the reference's golden data and against the CPU oracle."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from _gpu_util import BF16, F16, F32, TOL, from_dev, random_bits, to_dev
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def srt():
+    import swiftrt_b200 as s
+    assert torch.cuda.is_available()
+    return s
+
+
+@pytest.fixture(scope="module")
+def kat():
+    with open(os.path.join(HERE, "golden", "lstm_kat.json")) as f:
+        return json.load(f)
+
+
+def _t(x):
+    return torch.tensor(x, dtype=torch.float32, device="cuda:0")
+
+
+def test_reference_golden_sequence(srt, kat):
+    """Tests/SwiftRTLayerTests/test_Recurrent.swift:47-66 with its data (:97-167): the hidden state
+    after each of the four steps and the final cell state, to the reference's accuracy of 1e-6."""
+    cell = srt.LSTMCell(_t(kat["fused_weight"]), _t(kat["fused_bias"]))
+    assert cell.hidden_size == 4
+    state = srt.LSTMState(_t([kat["initial_cell"]]), _t([kat["initial_hidden"]]))
+    before = srt.launch_count()
+    outputs = srt.run_sequence(cell, [_t([x]) for x in kat["inputs"]], state)
+    torch.cuda.synchronize()
+    assert srt.launch_count() - before == 4 * 3          # concatenation, product, gates per step
+    assert len(outputs) == 4
+    hidden = torch.cat([s.hidden for s in outputs]).cpu().numpy()
+    assert np.abs(hidden - np.array(kat["expected_hidden_per_step"], np.float32)).max() <= kat["accuracy"]
+    assert np.abs(outputs[-1].cell.cpu().numpy()[0] - np.array(kat["expected_final_cell"], np.float32)).max() <= kat["accuracy"]
+
+
+def test_reference_golden_gradients_through_the_gpu_operators(srt, kat):
+    """Back-propagation through the four steps with the library's own pieces -- srtMatmul with
+    transpose flags for x^T.dz and dz.W^T, srtBiasActivationBackward for the bias gradient -- must give
+    the reference's golden gradients of sum(final cell) (test_Recurrent.swift:169-240)."""
+    w, b = _t(kat["fused_weight"]), _t(kat["fused_bias"])
+    H, I = 4, 4
+    c, h = _t([kat["initial_cell"]]), _t([kat["initial_hidden"]])
+    saved = []
+    for x in kat["inputs"]:
+        gate_in = torch.cat([_t([x]), h], dim=1)
+        fused = srt.matmul(gate_in, w, bias=b)
+        gi, gu = torch.sigmoid(fused[:, :H]), torch.tanh(fused[:, H:2 * H])
+        gf, go = torch.sigmoid(fused[:, 2 * H:3 * H]), torch.sigmoid(fused[:, 3 * H:])
+        c_new = c * gf + gi * gu
+        saved.append((gate_in, gi, gu, gf, go, c, c_new))
+        h, c = torch.tanh(c_new) * go, c_new
+    dc, dh = torch.ones_like(c), torch.zeros_like(c)
+    dw, db, dxs = torch.zeros_like(w), torch.zeros_like(b), []
+    for gate_in, gi, gu, gf, go, c_prev, c_new in reversed(saved):
+        t = torch.tanh(c_new)
+        dc = dc + dh * go * (1 - t * t)
+        dfused = torch.cat([dc * gu * gi * (1 - gi), dc * gi * (1 - gu * gu), dc * c_prev * gf * (1 - gf),
+                            dh * t * go * (1 - go)], dim=1).contiguous()
+        dgate, step_dw = srt.matmul_gradients(dfused, gate_in, False, w, False)
+        _, step_db = srt.bias_activation_backward(dfused, None, srt.ActivationType.identity, want_dz=False)
+        dw += step_dw
+        db += step_db
+        dxs.append(dgate[0, :I].clone())
+        dh = dgate[:, I:]
+        dc = dc * gf
+    dxs.reverse()
+    tol = 2e-6
+    assert (dw.cpu().numpy() - np.array(kat["grad_fused_weight"], np.float32)).__abs__().max() <= tol
+    assert (db.cpu().numpy() - np.array(kat["grad_fused_bias"], np.float32)).__abs__().max() <= tol
+    assert (torch.stack(dxs).cpu().numpy() - np.array(kat["grad_inputs"], np.float32)).__abs__().max() <= tol
+    assert (dc.cpu().numpy()[0] - np.array(kat["grad_initial_cell"], np.float32)).__abs__().max() <= tol
+    assert (dh.cpu().numpy()[0] - np.array(kat["grad_initial_hidden"], np.float32)).__abs__().max() <= tol
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("batch,nx,nh", [(3, 5, 7), (64, 96, 128), (256, 512, 512), (1, 1024, 256)])
+def test_cell_step_matches_oracle(srt, oracle, dtype, batch, nx, nh):
+    rng = np.random.default_rng(batch + 3 * nx + 7 * nh + dtype)
+    x = random_bits(oracle, rng, (batch, nx), dtype)
+    h = random_bits(oracle, rng, (batch, nh), dtype)
+    c = random_bits(oracle, rng, (batch, nh), dtype, dist="normal")
+    w = random_bits(oracle, rng, (nx + nh, 4 * nh), dtype, scale=1.0 / np.sqrt(nx + nh))
+    b = random_bits(oracle, rng, (4 * nh,), dtype, scale=0.5)
+    ref_c, ref_h = oracle.lstm_cell(x, h, c, w, b, dtype)
+    cell = srt.LSTMCell(to_dev(w, dtype), to_dev(b, dtype))
+    out = cell(to_dev(x, dtype), srt.LSTMState(to_dev(c, dtype), to_dev(h, dtype)))
+    torch.cuda.synchronize()
+    assert srt.check_status() == 0
+    for got, ref in ((out.cell, ref_c), (out.hidden, ref_h)):
+        err = oracle.rel_frobenius(oracle.decode(from_dev(got, dtype), dtype), oracle.decode(ref, dtype))
+        assert err <= TOL[dtype], err
+    if dtype != F32:
+        # rounding every intermediate, as the composed reference operators would, stays inside the tolerance too
+        step_c, step_h = oracle.lstm_cell(x, h, c, w, b, dtype, stepwise=True)
+        assert oracle.rel_frobenius(oracle.decode(from_dev(out.hidden, dtype), dtype), oracle.decode(step_h, dtype)) <= TOL[dtype]
+
+
+def test_strided_state_views_no_bias_and_argument_errors(srt, oracle):
+    rng = np.random.default_rng(9)
+    batch, nx, nh = 10, 12, 16
+    x = random_bits(oracle, rng, (batch, nx), F32)
+    big_h = random_bits(oracle, rng, (batch, 2 * nh), F32)
+    big_c = random_bits(oracle, rng, (2 * batch, nh), F32)
+    h, c = big_h[:, ::2], big_c[::2]                                   # column stride 2, row stride 2
+    w = random_bits(oracle, rng, (nx + nh, 4 * nh), F32, scale=0.2)
+    ref_c, ref_h = oracle.lstm_cell(x, np.ascontiguousarray(h), np.ascontiguousarray(c), w, None, F32)
+    cell = srt.LSTMCell(to_dev(w, F32), None)
+    out = cell(to_dev(x, F32), srt.LSTMState(to_dev(c, F32), to_dev(h, F32)))
+    assert oracle.rel_frobenius(from_dev(out.cell, F32), ref_c) <= TOL[F32]
+    assert oracle.rel_frobenius(from_dev(out.hidden, F32), ref_h) <= TOL[F32]
+    zero = cell.zero_state(to_dev(x, F32))
+    assert zero.cell.shape == (batch, nh) and float(zero.hidden.abs().sum()) == 0.0
+    with pytest.raises(srt.MatmulError) as e:
+        cell(to_dev(x[:, :5].copy(), F32), srt.LSTMState(to_dev(c, F32), to_dev(h, F32)))      # inputSize mismatch
+    assert e.value.code == 1 and "fusedWeight" in str(e.value)
+    with pytest.raises(ValueError):
+        srt.LSTMCell(to_dev(w[:, :30].copy(), F32), None)

@@ -198,3 +198,78 @@ def test_bias_activation_backward_restatement(oracle, dtype, act):
         assert np.array_equal(db_step, db)          # fp32 elements: rounding every row IS the fp32 running sum
     else:
         assert oracle.rel_frobenius(oracle.decode(db_step, dtype), oracle.decode(db, dtype)) < 0.1
+
+
+# ------------------------------------------------------------------ LSTM cell: the reference's golden data
+def _lstm_kat():
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "lstm_kat.json")) as f:
+        return json.load(f)
+
+
+def test_lstm_cell_restatement_reproduces_reference_golden_states(oracle):
+    """Four time steps with the reference's weights, bias and initial state
+    (Tests/SwiftRTLayerTests/test_Recurrent.swift:97-167): hidden state after every step and the
+    final cell state, to the reference's own accuracy of 1e-6.  This pins matmul(bias:)."""
+    k = _lstm_kat()
+    w = np.array(k["fused_weight"], np.float32)
+    b = np.array(k["fused_bias"], np.float32)
+    c = np.array([k["initial_cell"]], np.float32)
+    h = np.array([k["initial_hidden"]], np.float32)
+    for step, x in enumerate(k["inputs"]):
+        c, h = oracle.lstm_cell(np.array([x], np.float32), h, c, w, b, 0)
+        assert np.abs(h[0] - np.array(k["expected_hidden_per_step"][step], np.float32)).max() <= k["accuracy"]
+    assert np.abs(c[0] - np.array(k["expected_final_cell"], np.float32)).max() <= k["accuracy"]
+    # Float32: rounding every intermediate changes nothing
+    c2, h2 = oracle.lstm_cell(np.array([k["inputs"][0]], np.float32), np.array([k["initial_hidden"]], np.float32),
+                              np.array([k["initial_cell"]], np.float32), w, b, 0, stepwise=True)
+    c1, h1 = oracle.lstm_cell(np.array([k["inputs"][0]], np.float32), np.array([k["initial_hidden"]], np.float32),
+                              np.array([k["initial_cell"]], np.float32), w, b, 0)
+    assert np.array_equal(c1, c2) and np.array_equal(h1, h2)
+
+
+def test_lstm_golden_gradients_pin_the_backward_restatements(oracle):
+    """Back-propagation through the four steps, built from the oracle's own pieces -- the two
+    transposed products of matmulGradients and the bias gradient as a column sum
+    (oracle_bias_activation_backward) -- must reproduce the reference's golden gradients of
+    sum(final cell) (test_Recurrent.swift:169-240)."""
+    k = _lstm_kat()
+    F32 = 0
+    w = np.array(k["fused_weight"], np.float32)
+    b = np.array(k["fused_bias"], np.float32)
+    H, I = 4, 4
+    c = np.array([k["initial_cell"]], np.float32)
+    h = np.array([k["initial_hidden"]], np.float32)
+    sig = lambda v: (1 / (1 + np.exp(-v.astype(np.float64)))).astype(np.float32)
+    saved = []
+    for x in k["inputs"]:
+        gate_in = np.concatenate([np.array([x], np.float32), h], axis=1)
+        fused = oracle.matmul(np.ascontiguousarray(gate_in), w, F32, bias=b)
+        gi, gu, gf, go = sig(fused[:, :H]), np.tanh(fused[:, H:2 * H]), sig(fused[:, 2 * H:3 * H]), sig(fused[:, 3 * H:])
+        c_new = c * gf + gi * gu
+        saved.append((gate_in, gi, gu, gf, go, c, c_new))
+        h = np.tanh(c_new) * go
+        c = c_new
+    dc = np.ones((1, H), np.float32)
+    dh = np.zeros((1, H), np.float32)
+    dw = np.zeros_like(w)
+    db = np.zeros_like(b)
+    dxs = []
+    for gate_in, gi, gu, gf, go, c_prev, c_new in reversed(saved):
+        t = np.tanh(c_new)
+        dc = dc + dh * go * (1 - t * t)
+        dfused = np.concatenate([dc * gu * gi * (1 - gi), dc * gi * (1 - gu * gu), dc * c_prev * gf * (1 - gf),
+                                 dh * t * go * (1 - go)], axis=1).astype(np.float32)
+        dw += oracle.matmul(np.ascontiguousarray(gate_in), dfused, F32, True, False)        # x^T . dz
+        _, step_db = oracle.bias_activation_backward(dfused, dfused, F32, "identity")       # column sums
+        db += step_db
+        dgate = oracle.matmul(dfused, w, F32, False, True)                                  # dz . W^T
+        dxs.append(dgate[0, :I])
+        dh = dgate[:, I:]
+        dc = dc * gf
+    dxs.reverse()
+    tol = 2e-6
+    assert np.abs(dw - np.array(k["grad_fused_weight"], np.float32)).max() <= tol
+    assert np.abs(db - np.array(k["grad_fused_bias"], np.float32)).max() <= tol
+    assert np.abs(np.array(dxs) - np.array(k["grad_inputs"], np.float32)).max() <= tol
+    assert np.abs(dc[0] - np.array(k["grad_initial_cell"], np.float32)).max() <= tol
+    assert np.abs(dh[0] - np.array(k["grad_initial_hidden"], np.float32)).max() <= tol
