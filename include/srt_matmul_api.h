@@ -196,6 +196,30 @@ cudaError_t srtMatmulQueryPlan(
  * tileN: 64, 128 or 256; stages: 2..8; maxCtas: cap on the persistent grid. */
 cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas);
 
+/* srtMatmulTune: measures, for this exact call, every kernel and tile width the element type allows
+ * (the cost model's own choice first), keeps the fastest in the process's plan table and leaves
+ * `out` holding the product.  Later calls with the same signature -- sizes, element type, which
+ * strides are 1, bias or not -- use the tuned choice whenever no process-wide tuning is set.
+ * Stands in for MatmulAlgorithm.search and its timing loop
+ * (Sources/SwiftRTCore/platform/cuda/cublaslt/MatmulAlgorithmSearch.swift:128-216).
+ * Synchronises `stream` (it times with events on it).  `best` and `bestMicroseconds` may be NULL. */
+cudaError_t srtMatmulTune(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* bias, const srtTensorDescriptor* biasDesc,
+    srtActivationType activation,
+    void* out, const srtTensorDescriptor* oDesc,
+    cudaStream_t stream, srtMatmulPlan* best, float* bestMicroseconds);
+
+/* The plan table as a text file (one line per tuned signature), so that tuning survives the
+ * process: Save writes all entries, Load merges a file into the table (`entries`, if not NULL,
+ * receives the number read), Clear empties the table.  A file named by the environment variable
+ * SRT_MATMUL_PLAN_CACHE is loaded before the first plan is made.  Entries are specific to the GPU
+ * model they were measured on. */
+cudaError_t srtMatmulPlanCacheSave(const char* path);
+cudaError_t srtMatmulPlanCacheLoad(const char* path, int32_t* entries);
+cudaError_t srtMatmulPlanCacheClear(void);
+
 /* Split-K override, process-wide: 0 = automatic (Float32 with K > 2048; few tiles with a long
  * reduction), 1 = never, n > 1 = cut the reduction into (up to) n parts whenever the tensor-core
  * kernel for one CTA per tile runs.  The fp32 partial sums live in a workspace that the library

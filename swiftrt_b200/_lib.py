@@ -40,7 +40,8 @@ class MatmulPlan(ctypes.Structure):
 # every symbol include/srt_matmul_api.h declares
 EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString",
-           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell"]
+           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell",
+           "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -93,6 +94,15 @@ lib.srtPeerMemFree.argtypes = [_P]
 
 lib.srtLstmCell.restype = ctypes.c_int
 lib.srtLstmCell.argtypes = [_P, _D] * 7 + [_P]
+lib.srtMatmulTune.restype = ctypes.c_int
+lib.srtMatmulTune.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_int, _P, _D, _P,
+                              ctypes.POINTER(MatmulPlan), ctypes.POINTER(ctypes.c_float)]
+lib.srtMatmulPlanCacheSave.restype = ctypes.c_int
+lib.srtMatmulPlanCacheSave.argtypes = [ctypes.c_char_p]
+lib.srtMatmulPlanCacheLoad.restype = ctypes.c_int
+lib.srtMatmulPlanCacheLoad.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32)]
+lib.srtMatmulPlanCacheClear.restype = ctypes.c_int
+lib.srtMatmulPlanCacheClear.argtypes = []
 
 
 def last_error() -> str:

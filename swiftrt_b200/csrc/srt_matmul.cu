@@ -149,6 +149,75 @@ cudaError_t parse(const void* a, const srtTensorDescriptor* ad, bool ta,
 }
 
 // ------------------------------------------------------------------ per-device state
+// ------------------------------------------------------------------ tuning choices and the plan table
+// What the planner may be told instead of deciding by its cost model: 0 = decide.
+struct Choice { int32_t force, tile_n, stages, max_ctas, split_k; };
+
+// Set by srtMatmulTune while it times a candidate on this thread.
+thread_local const Choice* t_choice_override = nullptr;
+
+// Tuned choices by problem signature: sizes, element type and which strides are 1 (majorness of
+// the operands and order of the output).  Filled by srtMatmulTune / srtMatmulPlanCacheLoad and
+// consulted whenever no process-wide tuning is set.
+struct PlanKey {
+    int32_t type;
+    uint32_t flags;                // bit 0 a_k == 1, 1 a_m == 1, 2 b_n == 1, 3 b_k == 1, 4 o_n == 1, 5 o_m == 1, 6 bias
+    uint64_t M, N, K, batch;
+};
+struct PlanEntry { PlanKey key; Choice choice; float us; };
+std::mutex g_plan_mutex;
+std::vector<PlanEntry> g_plan_table;
+std::atomic<uint32_t> g_plan_epoch{0};      // part of the call-cache key: bumps invalidate cached launches
+std::once_flag g_plan_env_once;
+
+PlanKey plan_key(const Problem& P)
+{
+    PlanKey k;
+    memset(&k, 0, sizeof k);
+    k.type = (int32_t)P.type;
+    k.flags = (P.a_k == 1 ? 1u : 0u) | (P.a_m == 1 ? 2u : 0u) | (P.b_n == 1 ? 4u : 0u) | (P.b_k == 1 ? 8u : 0u) |
+              (P.o_n == 1 ? 16u : 0u) | (P.o_m == 1 ? 32u : 0u) | (P.bias ? 64u : 0u);
+    k.M = P.M; k.N = P.N; k.K = P.K; k.batch = P.batch;
+    return k;
+}
+
+int plan_table_load(const char* path);      // defined with the entry points
+
+bool plan_lookup(const Problem& P, Choice& out)
+{
+    std::call_once(g_plan_env_once, [] {
+        const char* path = getenv("SRT_MATMUL_PLAN_CACHE");
+        if (path && *path) plan_table_load(path);
+    });
+    const PlanKey k = plan_key(P);
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (const PlanEntry& e : g_plan_table)
+        if (memcmp(&e.key, &k, sizeof k) == 0) { out = e.choice; return true; }
+    return false;
+}
+
+void plan_store(const PlanKey& k, const Choice& c, float us)
+{
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (PlanEntry& e : g_plan_table)
+        if (memcmp(&e.key, &k, sizeof k) == 0) { e.choice = c; e.us = us; return; }
+    g_plan_table.push_back(PlanEntry{k, c, us});
+}
+
+// The choice a plan is made under: the tuner's candidate, else the process-wide tuning, else a
+// tuned entry of the plan table, else all zeros (the cost model decides).
+Choice effective_choice(const Problem& P)
+{
+    if (t_choice_override) return *t_choice_override;
+    Choice c = {g_tuning.force_kernel.load(), g_tuning.tile_n.load(), g_tuning.stages.load(), g_tuning.max_ctas.load(),
+                g_tuning.split_k.load()};
+    if (c.force == 0 && c.tile_n == 0 && c.stages == 0 && c.max_ctas == 0 && c.split_k == 0) {
+        Choice tuned;
+        if (plan_lookup(P, tuned)) return tuned;
+    }
+    return c;
+}
+
 struct DeviceInfo {
     int sms = 0;
     bool sm100 = false;
@@ -241,7 +310,8 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     plan.Q = P;
     plan.swapped = false;
     plan.bias_mode = P.bias ? 1 : 0;
-    const int32_t force = g_tuning.force_kernel.load();
+    const Choice choice = effective_choice(P);
+    const int32_t force = choice.force;
 
     bool tc = dev.sm100 && force != srtMatmulKernelSimt;
     // the tensor-core path writes rows of contiguous columns; a col-order out is computed
@@ -294,7 +364,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     }
 
     plan.Q = Q;
-    uint32_t bn = (uint32_t)g_tuning.tile_n.load();
+    uint32_t bn = (uint32_t)choice.tile_n;
     // Tile choice by a small cost model: time ~ waves x (time of one tile).  A 128 x BN tile costs
     // BN / efficiency(BN) (narrow MMAs re-read A more often per flop); a CTA pair's 256 x BN tile
     // costs about the same as one CTA's 128 x BN tile and fills the device with half as many tiles.
@@ -339,7 +409,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     static const bool tf32_single = getenv("SRT_MATMUL_TF32_SINGLE") != nullptr;   // experiment knob: 1 x TF32
     const bool split3 = split && !tf32_single;
     const uint32_t stage_bytes = (kATileBytes + (pair ? bn / 2 : bn) * kRowBytes) * (split3 ? 2 : 1);
-    uint32_t stages = (uint32_t)g_tuning.stages.load();
+    uint32_t stages = (uint32_t)choice.stages;
     uint32_t max_stages = (227u * 1024u - 2048u - kEpilogueStagingBytes) / stage_bytes;
     if (split3 && max_stages > 4) max_stages = 4;
     // Four 32 KB stages keep the pair kernel's MMAs fed; deeper rings measured slower on a
@@ -353,7 +423,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     // give every SM work.  Partial sums go to an fp32 workspace [split][batch][M][N].
     const uint32_t k_blocks = (uint32_t)((Q.K + kb_elems - 1) / kb_elems);
     uint32_t splits = 1, kb_per_split = k_blocks;
-    const int32_t want_split = g_tuning.split_k.load();
+    const int32_t want_split = choice.split_k;
     if (!pair && want_split != 1) {
         uint32_t target = 1;
         if (want_split > 1) target = (uint32_t)want_split;
@@ -392,7 +462,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     const uint64_t work_units = tiles * splits;
     const uint64_t units = pair ? (uint64_t)dev.sms / 2 : (uint64_t)dev.sms;   // CTAs or CTA pairs
     uint32_t ctas = (uint32_t)(work_units < units ? work_units : units);
-    const int32_t cap = g_tuning.max_ctas.load();
+    const int32_t cap = choice.max_ctas;
     if (cap > 0 && ctas > (uint32_t)cap) ctas = (uint32_t)cap;
     if (pair) ctas *= 2;
 
@@ -873,6 +943,8 @@ struct CallKey {
     Problem P;
     int32_t force, tile_n, stages, max_ctas, split_k;
     int32_t device;
+    uint32_t plan_epoch;
+    uint32_t pad;
 };
 
 constexpr int kCallCacheSize = 64;
@@ -944,6 +1016,85 @@ cudaError_t launch_dense_backward(const DenseBackwardParams& bp, bool vec, uint3
     return e;
 }
 
+// ------------------------------------------------------------------ plan table: file form and tuner
+// One text line per entry:
+//   type flags M N K batch  force tileN stages maxCtas splitK  microseconds
+// under a header line.  Lines that do not parse are skipped.
+constexpr const char* kPlanFileHeader = "srt_matmul_plan_cache v1";
+
+int plan_table_load(const char* path)
+{
+    FILE* f = fopen(path, "r");
+    if (!f) return -1;
+    char line[512];
+    int loaded = 0;
+    bool header_ok = false;
+    while (fgets(line, sizeof line, f)) {
+        if (!header_ok) {
+            if (strncmp(line, kPlanFileHeader, strlen(kPlanFileHeader)) != 0) { fclose(f); return -2; }
+            header_ok = true;
+            continue;
+        }
+        if (line[0] == '#' || line[0] == '\n') continue;
+        PlanKey k;
+        memset(&k, 0, sizeof k);
+        Choice c;
+        float us = 0.0f;
+        unsigned long long M, N, K, batch;
+        if (sscanf(line, "%d %u %llu %llu %llu %llu %d %d %d %d %d %f", &k.type, &k.flags, &M, &N, &K, &batch, &c.force, &c.tile_n,
+                   &c.stages, &c.max_ctas, &c.split_k, &us) != 12)
+            continue;
+        if (c.force < 0 || c.force > srtMatmulKernelTcgen05Split) continue;
+        k.M = M; k.N = N; k.K = K; k.batch = batch;
+        plan_store(k, c, us);
+        ++loaded;
+    }
+    fclose(f);
+    if (!header_ok) return -2;
+    g_plan_epoch.fetch_add(1, std::memory_order_relaxed);
+    return loaded;
+}
+
+int plan_table_save(const char* path)
+{
+    FILE* f = fopen(path, "w");
+    if (!f) return -1;
+    fprintf(f, "%s\n# type flags M N K batch  force tileN stages maxCtas splitK  microseconds\n", kPlanFileHeader);
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (const PlanEntry& e : g_plan_table)
+        fprintf(f, "%d %u %llu %llu %llu %llu %d %d %d %d %d %.3f\n", e.key.type, e.key.flags, (unsigned long long)e.key.M,
+                (unsigned long long)e.key.N, (unsigned long long)e.key.K, (unsigned long long)e.key.batch, e.choice.force,
+                e.choice.tile_n, e.choice.stages, e.choice.max_ctas, e.choice.split_k, e.us);
+    const int n = (int)g_plan_table.size();
+    fclose(f);
+    return n;
+}
+
+// Average device time of one launch of `pr` on `stream`, in microseconds (events on that stream).
+cudaError_t time_prepared(Prepared& pr, cudaStream_t stream, cudaEvent_t e0, cudaEvent_t e1, float& us)
+{
+    cudaError_t e = launch_prepared(pr, stream);               // warm-up: attributes, workspace, caches
+    if (e != cudaSuccess) return e;
+    if ((e = cudaEventRecord(e0, stream)) != cudaSuccess) return e;
+    if ((e = launch_prepared(pr, stream)) != cudaSuccess) return e;
+    if ((e = cudaEventRecord(e1, stream)) != cudaSuccess) return e;
+    if ((e = cudaEventSynchronize(e1)) != cudaSuccess) return e;
+    float ms = 0.0f;
+    if ((e = cudaEventElapsedTime(&ms, e0, e1)) != cudaSuccess) return e;
+    // as many repetitions as fit in ~10 ms, between 3 and 50
+    int reps = ms > 0.0f ? (int)(10.0f / ms) : 50;
+    if (reps < 3) reps = 3;
+    if (reps > 50) reps = 50;
+    if ((e = cudaEventRecord(e0, stream)) != cudaSuccess) return e;
+    for (int i = 0; i < reps; ++i)
+        if ((e = launch_prepared(pr, stream)) != cudaSuccess) return e;
+    if ((e = cudaEventRecord(e1, stream)) != cudaSuccess) return e;
+    if ((e = cudaEventSynchronize(e1)) != cudaSuccess) return e;
+    if ((e = cudaEventElapsedTime(&ms, e0, e1)) != cudaSuccess) return e;
+    us = ms * 1000.0f / (float)reps;
+    return cudaSuccess;
+}
+
 // ------------------------------------------------------------------ srtLstmCell helpers
 cudaError_t view2(const srtTensorDescriptor* d, const char* what, srtDataType type, uint64_t& rows, uint64_t& cols,
                          long long& s_m, long long& s_n)
@@ -999,6 +1150,7 @@ cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aD
     key.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
     key.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
     key.device = dev;
+    key.plan_epoch = g_plan_epoch.load(std::memory_order_relaxed);
     if (!t_cache) t_cache = new CallCache();
     const int slot = (int)(hash_key(key) % kCallCacheSize);
     if (t_cache->valid[slot] && memcmp(&t_cache->key[slot], &key, sizeof key) == 0)
@@ -1059,6 +1211,101 @@ cudaError_t srtMatmulSetSplitK(int32_t splits)
 {
     if (splits < 0 || splits > 64) return fail(cudaErrorInvalidValue, "splits must be 0 (automatic) or 1..64");
     g_tuning.split_k = splits;
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulTune(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                          const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                          const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                          const srtTensorDescriptor* oDesc, cudaStream_t stream, srtMatmulPlan* best, float* bestMicroseconds)
+{
+    Problem P;
+    memset(&P, 0, sizeof P);
+    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
+    if (e != cudaSuccess) return e;
+    // candidates: the cost model's own choice first, then every kernel / tile width the type allows
+    std::vector<Choice> cands;
+    cands.push_back(Choice{0, 0, 0, 0, 0});
+    if (P.type == real32F) {
+        cands.push_back(Choice{srtMatmulKernelSimt, 0, 0, 0, 0});
+        for (int32_t tn : {64, 128, 256}) cands.push_back(Choice{srtMatmulKernelTcgen05Split, tn, 0, 0, 0});
+    } else {
+        for (int32_t tn : {64, 128, 256}) {
+            cands.push_back(Choice{srtMatmulKernelTcgen05, tn, 0, 0, 0});
+            cands.push_back(Choice{srtMatmulKernelTcgen05, tn, 0, 0, 1});        // the same without split-K
+        }
+        for (int32_t tn : {128, 256}) cands.push_back(Choice{srtMatmulKernelTcgen05Pair, tn, 0, 0, 0});
+    }
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if ((e = cudaEventCreate(&e0)) != cudaSuccess) return e;
+    if ((e = cudaEventCreate(&e1)) != cudaSuccess) { cudaEventDestroy(e0); return e; }
+    std::vector<srtMatmulPlan> seen;
+    float best_us = 0.0f;
+    Choice best_choice = cands[0];
+    srtMatmulPlan best_plan;
+    memset(&best_plan, 0, sizeof best_plan);
+    bool have = false;
+    Prepared* pr = new Prepared();
+    for (const Choice& c : cands) {
+        t_choice_override = &c;
+        Plan plan;
+        e = plan_for(P, plan);
+        t_choice_override = nullptr;
+        if (e != cudaSuccess) break;
+        bool dup = false;
+        for (const srtMatmulPlan& s : seen) dup = dup || memcmp(&s, &plan.pub, sizeof s) == 0;
+        if (dup) continue;
+        seen.push_back(plan.pub);
+        e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, *pr) : prepare_tc(plan, *pr);
+        if (e != cudaSuccess) break;
+        float us = 0.0f;
+        e = time_prepared(*pr, stream, e0, e1, us);
+        if (e != cudaSuccess) break;
+        if (!have || us < best_us) { have = true; best_us = us; best_choice = c; best_plan = plan.pub; }
+    }
+    delete pr;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e != cudaSuccess) return e;
+    if (!have) return fail(cudaErrorUnknown, "srtMatmulTune: no candidate ran");
+    // pin what the winner actually ran, so that a later change of the cost model cannot alter it
+    best_choice.force = best_plan.kernel;
+    if (best_plan.kernel != srtMatmulKernelSimt) {
+        best_choice.tile_n = best_plan.tileN;
+        best_choice.stages = best_plan.stages;
+        if (best_choice.split_k == 0 && best_plan.splitK <= 1) best_choice.split_k = 1;
+    }
+    plan_store(plan_key(P), best_choice, best_us);
+    g_plan_epoch.fetch_add(1, std::memory_order_relaxed);
+    if (best) *best = best_plan;
+    if (bestMicroseconds) *bestMicroseconds = best_us;
+    // leave `out` holding the product computed by the chosen plan
+    return srtMatmulBiasActivation(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, activation, out, oDesc, stream);
+}
+
+cudaError_t srtMatmulPlanCacheSave(const char* path)
+{
+    if (!path) return fail(cudaErrorInvalidValue, "srtMatmulPlanCacheSave: null path");
+    return plan_table_save(path) >= 0 ? cudaSuccess : fail(cudaErrorInvalidValue, "srtMatmulPlanCacheSave: cannot write %s", path);
+}
+
+cudaError_t srtMatmulPlanCacheLoad(const char* path, int32_t* entries)
+{
+    if (!path) return fail(cudaErrorInvalidValue, "srtMatmulPlanCacheLoad: null path");
+    const int n = plan_table_load(path);
+    if (n == -1) return fail(cudaErrorInvalidValue, "srtMatmulPlanCacheLoad: cannot read %s", path);
+    if (n == -2) return fail(cudaErrorInvalidValue, "srtMatmulPlanCacheLoad: %s is not a plan cache file", path);
+    if (entries) *entries = n;
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulPlanCacheClear(void)
+{
+    {
+        std::lock_guard<std::mutex> lock(g_plan_mutex);
+        g_plan_table.clear();
+    }
+    g_plan_epoch.fetch_add(1, std::memory_order_relaxed);
     return cudaSuccess;
 }
 
@@ -1389,6 +1636,7 @@ cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, 
     key.call.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
     key.call.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
     key.call.device = dev;
+    key.call.plan_epoch = g_plan_epoch.load(std::memory_order_relaxed);
     key.count = peerCount;
     for (int32_t i = 0; i < peerCount; ++i) {
         if (!peerOut[i]) return fail(cudaErrorInvalidValue, "srtMatmulAllGather: peerOut[%d] is null", i);

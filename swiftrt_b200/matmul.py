@@ -243,6 +243,48 @@ def query_plan(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, transpos
     return {name: getattr(plan, name) for name, _ in plan._fields_}
 
 
+def tune(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, transposed_lhs: bool = False,
+         transposed_rhs: bool = False, bias: torch.Tensor | None = None,
+         activation: ActivationType | None = None) -> dict:
+    """Times every kernel / tile width for this call and keeps the fastest for later calls with the
+    same signature (srtMatmulTune; stands in for MatmulAlgorithm.search,
+    cublaslt/MatmulAlgorithmSearch.swift:128-216).  Returns the winning plan plus its time
+    ("microseconds"); `out` holds the product afterwards."""
+    plan = _lib.MatmulPlan()
+    us = ctypes.c_float()
+    da, db, do = Descriptor(lhs), Descriptor(rhs), Descriptor(out)
+    dbias = Descriptor(bias) if bias is not None else None
+    with torch.cuda.device(out.device):
+        rc = lib.srtMatmulTune(lhs.data_ptr(), da.ref(), transposed_lhs, rhs.data_ptr(), db.ref(), transposed_rhs,
+                               bias.data_ptr() if bias is not None else None, dbias.ref() if dbias is not None else None,
+                               int(activation if activation is not None else ActivationType.identity),
+                               out.data_ptr(), do.ref(), torch.cuda.current_stream(out.device).cuda_stream,
+                               ctypes.byref(plan), ctypes.byref(us))
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+    result = {name: getattr(plan, name) for name, _ in plan._fields_}
+    result["microseconds"] = float(us.value)
+    return result
+
+
+def save_plan_cache(path: str) -> None:
+    """Writes the tuned plans to a text file (srtMatmulPlanCacheSave)."""
+    if lib.srtMatmulPlanCacheSave(str(path).encode()) != _lib.cudaSuccess:
+        raise MatmulError(_lib.cudaErrorInvalidValue, _lib.last_error())
+
+
+def load_plan_cache(path: str) -> int:
+    """Merges a plan cache file into the process's table; returns the number of entries read."""
+    n = ctypes.c_int32()
+    if lib.srtMatmulPlanCacheLoad(str(path).encode(), ctypes.byref(n)) != _lib.cudaSuccess:
+        raise MatmulError(_lib.cudaErrorInvalidValue, _lib.last_error())
+    return int(n.value)
+
+
+def clear_plan_cache() -> None:
+    lib.srtMatmulPlanCacheClear()
+
+
 def set_tuning(force_kernel: int = 0, tile_n: int = 0, stages: int = 0, max_ctas: int = 0) -> None:
     rc = lib.srtMatmulSetTuning(force_kernel, tile_n, stages, max_ctas)
     if rc != _lib.cudaSuccess:

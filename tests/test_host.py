@@ -111,3 +111,31 @@ def test_sharded_matmul_with_peer_buffers_fills_every_rank(axis, ash, bsh, tl, t
     with pytest.raises(ValueError):
         srt.sharded_matmul(a, b, tl, tr, axis=axis, rank=0, world=world,
                            peer_buffer=_FakePeerBuffer([torch.zeros(2, 2)] * 2, 0), gather_fn=gather_fn)
+
+
+def test_plan_cache_file_round_trip_without_a_gpu(tmp_path):
+    """The plan table's file form: load merges entries (bad lines are skipped, a wrong header is
+    refused), save writes them back, clear empties the table."""
+    import swiftrt_b200 as srt
+    srt.clear_plan_cache()
+    src = tmp_path / "plans.txt"
+    src.write_text("srt_matmul_plan_cache v1\n# comment\n"
+                   "14 85 1024 4096 4096 1 3 256 4 0 1 29.5\n"
+                   "0 21 65536 256 1024 1 4 128 3 0 1 184.0\n"
+                   "not a plan line\n"
+                   "14 85 1024 4096 4096 1 2 128 6 0 1 31.0\n")       # same signature again: the later line wins
+    assert srt.load_plan_cache(str(src)) == 3
+    dst = tmp_path / "out.txt"
+    srt.save_plan_cache(str(dst))
+    lines = [l for l in dst.read_text().splitlines() if l and not l.startswith("#")]
+    assert lines[0] == "srt_matmul_plan_cache v1"
+    assert sorted(lines[1:]) == sorted(["14 85 1024 4096 4096 1 2 128 6 0 1 31.000", "0 21 65536 256 1024 1 4 128 3 0 1 184.000"])
+    bad = tmp_path / "bad.txt"
+    bad.write_text("something else\n1 2 3\n")
+    with pytest.raises(srt.MatmulError):
+        srt.load_plan_cache(str(bad))
+    with pytest.raises(srt.MatmulError):
+        srt.load_plan_cache(str(tmp_path / "missing.txt"))
+    srt.clear_plan_cache()
+    srt.save_plan_cache(str(dst))
+    assert [l for l in dst.read_text().splitlines() if l and not l.startswith("#")] == ["srt_matmul_plan_cache v1"]
