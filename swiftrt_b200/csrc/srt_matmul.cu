@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <vector>
 
@@ -953,7 +954,7 @@ struct CallCache {
     CallKey key[kCallCacheSize];
     Prepared value[kCallCacheSize];
 };
-thread_local CallCache* t_cache = nullptr;
+thread_local std::unique_ptr<CallCache> t_cache;
 
 uint64_t hash_key(const CallKey& k)
 {
@@ -1151,7 +1152,7 @@ cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aD
     key.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
     key.device = dev;
     key.plan_epoch = g_plan_epoch.load(std::memory_order_relaxed);
-    if (!t_cache) t_cache = new CallCache();
+    if (!t_cache) t_cache.reset(new CallCache());
     const int slot = (int)(hash_key(key) % kCallCacheSize);
     if (t_cache->valid[slot] && memcmp(&t_cache->key[slot], &key, sizeof key) == 0)
         return launch_prepared(t_cache->value[slot], stream);
@@ -1587,7 +1588,7 @@ struct GatherEntry {
     PeerMaps maps;
 };
 constexpr int kGatherCacheSize = 8;
-static thread_local GatherEntry* t_gather = nullptr;
+static thread_local std::unique_ptr<GatherEntry[]> t_gather;
 
 static cudaError_t copy_view_to_peers(const Problem& P, const srtTensorDescriptor* oDesc, const void* out, int32_t count,
                                void* const* peers, cudaStream_t stream)
@@ -1642,7 +1643,7 @@ cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, 
         if (!peerOut[i]) return fail(cudaErrorInvalidValue, "srtMatmulAllGather: peerOut[%d] is null", i);
         key.peers[i] = peerOut[i];
     }
-    if (!t_gather) t_gather = new GatherEntry[kGatherCacheSize];
+    if (!t_gather) t_gather.reset(new GatherEntry[kGatherCacheSize]);
     GatherEntry& ent = t_gather[hash_key(key.call) % kGatherCacheSize];
     if (!(ent.valid && memcmp(&ent.key, &key, sizeof key) == 0)) {
         ent.valid = false;

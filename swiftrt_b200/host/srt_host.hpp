@@ -9,6 +9,7 @@
 //   matmul(..., bias:)                                    operators/Matmul.swift:57-72
 //   matmulGradients                                       differentiable/MathDerivatives.swift:460-482
 //   Dense                                                 Sources/SwiftRTLayers/Dense.swift:21-71
+//   LSTMCell, its State and the time-step loop            Sources/SwiftRTLayers/Recurrent.swift:165-266, 346-370
 // Header-only; link against libsrt_b200.so and the CUDA runtime.  Every product runs on the GPU
 // through srtMatmul*; there is no host fallback.
 #pragma once
@@ -269,5 +270,55 @@ struct Dense {
         return matmul(input, false, weight, false, bias, activation, stream);
     }
 };
+
+// LSTMCell (Recurrent.swift:165-266): fusedWeight [(inputSize + hiddenSize) x 4 hiddenSize], fusedBias
+// [4 hiddenSize]; one call is one time step through srtLstmCell.
+template <typename E>
+struct LSTMCell {
+    struct State { Tensor<E> cell, hidden; };
+    Tensor<E> fusedWeight, fusedBias;
+    size_t hiddenSize;
+    LSTMCell(Tensor<E> fusedWeight_, Tensor<E> fusedBias_)
+        : fusedWeight(std::move(fusedWeight_)), fusedBias(std::move(fusedBias_)), hiddenSize(fusedWeight.shape[1] / 4)
+    {
+        if (fusedWeight.rank() != 2 || fusedWeight.shape[1] % 4 != 0 || fusedBias.rank() != 1 ||
+            fusedBias.shape[0] != fusedWeight.shape[1])
+            throw Error(cudaErrorInvalidValue, "fusedWeight is [(inputSize + hiddenSize) x 4 hiddenSize], fusedBias [4 hiddenSize]");
+    }
+    // zeroState(for:) (Recurrent.swift:245-248)
+    State zeroState(const Tensor<E>& input) const
+    {
+        State s{Tensor<E>({input.shape[0], hiddenSize}), Tensor<E>({input.shape[0], hiddenSize})};
+        s.cell.assign(std::vector<float>(s.cell.count(), 0.0f));
+        s.hidden.assign(std::vector<float>(s.hidden.count(), 0.0f));
+        return s;
+    }
+    State operator()(const Tensor<E>& input, const State& state, cudaStream_t stream = nullptr) const
+    {
+        State next{Tensor<E>({input.shape[0], hiddenSize}), Tensor<E>({input.shape[0], hiddenSize})};
+        const srtTensorDescriptor x = input.descriptor(), h = state.hidden.descriptor(), c = state.cell.descriptor(),
+                                  w = fusedWeight.descriptor(), b = fusedBias.descriptor(), nc = next.cell.descriptor(),
+                                  nh = next.hidden.descriptor();
+        check(srtLstmCell(input.data(), &x, state.hidden.data(), &h, state.cell.data(), &c, fusedWeight.data(), &w,
+                          fusedBias.data(), &b, next.cell.data(), &nc, next.hidden.data(), &nh, stream),
+              "srtLstmCell");
+        return next;
+    }
+};
+
+// RecurrentLayer.callAsFunction(_:initialState:) (Recurrent.swift:356-370)
+template <typename E>
+std::vector<typename LSTMCell<E>::State> runSequence(const LSTMCell<E>& cell, const std::vector<Tensor<E>>& inputs,
+                                                     const typename LSTMCell<E>::State& initialState,
+                                                     cudaStream_t stream = nullptr)
+{
+    std::vector<typename LSTMCell<E>::State> outputs;
+    typename LSTMCell<E>::State state = initialState;
+    for (const Tensor<E>& x : inputs) {
+        state = cell(x, state, stream);
+        outputs.push_back(state);
+    }
+    return outputs;
+}
 
 }  // namespace srt_host

@@ -1,8 +1,14 @@
 // The reference's matmul tests, restated over the C++ host mirror (swiftrt_b200/host/srt_host.hpp),
 // which calls the CUDA library through its C ABI.  Literals: Tests/SwiftRTCoreTests/
 // test_AlgebraicField.swift:551-645 (test_matmul is live there, the batched ones are commented out
-// but numerically valid).  Exit code 0 = all checks passed; needs a GPU.
+// but numerically valid), and the LSTM golden sequence of Tests/SwiftRTLayerTests/test_Recurrent.swift.
+// Argument: path of tests/golden/lstm_kat.json.  Exit code 0 = all checks passed; needs a GPU.
+#include <cmath>
 #include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <sstream>
+#include <string>
 #include <vector>
 
 #include "srt_host.hpp"
@@ -88,7 +94,62 @@ static void test_dense_and_errors()
     EXPECT(threw);
 }
 
-int main()
+// All numbers of the (possibly nested) array stored under `key` in a JSON text, flattened.
+static std::vector<float> json_numbers(const std::string& text, const std::string& key)
+{
+    std::vector<float> out;
+    size_t pos = text.find("\"" + key + "\"");
+    if (pos == std::string::npos) return out;
+    pos = text.find('[', pos);
+    int depth = 0;
+    for (size_t i = pos; i < text.size(); ++i) {
+        const char ch = text[i];
+        if (ch == '[') ++depth;
+        else if (ch == ']') { if (--depth == 0) break; }
+        else if (ch == '-' || (ch >= '0' && ch <= '9')) {
+            char* end = nullptr;
+            out.push_back(std::strtof(text.c_str() + i, &end));
+            i = static_cast<size_t>(end - text.c_str()) - 1;
+        }
+    }
+    return out;
+}
+
+// The reference's LSTM golden data (Tests/SwiftRTLayerTests/test_Recurrent.swift:97-167), read from the
+// fixture next to the Python tests: four time steps, hidden state after each, final cell state, to 1e-6.
+static void test_lstm_golden_sequence(const char* fixture)
+{
+    std::ifstream in(fixture);
+    EXPECT(in.good());
+    if (!in.good()) return;
+    std::stringstream buf;
+    buf << in.rdbuf();
+    const std::string text = buf.str();
+    const auto inputs = json_numbers(text, "inputs"), w = json_numbers(text, "fused_weight"), b = json_numbers(text, "fused_bias"),
+               c0 = json_numbers(text, "initial_cell"), h0 = json_numbers(text, "initial_hidden"),
+               want_h = json_numbers(text, "expected_hidden_per_step"), want_c = json_numbers(text, "expected_final_cell");
+    EXPECT(inputs.size() == 16 && w.size() == 128 && b.size() == 16 && want_h.size() == 16 && want_c.size() == 4);
+    if (failures) return;
+    LSTMCell<float> cell(array(w, {8, 16}), array(b, {16}));
+    EXPECT(cell.hiddenSize == 4);
+    std::vector<Tensor<float>> steps;
+    for (int t = 0; t < 4; ++t) steps.push_back(array(std::vector<float>(inputs.begin() + 4 * t, inputs.begin() + 4 * t + 4), {1, 4}));
+    LSTMCell<float>::State init{array(c0, {1, 4}), array(h0, {1, 4})};
+    const auto outputs = runSequence(cell, steps, init);
+    EXPECT(outputs.size() == 4);
+    float worst = 0.0f;
+    for (int t = 0; t < 4; ++t) {
+        const auto h = outputs[t].hidden.values();
+        for (int j = 0; j < 4; ++j) worst = std::fmax(worst, std::fabs(h[j] - want_h[4 * t + j]));
+    }
+    const auto c = outputs.back().cell.values();
+    for (int j = 0; j < 4; ++j) worst = std::fmax(worst, std::fabs(c[j] - want_c[j]));
+    EXPECT(worst <= 1e-6f);
+    const auto zero = cell.zeroState(steps[0]);
+    EXPECT(zero.cell.shape == std::vector<size_t>({1, 4}) && zero.hidden.values() == std::vector<float>(4, 0.0f));
+}
+
+int main(int argc, char** argv)
 {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { std::printf("no CUDA device\n"); return 2; }
@@ -97,6 +158,7 @@ int main()
     test_leftAndRightBatchMatmul();
     test_transposes_orders_and_types();
     test_dense_and_errors();
+    test_lstm_golden_sequence(argc > 1 ? argv[1] : "tests/golden/lstm_kat.json");
     uint32_t status = 1;
     EXPECT(srtMatmulCheckStatus(nullptr, &status) == cudaSuccess && status == 0);
     std::printf(failures ? "%d check(s) FAILED\n" : "all host-mirror checks passed (%d failures)\n", failures);

@@ -17,6 +17,7 @@ def test_cpp_host_mirror_known_answers():
         b = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(b)
         b.build_host_test()
-    res = subprocess.run([binary], capture_output=True, text=True, timeout=300)
+    fixture = os.path.join(ROOT, "tests", "golden", "lstm_kat.json")
+    res = subprocess.run([binary, fixture], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "all host-mirror checks passed" in res.stdout
