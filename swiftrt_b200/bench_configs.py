@@ -113,6 +113,60 @@ def run(cfg: dict, iters: int, flush: torch.Tensor, peaks: dict, autotune: bool 
     return rec
 
 
+def _time_cold(fn, iters: int, flush: torch.Tensor) -> tuple[float, float]:
+    """Median and best device time (ms) of fn() after an L2 flush, over `iters` runs."""
+    sink = torch.zeros((), dtype=torch.float32, device=flush.device)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        sink.copy_(flush.sum())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def run_backward(dev, iters: int, flush: torch.Tensor, peaks: dict, rows: int = 16384, cols: int = 8192) -> dict:
+    """f1: srtBiasActivationBackward, bf16 [rows x cols], ReLU: reads dy and y, writes dz (+ column sums)."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    dy = torch.randn((rows, cols), device=dev, generator=g).to(torch.bfloat16)
+    y = torch.relu(torch.randn((rows, cols), device=dev, generator=g)).to(torch.bfloat16)
+    med, best = _time_cold(lambda: srt.bias_activation_backward(dy, y, srt.ActivationType.relu), iters, flush)
+    nbytes = 3 * dy.numel() * 2 + cols * 2
+    rec = {"config": "f1", "what": f"bias/activation backward bf16 [{rows}x{cols}] ReLU (dz and dbias)",
+           "kernel": "dense_backward_kernel + dense_backward_finish_kernel", "ms_median": med, "ms_best": best,
+           "algorithmic_bytes": nbytes, "gbs": nbytes / med / 1e6, "bound": "hbm", "frac_of_nominal": nbytes / med / 1e6 / NOMINAL["hbm_gbs"]}
+    if "hbm_gbs" in peaks:
+        rec["frac_of_measured"] = rec["gbs"] / peaks["hbm_gbs"]
+    return rec
+
+
+def run_lstm(dev, iters: int, flush: torch.Tensor, peaks: dict, batch: int = 4096, nx: int = 1024, nh: int = 1024) -> dict:
+    """f4: one LSTM cell step, bf16: concatenation, fused product [batch x (nx+nh)].[(nx+nh) x 4nh] + bias, gate pass."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf16 = torch.bfloat16
+    x = _uniform((batch, nx), bf16, dev, g, -1, 1)
+    state = srt.LSTMState(_uniform((batch, nh), bf16, dev, g, -1, 1), _uniform((batch, nh), bf16, dev, g, -1, 1))
+    cell = srt.LSTMCell(_uniform((nx + nh, 4 * nh), bf16, dev, g, -0.03, 0.03), _uniform((4 * nh,), bf16, dev, g, -0.5, 0.5))
+    med, best = _time_cold(lambda: cell(x, state), iters, flush)
+    flops = 2.0 * batch * (nx + nh) * 4 * nh
+    # each tensor once: x, h, c, W, b in; c', h' out (the concatenated input and the fused product are intermediates)
+    nbytes = 2 * (batch * nx + 2 * batch * nh + (nx + nh) * 4 * nh + 4 * nh + 2 * batch * nh)
+    rec = {"config": "f4", "what": f"LSTM cell step bf16 batch {batch}, input {nx}, hidden {nh}",
+           "kernel": "concat_kernel + gemm + lstm_gates_kernel", "ms_median": med, "ms_best": best,
+           "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": flops / med / 1e9, "gbs": nbytes / med / 1e6,
+           "bound": "tensor", "frac_of_nominal": flops / med / 1e9 / NOMINAL["bf16_tflops"]}
+    if "bf16_tflops" in peaks:
+        rec["frac_of_measured"] = rec["tflops"] / peaks["bf16_tflops"]
+    return rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
@@ -126,8 +180,14 @@ def main():
         srt.set_tuning(*[int(x) for x in args.tune.split(",")])
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
     peaks = measured_peaks()
+    only = args.only.split(",") if args.only else []
+    # the callers either side of the product are measured on request only (--only f1,f4)
+    if "f1" in only:
+        print(json.dumps(run_backward(dev, args.iters, flush, peaks)), flush=True)
+    if "f4" in only:
+        print(json.dumps(run_lstm(dev, args.iters, flush, peaks)), flush=True)
     for make in configs(dev):
-        if args.only and make.__name__ not in args.only.split(","):
+        if only and make.__name__ not in only:
             continue
         cfg = make()
         print(json.dumps(run(cfg, args.iters, flush, peaks, args.autotune)), flush=True)

@@ -20,20 +20,38 @@ struct ConcatParams {
     uint32_t rows, nx, nh;
 };
 
-template <typename T>
+// VEC elements (16 bytes) per thread when both inputs are row-contiguous and 16-byte aligned and
+// nx, nh are multiples of VEC; otherwise VEC = 1 with arbitrary strides.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 concat_kernel(const ConcatParams p)
 {
-    const uint32_t width = p.nx + p.nh;
-    const unsigned long long total = static_cast<unsigned long long>(p.rows) * width;
-    for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total; i += gridDim.x * 256ull) {
-        const uint32_t r = static_cast<uint32_t>(i / width), c = static_cast<uint32_t>(i % width);
-        const T* src = c < p.nx ? static_cast<const T*>(p.x) + static_cast<long long>(r) * p.x_m + static_cast<long long>(c) * p.x_n
-                                : static_cast<const T*>(p.h) + static_cast<long long>(r) * p.h_m +
-                                      static_cast<long long>(c - p.nx) * p.h_n;
-        static_cast<T*>(p.out)[i] = *src;
+    const uint32_t wx = p.nx / VEC, wh = p.nh / VEC, width = wx + wh;      // chunks per output row
+    const T* x = static_cast<const T*>(p.x);
+    const T* h = static_cast<const T*>(p.h);
+    T* out = static_cast<T*>(p.out);
+    for (uint32_t r = blockIdx.x; r < p.rows; r += gridDim.x) {
+        T* orow = out + static_cast<unsigned long long>(r) * (p.nx + p.nh);
+        for (uint32_t c = threadIdx.x; c < width; c += 256) {
+            if constexpr (VEC > 1) {
+                const T* src = c < wx ? x + static_cast<long long>(r) * p.x_m + static_cast<long long>(c) * VEC
+                                      : h + static_cast<long long>(r) * p.h_m + static_cast<long long>(c - wx) * VEC;
+                *reinterpret_cast<uint4*>(orow + static_cast<unsigned long long>(c) * VEC) = *reinterpret_cast<const uint4*>(src);
+            } else {
+                orow[c] = c < wx ? x[static_cast<long long>(r) * p.x_m + static_cast<long long>(c) * p.x_n]
+                                 : h[static_cast<long long>(r) * p.h_m + static_cast<long long>(c - wx) * p.h_n];
+            }
+        }
     }
 }
+
+// Gate nonlinearities.  Float32 uses the library functions (the reference's golden LSTM states are
+// pinned to 1e-6); for 16-bit elements, whose rounding step is 2^-9 or 2^-12 of the value, the
+// hardware exponential (relative error ~1e-6) is exact enough and several times cheaper.
+template <typename T> __device__ __forceinline__ float gate_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+template <> __device__ __forceinline__ float gate_sigmoid<float>(float x) { return apply_activation(kActSigmoid, x); }
+template <typename T> __device__ __forceinline__ float gate_tanh(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
+template <> __device__ __forceinline__ float gate_tanh<float>(float x) { return apply_activation(kActTanh, x); }
 
 struct LstmGateParams {
     const void* fused;                           // dense [rows x 4 hidden]: input | update | forget | output
@@ -42,24 +60,55 @@ struct LstmGateParams {
     uint32_t rows, hidden;
 };
 
-template <typename T>
+// One thread per VEC consecutive hidden units of one row (VEC = 16 bytes' worth when the state
+// tensors are row-contiguous and aligned, else 1).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 lstm_gates_kernel(const LstmGateParams p)
 {
-    const unsigned long long total = static_cast<unsigned long long>(p.rows) * p.hidden;
+    const uint32_t hchunks = p.hidden / VEC;
+    const uint32_t rows_per_pass = 256 / (hchunks < 256 ? hchunks : 256);       // >= 1
     const T* fused = static_cast<const T*>(p.fused);
-    for (unsigned long long idx = blockIdx.x * 256ull + threadIdx.x; idx < total; idx += gridDim.x * 256ull) {
-        const uint32_t r = static_cast<uint32_t>(idx / p.hidden), j = static_cast<uint32_t>(idx % p.hidden);
-        const T* row = fused + static_cast<unsigned long long>(r) * 4 * p.hidden;
-        const float gi = apply_activation(kActSigmoid, to_float<T>(row[j]));
-        const float gu = apply_activation(kActTanh, to_float<T>(row[p.hidden + j]));
-        const float gf = apply_activation(kActSigmoid, to_float<T>(row[2 * p.hidden + j]));
-        const float go = apply_activation(kActSigmoid, to_float<T>(row[3 * p.hidden + j]));
-        const float c = to_float<T>(static_cast<const T*>(p.cell)[static_cast<long long>(r) * p.c_m + static_cast<long long>(j) * p.c_n]);
-        const T nc = from_float<T>(__fadd_rn(__fmul_rn(c, gf), __fmul_rn(gi, gu)));
-        static_cast<T*>(p.new_cell)[static_cast<long long>(r) * p.nc_m + static_cast<long long>(j) * p.nc_n] = nc;
-        const float nh = __fmul_rn(apply_activation(kActTanh, to_float<T>(nc)), go);
-        static_cast<T*>(p.new_hidden)[static_cast<long long>(r) * p.nh_m + static_cast<long long>(j) * p.nh_n] = from_float<T>(nh);
+    const T* cell = static_cast<const T*>(p.cell);
+    T* new_cell = static_cast<T*>(p.new_cell);
+    T* new_hidden = static_cast<T*>(p.new_hidden);
+    // a block walks row groups; inside a group thread t owns (row t / hchunks, chunk t % hchunks) when a
+    // row is narrower than the block, else chunks t, t + 256, ... of one row
+    for (uint32_t r0 = blockIdx.x * rows_per_pass; r0 < p.rows; r0 += gridDim.x * rows_per_pass) {
+        const uint32_t sub = hchunks < 256 ? threadIdx.x / hchunks : 0;
+        const uint32_t r = r0 + sub;
+        if (sub >= rows_per_pass || r >= p.rows) continue;
+        const T* frow = fused + static_cast<unsigned long long>(r) * 4 * p.hidden;
+        for (uint32_t ch = hchunks < 256 ? threadIdx.x % hchunks : threadIdx.x; ch < hchunks; ch += 256) {
+            const uint32_t j0 = ch * VEC;
+            __align__(16) T gi[VEC], gu[VEC], gf[VEC], go[VEC], c[VEC], nc[VEC], nh[VEC];
+            if constexpr (VEC > 1) {
+                *reinterpret_cast<uint4*>(gi) = *reinterpret_cast<const uint4*>(frow + j0);
+                *reinterpret_cast<uint4*>(gu) = *reinterpret_cast<const uint4*>(frow + p.hidden + j0);
+                *reinterpret_cast<uint4*>(gf) = *reinterpret_cast<const uint4*>(frow + 2 * p.hidden + j0);
+                *reinterpret_cast<uint4*>(go) = *reinterpret_cast<const uint4*>(frow + 3 * p.hidden + j0);
+                *reinterpret_cast<uint4*>(c) = *reinterpret_cast<const uint4*>(cell + static_cast<long long>(r) * p.c_m + j0);
+            } else {
+                gi[0] = frow[j0]; gu[0] = frow[p.hidden + j0]; gf[0] = frow[2 * p.hidden + j0]; go[0] = frow[3 * p.hidden + j0];
+                c[0] = cell[static_cast<long long>(r) * p.c_m + static_cast<long long>(j0) * p.c_n];
+            }
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                const float i = gate_sigmoid<T>(to_float<T>(gi[v]));
+                const float u = gate_tanh<T>(to_float<T>(gu[v]));
+                const float f = gate_sigmoid<T>(to_float<T>(gf[v]));
+                const float o = gate_sigmoid<T>(to_float<T>(go[v]));
+                nc[v] = from_float<T>(__fadd_rn(__fmul_rn(to_float<T>(c[v]), f), __fmul_rn(i, u)));
+                nh[v] = from_float<T>(__fmul_rn(gate_tanh<T>(to_float<T>(nc[v])), o));
+            }
+            if constexpr (VEC > 1) {
+                *reinterpret_cast<uint4*>(new_cell + static_cast<long long>(r) * p.nc_m + j0) = *reinterpret_cast<const uint4*>(nc);
+                *reinterpret_cast<uint4*>(new_hidden + static_cast<long long>(r) * p.nh_m + j0) = *reinterpret_cast<const uint4*>(nh);
+            } else {
+                new_cell[static_cast<long long>(r) * p.nc_m + static_cast<long long>(j0) * p.nc_n] = nc[0];
+                new_hidden[static_cast<long long>(r) * p.nh_m + static_cast<long long>(j0) * p.nh_n] = nh[0];
+            }
+        }
     }
 }
 

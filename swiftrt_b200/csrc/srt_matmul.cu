@@ -1108,19 +1108,31 @@ cudaError_t view2(const srtTensorDescriptor* d, const char* what, srtDataType ty
     return cudaSuccess;
 }
 
+inline bool aligned16(const void* p, long long row_stride_elems, size_t elem)
+{
+    return reinterpret_cast<uintptr_t>(p) % 16 == 0 && (row_stride_elems * (long long)elem) % 16 == 0;
+}
+
 template <typename T>
 cudaError_t launch_lstm_elementwise(const ConcatParams* cp, const LstmGateParams* gp, cudaStream_t stream)
 {
+    constexpr int kVec = 16 / sizeof(T);
     if (cp) {
-        const unsigned long long total = (unsigned long long)cp->rows * (cp->nx + cp->nh);
-        unsigned long long blocks = (total + 255) / 256;
-        if (blocks > 148ull * 8) blocks = 148ull * 8;
-        concat_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(*cp);
+        const bool vec = cp->x_n == 1 && cp->h_n == 1 && cp->nx % kVec == 0 && cp->nh % kVec == 0 &&
+                         aligned16(cp->x, cp->x_m, sizeof(T)) && aligned16(cp->h, cp->h_m, sizeof(T));
+        unsigned blocks = cp->rows < 148u * 16 ? cp->rows : 148u * 16;
+        if (vec) concat_kernel<T, kVec><<<blocks, 256, 0, stream>>>(*cp);
+        else     concat_kernel<T, 1><<<blocks, 256, 0, stream>>>(*cp);
     } else {
-        const unsigned long long total = (unsigned long long)gp->rows * gp->hidden;
-        unsigned long long blocks = (total + 255) / 256;
-        if (blocks > 148ull * 8) blocks = 148ull * 8;
-        lstm_gates_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(*gp);
+        const bool vec = gp->hidden % kVec == 0 && gp->c_n == 1 && gp->nc_n == 1 && gp->nh_n == 1 &&
+                         aligned16(gp->cell, gp->c_m, sizeof(T)) && aligned16(gp->new_cell, gp->nc_m, sizeof(T)) &&
+                         aligned16(gp->new_hidden, gp->nh_m, sizeof(T));
+        const uint32_t hchunks = vec ? gp->hidden / kVec : gp->hidden;
+        const uint32_t rows_per_pass = 256 / (hchunks < 256 ? hchunks : 256);
+        unsigned long long groups = ((unsigned long long)gp->rows + rows_per_pass - 1) / rows_per_pass;
+        unsigned blocks = (unsigned)(groups < 148ull * 16 ? groups : 148ull * 16);
+        if (vec) lstm_gates_kernel<T, kVec><<<blocks, 256, 0, stream>>>(*gp);
+        else     lstm_gates_kernel<T, 1><<<blocks, 256, 0, stream>>>(*gp);
     }
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
