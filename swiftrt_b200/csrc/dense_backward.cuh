@@ -58,31 +58,44 @@ dense_backward_kernel(const DenseBackwardParams p)
     for (int j = 0; j < VEC; ++j) sum[j] = 0.0f;
 
     if (col0 < p.N) {
-        for (unsigned long long r = r_begin + warp; r < r_end; r += 8) {
-            const uint32_t b = static_cast<uint32_t>(r / p.M), m = static_cast<uint32_t>(r % p.M);
-            const long long o_dy = b * p.dy_b + m * p.dy_m + static_cast<long long>(col0) * p.dy_n;
-            const long long o_y = b * p.y_b + m * p.y_m + static_cast<long long>(col0) * p.y_n;
-            const long long o_dz = b * p.dz_b + m * p.dz_m + static_cast<long long>(col0) * p.dz_n;
-            __align__(16) T g[VEC];
-            __align__(16) T o[VEC];
-            __align__(16) T d[VEC];
-            if constexpr (VEC > 1) {
-                *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(dy + o_dy);
-                if (y) *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(y + o_y);
-            } else {
-                g[0] = dy[o_dy];
-                if (y) o[0] = y[o_y];
+        // two rows per iteration: both rows' loads are issued before either row is used
+        for (unsigned long long r = r_begin + warp; r < r_end; r += 16) {
+            __align__(16) T g[2][VEC];
+            __align__(16) T o[2][VEC];
+            long long o_dz[2];
+            bool live[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const unsigned long long ru = r + 8ull * u;
+                live[u] = ru < r_end;
+                if (!live[u]) continue;
+                const uint32_t b = static_cast<uint32_t>(ru / p.M), m = static_cast<uint32_t>(ru % p.M);
+                const long long o_dy = b * p.dy_b + m * p.dy_m + static_cast<long long>(col0) * p.dy_n;
+                const long long o_y = b * p.y_b + m * p.y_m + static_cast<long long>(col0) * p.y_n;
+                o_dz[u] = b * p.dz_b + m * p.dz_m + static_cast<long long>(col0) * p.dz_n;
+                if constexpr (VEC > 1) {
+                    *reinterpret_cast<uint4*>(g[u]) = *reinterpret_cast<const uint4*>(dy + o_dy);
+                    if (y) *reinterpret_cast<uint4*>(o[u]) = *reinterpret_cast<const uint4*>(y + o_y);
+                } else {
+                    g[u][0] = dy[o_dy];
+                    if (y) o[u][0] = y[o_y];
+                }
             }
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) {
-                const float gf = to_float<T>(g[j]);
-                const float df = y ? activation_grad(p.act, gf, to_float<T>(o[j])) : gf;
-                d[j] = from_float<T>(df);
-                sum[j] = __fadd_rn(sum[j], to_float<T>(d[j]));
-            }
-            if (dz) {
-                if constexpr (VEC > 1) *reinterpret_cast<uint4*>(dz + o_dz) = *reinterpret_cast<const uint4*>(d);
-                else dz[o_dz] = d[0];
+            for (int u = 0; u < 2; ++u) {
+                if (!live[u]) continue;
+                __align__(16) T d[VEC];
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    const float gf = to_float<T>(g[u][j]);
+                    const float df = y ? activation_grad(p.act, gf, to_float<T>(o[u][j])) : gf;
+                    d[j] = from_float<T>(df);
+                    sum[j] = __fadd_rn(sum[j], to_float<T>(d[j]));
+                }
+                if (dz) {
+                    if constexpr (VEC > 1) *reinterpret_cast<uint4*>(dz + o_dz[u]) = *reinterpret_cast<const uint4*>(d);
+                    else dz[o_dz[u]] = d[0];
+                }
             }
         }
     }

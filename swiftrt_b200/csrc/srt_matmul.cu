@@ -1406,7 +1406,8 @@ cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor*
     // enough blocks to fill the device a few times over, at least 8 rows (one per warp) per chunk
     const uint64_t rows = vg.batch * vg.M;
     const uint64_t col_blocks = (vg.N + 32 * (vec ? vecw : 1) - 1) / (32 * (vec ? vecw : 1));
-    uint64_t chunks = ((uint64_t)info.sms * 4 + col_blocks - 1) / col_blocks;
+    // one wave of 6 blocks per SM (40 registers x 256 threads): as many row loads in flight as fit
+    uint64_t chunks = ((uint64_t)info.sms * 6) / col_blocks;
     if (chunks > (rows + 7) / 8) chunks = (rows + 7) / 8;
     if (chunks < 1) chunks = 1;
     if (chunks > 65535) chunks = 65535;
