@@ -72,3 +72,47 @@ def run_sequence(cell: LSTMCell, inputs: Sequence[torch.Tensor], initial_state: 
         state = cell(x, state)
         outputs.append(state)
     return outputs
+
+
+class GraphedSequence:
+    """A fixed number of time steps of one cell captured into a CUDA graph: short sequences of
+    small cells are bound by their 3 launches per step, and a replay enqueues all of them at once.
+
+    The cell's weights, the step count, batch and sizes are fixed at construction.  Inputs and the
+    initial state are copied into the graph's static buffers on every call; the returned states
+    are the graph's static outputs (overwritten by the next call).  The capture runs on a private
+    side stream, which also owns the library workspace the captured launches use."""
+
+    def __init__(self, cell: LSTMCell, steps: int, batch: int, input_size: int, dtype: torch.dtype,
+                 device: torch.device | str | None = None):
+        device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.cell = cell
+        self.inputs = [torch.zeros((batch, input_size), dtype=dtype, device=device) for _ in range(steps)]
+        self.initial = LSTMState(torch.zeros((batch, cell.hidden_size), dtype=dtype, device=device),
+                                 torch.zeros((batch, cell.hidden_size), dtype=dtype, device=device))
+        self._stream = torch.cuda.Stream(device=device)
+        current = torch.cuda.current_stream(device)
+        self._stream.wait_stream(current)
+        with torch.cuda.stream(self._stream):
+            # everything that allocates or sets attributes happens here, outside the capture:
+            # the workspace of this stream, kernel attributes, the planner's device query
+            run_sequence(cell, self.inputs, self.initial)
+        self._stream.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=self._stream):
+            self.outputs = run_sequence(cell, self.inputs, self.initial)
+        current.wait_stream(self._stream)
+
+    def __call__(self, inputs: Sequence[torch.Tensor], initial_state: LSTMState | None = None) -> list[LSTMState]:
+        if len(inputs) != len(self.inputs):
+            raise ValueError(f"captured for {len(self.inputs)} time steps")
+        for dst, src in zip(self.inputs, inputs):
+            dst.copy_(src)
+        if initial_state is None:
+            self.initial.cell.zero_()
+            self.initial.hidden.zero_()
+        else:
+            self.initial.cell.copy_(initial_state.cell)
+            self.initial.hidden.copy_(initial_state.hidden)
+        self.graph.replay()
+        return self.outputs
