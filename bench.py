@@ -216,8 +216,20 @@ def measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier):
     def nccl_step():
         srt.sharded_matmul(a, b_full, axis="n", gather=True, out=full)
 
+    # the same through an NVLink multicast mapping: each tile leaves the GPU once, the switch replicates it
+    mbuf = srt.PeerBuffer((M, N), a.dtype, multicast=True)
+    mview = mbuf.tensor.narrow(1, lo, hi - lo)
+    legs = [("fused", fused_step), ("nccl", nccl_step)]
+    if mbuf.multicast_base:
+        mc_op = srt.MatmulOp(mview, a, False, b_full[:, lo:hi], False, multicast_pointer=mbuf.multicast_pointer(mview))
+
+        def multicast_step():
+            mc_op()
+            mbuf.ranks_done()
+        legs.insert(1, ("fused_multicast", multicast_step))
+
     out = {"steps": steps, "bytes_sent_per_rank": int((world - 1) * M * (hi - lo) * a.element_size())}
-    for name, fn in (("fused", fused_step), ("nccl", nccl_step)):
+    for name, fn in legs:
         for _ in range(3):
             fn()
         barrier()
@@ -233,10 +245,11 @@ def measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier):
         out[name + "_ms"] = ms
         out[name + "_tflops"] = flops / (ms * 1e-3) / 1e12
     status = srt.check_status()
-    same = torch.equal(buf.tensor, full)
+    same = torch.equal(buf.tensor, full) and (not mbuf.multicast_base or torch.equal(mbuf.tensor, full))
     flag = torch.tensor([1 if (same and status == 0) else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     out["results_identical"] = bool(int(flag.item()))
+    mbuf.close()
     buf.close()
     return out
 

@@ -321,6 +321,25 @@ cudaError_t srtMatmulAllGather(
     int32_t peerCount, void* const* peerOut,
     cudaStream_t stream);
 
+/* srtMatmulAllGatherMulticast: the same delivery through an NVLink multicast (NVLS) mapping.
+ *
+ * `multicastOut` is the first element of the output view in a multicast mapping of the full-size
+ * buffers of all ranks (every rank's buffer bound to one multicast object, e.g. the multicast_ptr of
+ * torch.distributed._symmetric_memory); `out` is the same view in this rank's own buffer.  The
+ * epilogue stores each tile once with multimem.st and the NVSwitch replicates it into every rank's
+ * buffer, this rank's included, so each byte leaves the GPU once instead of once per peer.
+ * Only for products that run on the CTA-pair kernel with a 16-byte aligned, row-contiguous output
+ * whose rows are a multiple of 16 bytes long; anything else returns cudaErrorNotSupported and the
+ * caller uses srtMatmulAllGather.  Completion as for srtMatmulAllGather. */
+cudaError_t srtMatmulAllGatherMulticast(
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* bias, const srtTensorDescriptor* biasDesc,
+    srtActivationType activation,
+    void* out, const srtTensorDescriptor* oDesc,
+    void* multicastOut,
+    cudaStream_t stream);
+
 /* Device-side status of the last tensor-core launches on the current device: 0 = all
  * pipeline waits completed; non-zero = a bounded wait gave up (the code says which) and
  * the result of that launch is invalid.  Synchronises `stream` and resets the status. */

@@ -5,7 +5,8 @@ raises if it has not been built: there is no CPU or PyTorch fallback."""
 from ._lib import EXPORTS, SO  # noqa: F401  (raises ImportError when the library is missing)
 from .dense import Dense, bias_activation_backward  # noqa: F401
 from .matmul import (MatmulError, MatmulOp, check_status, launch_count, matmul, matmul_gradients,  # noqa: F401
-                     clear_plan_cache, load_plan_cache, matmul_all_gather_into, matmul_host, matmul_into, query_plan,
+                     clear_plan_cache, load_plan_cache, matmul_all_gather_into,
+                     matmul_all_gather_multicast_into, matmul_host, matmul_into, query_plan,
                      save_plan_cache, set_split_k, set_tuning, tune)
 from .tensor import ActivationType, DataType, Order, empty, order_of  # noqa: F401
 

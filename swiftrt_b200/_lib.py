@@ -41,7 +41,7 @@ class MatmulPlan(ctypes.Structure):
 EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString",
            "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell",
-           "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear"]
+           "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -83,6 +83,8 @@ class PeerMemHandle(ctypes.Structure):
 lib.srtMatmulAllGather.restype = ctypes.c_int
 lib.srtMatmulAllGather.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_int, _P, _D,
                                    ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p), _P]
+lib.srtMatmulAllGatherMulticast.restype = ctypes.c_int
+lib.srtMatmulAllGatherMulticast.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_int, _P, _D, _P, _P]
 lib.srtPeerMemAlloc.restype = ctypes.c_int
 lib.srtPeerMemAlloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(PeerMemHandle)]
 lib.srtPeerMemOpen.restype = ctypes.c_int

@@ -79,6 +79,7 @@ struct GemmParams {
     uint32_t out_vec_ok;         // 16-byte vector stores are aligned for every full chunk
     uint32_t out_tma;            // the output view is TMA-addressable: bulk tensor stores from shared memory
     uint32_t n_peers;            // gathering kernels only: peer copies of the output view (<= kMaxPeers)
+    uint32_t multicast;          // gathering kernels only: 1 = the result goes to a multicast mapping instead (no per-peer stores)
 };
 
 enum : uint32_t { kActSigmoid = 0, kActRelu = 1, kActTanh = 2, kActIdentity = 5, kActGelu = 6, kActGeluTanh = 7 };
@@ -223,9 +224,12 @@ constexpr uint32_t kEpilogueStagingBytes = 8 * 4096;         // 8 warps x (32 ro
 // GATHER: every staged segment is also stored through the tensor maps of `peers` (the same view
 // in the output buffers of other GPUs, mapped into this process), so that all of them hold the
 // tile when the kernel has finished.  Bulk tensor STORES to peer memory only; nothing is loaded
-// from a peer and no peer is waited for.
+// from a peer and no peer is waited for.  With p.multicast the segment is instead read back from
+// the staging buffer and stored once, 16 bytes per lane, to a multicast mapping of the view
+// (multimem.st): the NVSwitch replicates it to every GPU, this one included, so each byte leaves
+// the GPU once instead of once per peer.
 constexpr uint32_t kMaxPeers = 7;
-struct PeerMaps { CUtensorMap m[kMaxPeers]; };
+struct PeerMaps { CUtensorMap m[kMaxPeers]; void* multicast; };
 struct NoPeers { uint32_t unused; };
 template <bool GATHER> struct PeerArgOf { using type = NoPeers; };
 template <> struct PeerArgOf<true> { using type = PeerMaps; };
@@ -234,7 +238,7 @@ template <typename T, uint32_t BN, bool DUAL = false, uint32_t PARTS = 1, bool G
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tmap_out, uint32_t staging,
                                                   uint32_t part, uint32_t acc, uint32_t quarter, uint32_t lane,
                                                   uint32_t batch, uint32_t m0, uint32_t n0, uint32_t acc2 = 0,
-                                                  const CUtensorMap* peers = nullptr)
+                                                  const PeerMaps* peers = nullptr)
 {
     constexpr uint32_t kColsPerBox = 128 / sizeof(T);            // 64 (16-bit) or 32 (fp32)
     constexpr uint32_t kLoadsPerBox = kColsPerBox / 32;
@@ -302,15 +306,38 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                tma_store_3d(tmap_out, staging, static_cast<int32_t>(box_col), static_cast<int32_t>(m0 + quarter * 32),
-                             static_cast<int32_t>(batch));
-                if constexpr (GATHER) {
-                    for (uint32_t i = 0; i < p.n_peers; ++i)
-                        tma_store_3d(peers + i, staging, static_cast<int32_t>(box_col),
-                                     static_cast<int32_t>(m0 + quarter * 32), static_cast<int32_t>(batch));
+            bool multicast = false;
+            if constexpr (GATHER) multicast = p.multicast != 0;
+            if (!multicast) {
+                if (lane == 0) {
+                    tma_store_3d(tmap_out, staging, static_cast<int32_t>(box_col), static_cast<int32_t>(m0 + quarter * 32),
+                                 static_cast<int32_t>(batch));
+                    if constexpr (GATHER) {
+                        for (uint32_t i = 0; i < p.n_peers; ++i)
+                            tma_store_3d(&peers->m[i], staging, static_cast<int32_t>(box_col),
+                                         static_cast<int32_t>(m0 + quarter * 32), static_cast<int32_t>(batch));
+                    }
+                    bulk_commit_group();
                 }
-                bulk_commit_group();
+            } else if constexpr (GATHER) {
+                // 8 lanes cover one row of the segment (a full 128-byte line), a warp instruction 4 rows;
+                // N is a multiple of 16 bytes here, so a chunk is inside the row or outside it
+                constexpr uint32_t kPerChunk = 16 / sizeof(T);
+                const uint32_t sub = lane >> 3, q = lane & 7;
+                T* const mc = static_cast<T*>(peers->multicast);
+#pragma unroll 2
+                for (uint32_t it = 0; it < 8; ++it) {
+                    const uint32_t r = it * 4 + sub;
+                    uint4 v;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                 : "r"(staging + r * 128 + ((q ^ (r & 7)) << 4)) : "memory");
+                    const uint32_t grow = m0 + quarter * 32 + r, gcol = box_col + q * kPerChunk;
+                    if (grow < p.M && gcol < p.N)
+                        multimem_st_16(mc + static_cast<long long>(batch) * p.out_batch_stride +
+                                            static_cast<long long>(grow) * p.ldo + gcol, v);
+                }
+                __syncwarp();          // every lane has read the segment before the next one is staged
             }
         }
     }
@@ -654,7 +681,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if constexpr (GATHER)
                 drain_accumulator<T, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                          (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
-                                                         0, peer_maps.m);
+                                                         0, &peer_maps);
             else
                 drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                    (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);

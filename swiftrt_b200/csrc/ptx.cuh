@@ -173,6 +173,16 @@ __device__ __forceinline__ void bulk_wait_group()
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// 16 bytes to every replica of a multicast (NVLS) mapping: the NVSwitch delivers the store to all
+// GPUs bound to the multicast object, the issuing one included.  A plain bit copy, whatever the
+// element type.
+__device__ __forceinline__ void multimem_st_16(void* mc_ptr, const uint4& v)
+{
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_ptr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w)) : "memory");
+}
+
 // Same load issued by one CTA of a cta_group::2 pair: the data lands in this CTA's shared
 // memory, the byte count is signalled on `bar_cluster`, a shared::cluster address that may
 // name the barrier of either CTA of the pair (see map_to_cta).  Not a multicast: one

@@ -1590,6 +1590,7 @@ cudaError_t srtMatmulNoAlloc(const void* a, const srtTensorDescriptor* aDesc, bo
 struct GatherKey {
     CallKey call;
     void* peers[kMaxPeers];
+    void* multicast;
     int32_t count;
     int32_t pad;
 };
@@ -1625,16 +1626,16 @@ static cudaError_t copy_view_to_peers(const Problem& P, const srtTensorDescripto
     return cudaSuccess;
 }
 
-cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
                                const srtTensorDescriptor* bDesc, bool transB, const void* bias,
                                const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
-                               const srtTensorDescriptor* oDesc, int32_t peerCount, void* const* peerOut,
+                               const srtTensorDescriptor* oDesc, int32_t peerCount, void* const* peerOut, void* multicastOut,
                                cudaStream_t stream)
 {
     if (peerCount < 0 || peerCount > (int32_t)kMaxPeers)
         return fail(cudaErrorInvalidValue, "srtMatmulAllGather: peerCount %d outside 0..%u", peerCount, kMaxPeers);
     if (peerCount > 0 && !peerOut) return fail(cudaErrorInvalidValue, "srtMatmulAllGather: null peerOut");
-    if (peerCount == 0)
+    if (peerCount == 0 && !multicastOut)
         return srtMatmulBiasActivation(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, activation, out, oDesc, stream);
     GatherKey key;
     memset(&key, 0, sizeof key);
@@ -1652,6 +1653,7 @@ cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, 
     key.call.device = dev;
     key.call.plan_epoch = g_plan_epoch.load(std::memory_order_relaxed);
     key.count = peerCount;
+    key.multicast = multicastOut;
     for (int32_t i = 0; i < peerCount; ++i) {
         if (!peerOut[i]) return fail(cudaErrorInvalidValue, "srtMatmulAllGather: peerOut[%d] is null", i);
         key.peers[i] = peerOut[i];
@@ -1673,6 +1675,17 @@ cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, 
                 ent.fused = encode_out_map(&ent.maps.m[i], plan.Q, ent.pr.gp.ldo, peerOut[i]);
         }
         ent.pr.gp.n_peers = ent.fused ? (uint32_t)peerCount : 0u;
+        ent.pr.gp.multicast = 0;
+        if (multicastOut) {
+            // 16-byte multimem stores: whole chunks only, and the multicast view aligned like the local one
+            const bool ok = ent.fused && (plan.Q.N * plan.Q.elem) % 16 == 0 && reinterpret_cast<uintptr_t>(multicastOut) % 16 == 0;
+            if (!ok)
+                return fail(cudaErrorNotSupported,
+                            "srtMatmulAllGatherMulticast: this product does not run on the CTA-pair kernel with a 16-byte aligned, "
+                            "row-contiguous output whose row length is a multiple of 16 bytes; use srtMatmulAllGather");
+            ent.maps.multicast = multicastOut;
+            ent.pr.gp.multicast = 1;
+        }
         ent.key = key;
         ent.valid = true;
     }
@@ -1689,6 +1702,25 @@ cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, 
     }
     if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return e;
+}
+
+cudaError_t srtMatmulAllGather(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                               const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                               const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                               const srtTensorDescriptor* oDesc, int32_t peerCount, void* const* peerOut,
+                               cudaStream_t stream)
+{
+    return gather_impl(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, activation, out, oDesc, peerCount, peerOut, nullptr,
+                       stream);
+}
+
+cudaError_t srtMatmulAllGatherMulticast(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                                        const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                                        const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                                        const srtTensorDescriptor* oDesc, void* multicastOut, cudaStream_t stream)
+{
+    if (!multicastOut) return fail(cudaErrorInvalidValue, "srtMatmulAllGatherMulticast: null multicastOut");
+    return gather_impl(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, activation, out, oDesc, 0, nullptr, multicastOut, stream);
 }
 
 // ------------------------------------------------------------------ peer memory (one process per GPU)

@@ -64,10 +64,11 @@ class MatmulOp:
 
     def __init__(self, out: torch.Tensor, lhs: torch.Tensor, transpose_lhs: bool, rhs: torch.Tensor,
                  transpose_rhs: bool, bias: torch.Tensor | None = None,
-                 activation: ActivationType | None = None, peer_pointers=None):
+                 activation: ActivationType | None = None, peer_pointers=None, multicast_pointer: int | None = None):
         """`peer_pointers`: device addresses of the same output view in other GPUs' buffers
         (PeerBuffer.peer_pointers); the result block is then delivered to them as well
-        (srtMatmulAllGather)."""
+        (srtMatmulAllGather).  `multicast_pointer`: address of the view in an NVLink multicast
+        mapping instead (PeerBuffer.multicast_pointer, srtMatmulAllGatherMulticast)."""
         if not (lhs.is_cuda and rhs.is_cuda and out.is_cuda):
             raise ValueError("device tensors expected; use matmul_host for host buffers")
         self.out = out
@@ -76,7 +77,15 @@ class MatmulOp:
         self._index = out.device.index if out.device.index is not None else torch.cuda.current_device()
         da, db, do = _descriptor(lhs), _descriptor(rhs), _descriptor(out)
         self._descs = (da, db, do)
-        if peer_pointers:
+        if multicast_pointer:
+            dbias = _descriptor(bias) if bias is not None else None
+            self._descs += (dbias,)
+            self._fn = lib.srtMatmulAllGatherMulticast
+            self._args = (lhs.data_ptr(), da.ref(), bool(transpose_lhs), rhs.data_ptr(), db.ref(), bool(transpose_rhs),
+                          bias.data_ptr() if bias is not None else None, dbias.ref() if dbias is not None else None,
+                          int(activation if activation is not None else ActivationType.identity),
+                          out.data_ptr(), do.ref(), int(multicast_pointer))
+        elif peer_pointers:
             dbias = _descriptor(bias) if bias is not None else None
             self._descs += (dbias,)
             self._peers = (ctypes.c_void_p * len(peer_pointers))(*peer_pointers)
@@ -127,6 +136,15 @@ def matmul_all_gather_into(out: torch.Tensor, peer_pointers, lhs: torch.Tensor, 
     ranks' buffers).  The peers' copies are complete when this rank's stream has drained; order
     the ranks (PeerBuffer.ranks_done) before reading blocks that others wrote."""
     return MatmulOp(out, lhs, transpose_lhs, rhs, transpose_rhs, bias, activation, peer_pointers)()
+
+
+def matmul_all_gather_multicast_into(out: torch.Tensor, multicast_pointer: int, lhs: torch.Tensor, transpose_lhs: bool,
+                                     rhs: torch.Tensor, transpose_rhs: bool, bias: torch.Tensor | None = None,
+                                     activation: ActivationType | None = None) -> torch.Tensor:
+    """matmul_into whose result block is stored once to an NVLink multicast mapping and replicated
+    into every rank's buffer by the NVSwitch (srtMatmulAllGatherMulticast).  Raises MatmulError
+    with code 801 when the product is not eligible; use matmul_all_gather_into then."""
+    return MatmulOp(out, lhs, transpose_lhs, rhs, transpose_rhs, bias, activation, None, multicast_pointer)()
 
 
 def matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,

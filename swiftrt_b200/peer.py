@@ -41,8 +41,14 @@ class PeerBuffer:
     peer_base   {rank: device address of that rank's buffer, mapped into this process}
     """
 
-    def __init__(self, shape: Sequence[int], dtype: torch.dtype, group=None, device: Optional[torch.device] = None):
+    def __init__(self, shape: Sequence[int], dtype: torch.dtype, group=None, device: Optional[torch.device] = None,
+                 multicast: bool = False):
+        """`multicast=True` allocates the buffers as torch symmetric memory instead, which also binds
+        them to one NVLink multicast object: `multicast_base` is then the address of the multicast
+        mapping (0 when the machine has none) and the peers' addresses come from the same handle."""
         self.group = group
+        self.multicast_base = 0
+        self._symm = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if self.world > 8:
@@ -55,12 +61,22 @@ class PeerBuffer:
             count *= s
         self.nbytes = max(count * torch.empty((), dtype=dtype).element_size(), 16)
         self._ptr = ctypes.c_void_p()
+        self.peer_base: dict[int, int] = {}
+        if multicast and self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            with torch.cuda.device(self.device):
+                self.tensor = symm_mem.empty(self.shape, dtype=dtype, device=self.device)
+                self._symm = symm_mem.rendezvous(self.tensor, group if group is not None else dist.group.WORLD)
+            self.multicast_base = int(self._symm.multicast_ptr or 0)
+            self.peer_base = {r: int(p) for r, p in enumerate(self._symm.buffer_ptrs) if r != self.rank}
+            self._token = None
+            self._open = True
+            return
         handle = _lib.PeerMemHandle()
         with torch.cuda.device(self.device):
             _check(lib.srtPeerMemAlloc(self.nbytes, ctypes.byref(self._ptr), ctypes.byref(handle)))
         raw = torch.as_tensor(_RawDeviceMemory(self._ptr.value, self.nbytes), device=self.device)
         self.tensor = raw[: count * raw.new_empty((), dtype=dtype).element_size()].view(dtype).reshape(self.shape)
-        self.peer_base: dict[int, int] = {}
         if self.world > 1:
             handles: list = [None] * self.world
             dist.all_gather_object(handles, bytes(handle.bytes), group=group)
@@ -83,6 +99,15 @@ class PeerBuffer:
             raise ValueError("not a view of this buffer")
         return [base + offset for _, base in sorted(self.peer_base.items())]
 
+    def multicast_pointer(self, view: torch.Tensor) -> int:
+        """Address of `view` in the multicast mapping (0 without one)."""
+        if not self.multicast_base:
+            return 0
+        offset = view.data_ptr() - self.tensor.data_ptr()
+        if not 0 <= offset < self.nbytes:
+            raise ValueError("not a view of this buffer")
+        return self.multicast_base + offset
+
     def ranks_done(self) -> None:
         """Orders everything the ranks enqueued so far before what follows on this rank's current
         stream: after it, blocks written by other ranks may be read."""
@@ -101,6 +126,13 @@ class PeerBuffer:
         torch.cuda.synchronize(self.device)
         if self.world > 1:
             dist.barrier(group=self.group)
+        if self._symm is not None:
+            # symmetric memory is owned by torch: dropping the references releases the mappings
+            self.peer_base = {}
+            self.multicast_base = 0
+            self._symm = None
+            self.tensor = None
+            return
         with torch.cuda.device(self.device):
             for p in self.peer_base.values():
                 _check(lib.srtPeerMemClose(p))

@@ -97,10 +97,19 @@ def sharded_matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = 
     if peer_buffer is not None:
         if tuple(peer_buffer.tensor.shape) != tuple(full_shape):
             raise ValueError(f"peer buffer of shape {tuple(peer_buffer.tensor.shape)}, result is {tuple(full_shape)}")
-        if gather_fn is None:
-            from .matmul import matmul_all_gather_into as gather_fn
         if hi > lo:
             view = peer_buffer.tensor.narrow(dim, lo, hi - lo)
+            if gather_fn is None:
+                from .matmul import MatmulError, matmul_all_gather_into, matmul_all_gather_multicast_into
+                mc = peer_buffer.multicast_pointer(view) if getattr(peer_buffer, "multicast_base", 0) else 0
+                if mc:
+                    try:        # one multimem store per tile; products it does not take (code 801) go peer by peer
+                        matmul_all_gather_multicast_into(view, mc, a, transposed_lhs, b, transposed_rhs)
+                        return peer_buffer.tensor
+                    except MatmulError as e:
+                        if e.code != 801:
+                            raise
+                gather_fn = matmul_all_gather_into
             gather_fn(view, peer_buffer.peer_pointers(view), a, transposed_lhs, b, transposed_rhs)
         return peer_buffer.tensor
 

@@ -148,11 +148,16 @@ dist.init_process_group("nccl", device_id=torch.device(f"cuda:{rank}"))
 import swiftrt_b200 as srt
 torch.manual_seed(0)                                   # same operands on every rank
 ok = True
-for axis, ash, bsh in (("n", (1024, 1024), (1024, 2048)), ("m", (2048, 512), (512, 640)), ("batch", (4, 256, 256), (4, 256, 384))):
+cases = [(axis, ash, bsh, mc) for mc in (False, True)
+         for axis, ash, bsh in (("n", (1024, 1024), (1024, 2048)), ("m", (2048, 512), (512, 640)), ("batch", (4, 256, 256), (4, 256, 384)))]
+for axis, ash, bsh, mc in cases:
     a = torch.randn(ash, device="cuda", dtype=torch.bfloat16)
     b = torch.randn(bsh, device="cuda", dtype=torch.bfloat16)
     want = srt.matmul(a, b)
-    buf = srt.PeerBuffer(tuple(want.shape), torch.bfloat16)
+    # mc: buffers bound to one NVLink multicast object; eligible products store each tile once (multimem.st)
+    buf = srt.PeerBuffer(tuple(want.shape), torch.bfloat16, multicast=mc)
+    if mc and rank == 0:
+        print("multicast mapping:", hex(buf.multicast_base), flush=True)
     buf.tensor.fill_(-1.0)
     torch.cuda.synchronize(); dist.barrier()
     for _ in range(2):
