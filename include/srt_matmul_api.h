@@ -104,7 +104,8 @@ typedef enum {
  * views that meet the TMA rules (16-byte aligned base, one unit stride in the last two
  * dims, the other strides multiples of 16 bytes) run on the tensor-core kernel, the rest
  * on a strided SIMT kernel.  `out` is write-only, may be a strided view, and must not
- * alias an input.  Inputs may alias each other.
+ * alias an input.  Inputs may alias each other.  An `out` without elements (M, N or the batch
+ * is 0) succeeds and launches nothing; K = 0 writes activation(0 + bias) to every element.
  */
 cudaError_t srtMatmul(
     const void* a, const srtTensorDescriptor* aDesc, bool transA,

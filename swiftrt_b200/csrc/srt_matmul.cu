@@ -68,9 +68,12 @@ cudaError_t parse(const void* a, const srtTensorDescriptor* ad, bool ta,
                   const void* bias, const srtTensorDescriptor* biasd, int act,
                   const void* out, const srtTensorDescriptor* od, Problem& P)
 {
-    if (!a || !b || !out || !ad || !bd || !od) return fail(cudaErrorInvalidValue, "null tensor or descriptor");
+    if (!ad || !bd || !od) return fail(cudaErrorInvalidValue, "null tensor or descriptor");
     if (!ad->shape || !ad->strides || !bd->shape || !bd->strides || !od->shape || !od->strides)
         return fail(cudaErrorInvalidValue, "descriptor without shape or strides");
+    // tensors without elements have no storage to point at
+    if ((!a && ad->count != 0) || (!b && bd->count != 0) || (!out && od->count != 0))
+        return fail(cudaErrorInvalidValue, "null tensor or descriptor");
     if (ad->type != od->type || bd->type != od->type)
         return fail(cudaErrorInvalidValue, "a, b and out must have the same element type");
     P.type = od->type;
@@ -96,7 +99,8 @@ cudaError_t parse(const void* a, const srtTensorDescriptor* ad, bool ta,
         return fail(cudaErrorInvalidValue, "out shape [%llu x %llu] does not match op(a).op(b) [%llu x %llu]",
                     (unsigned long long)P.M, (unsigned long long)P.N, (unsigned long long)aM, (unsigned long long)bN);
     P.K = aK;
-    if (P.M == 0 || P.N == 0 || P.K == 0 || P.batch == 0) return fail(cudaErrorInvalidValue, "zero-sized dimension");
+    // empty results (M, N or batch = 0) are accepted and launch nothing (see is_empty); an empty
+    // reduction (K = 0) is a sum of no terms: out = activation(0 + bias), computed by the strided kernel
     const uint64_t lim = 0x7fffffffull;       // the reference limits dims to Int32.max (MatrixLayout.swift:117-142)
     if (P.M > lim || P.N > lim || P.K > lim || P.batch > 65535)
         return fail(cudaErrorInvalidValue, "dimension exceeds the supported range");
@@ -150,6 +154,8 @@ cudaError_t parse(const void* a, const srtTensorDescriptor* ad, bool ta,
 }
 
 // ------------------------------------------------------------------ per-device state
+inline bool is_empty(const Problem& P) { return P.M == 0 || P.N == 0 || P.batch == 0; }
+
 // ------------------------------------------------------------------ tuning choices and the plan table
 // What the planner may be told instead of deciding by its cost model: 0 = decide.
 struct Choice { int32_t force, tile_n, stages, max_ctas, split_k; };
@@ -314,7 +320,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     const Choice choice = effective_choice(P);
     const int32_t force = choice.force;
 
-    bool tc = dev.sm100 && force != srtMatmulKernelSimt;
+    bool tc = dev.sm100 && force != srtMatmulKernelSimt && P.K > 0;
     // the tensor-core path writes rows of contiguous columns; a col-order out is computed
     // as out^T = op(b)^T . op(a)^T, which is the same memory
     Problem Q = P;
@@ -1154,6 +1160,7 @@ cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aD
     Problem& P = key.P;
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
     if (e != cudaSuccess) return e;
+    if (is_empty(P)) return cudaSuccess;
     int dev = 0;
     e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
@@ -1200,6 +1207,7 @@ cudaError_t srtMatmulQueryPlan(const void* a, const srtTensorDescriptor* aDesc, 
     Problem P;
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out, oDesc, P);
     if (e != cudaSuccess) return e;
+    if (is_empty(P)) { memset(plan_out, 0, sizeof *plan_out); return cudaSuccess; }      // nothing to launch
     Plan plan;
     e = plan_for(P, plan);
     if (e != cudaSuccess) return e;
@@ -1236,6 +1244,7 @@ cudaError_t srtMatmulTune(const void* a, const srtTensorDescriptor* aDesc, bool 
     memset(&P, 0, sizeof P);
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
     if (e != cudaSuccess) return e;
+    if (is_empty(P)) return fail(cudaErrorInvalidValue, "srtMatmulTune: empty result");
     // candidates: the cost model's own choice first, then every kernel / tile width the type allows
     std::vector<Choice> cands;
     cands.push_back(Choice{0, 0, 0, 0, 0});
@@ -1535,6 +1544,7 @@ cudaError_t srtMatmulNoAlloc(const void* a, const srtTensorDescriptor* aDesc, bo
     memset(&P, 0, sizeof P);
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out, oDesc, P);
     if (e != cudaSuccess) return e;
+    if (is_empty(P)) return cudaSuccess;
     Plan plan;
     e = plan_for(P, plan);
     if (e != cudaSuccess) return e;
@@ -1642,6 +1652,7 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
     Problem& P = key.call.P;
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
     if (e != cudaSuccess) return e;
+    if (is_empty(P)) return cudaSuccess;
     int dev = 0;
     e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;

@@ -496,3 +496,23 @@ def test_unsupported_inputs_return_not_supported(srt):
     with pytest.raises(srt.MatmulError) as e:
         srt.matmul(a, a)
     assert e.value.code == 801
+
+
+def test_empty_results_and_empty_reductions(srt):
+    """Edge cases of the loop nest (CpuMath.swift:1141-1186): no rows, no columns or no batch items
+    write nothing; a reduction over no terms gives 0 (+ bias, activation) in every element."""
+    dev = "cuda:0"
+    before = srt.launch_count()
+    for ash, bsh in (((0, 8), (8, 5)), ((4, 8), (8, 0)), ((0, 3, 8), (0, 8, 5))):
+        c = srt.matmul(torch.zeros(ash, device=dev), torch.zeros(bsh, device=dev))
+        assert tuple(c.shape) == tuple(ash[:-1]) + (bsh[-1],) and c.numel() == 0
+    assert srt.launch_count() == before                                   # nothing was launched
+    for dtype in (torch.float32, torch.bfloat16):
+        a, b = torch.zeros((6, 0), device=dev, dtype=dtype), torch.zeros((0, 10), device=dev, dtype=dtype)
+        out = torch.full((6, 10), 7.0, device=dev, dtype=dtype)
+        srt.matmul_into(out, a, False, b, False)
+        assert bool((out == 0).all())
+        bias = torch.arange(-5, 5, device=dev).to(dtype)
+        y = srt.matmul(a, b, bias=bias, activation=srt.ActivationType.relu)
+        assert torch.equal(y, torch.relu(bias).expand(6, 10))
+    torch.cuda.synchronize()
