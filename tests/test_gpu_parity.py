@@ -516,3 +516,37 @@ def test_empty_results_and_empty_reductions(srt):
         y = srt.matmul(a, b, bias=bias, activation=srt.ActivationType.relu)
         assert torch.equal(y, torch.relu(bias).expand(6, 10))
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype,kernel", [(F32, SIMT), (BF16, TC), (F16, PAIR), (F32, SPLIT)])
+def test_small_shape_sweep_with_guard_bands(srt, oracle, dtype, kernel):
+    """Every combination of M, N, K from {1, 2, 3, 5, 8, 9, 16, 17, 31, 32, 33}: the strided kernel
+    bit-exact, the tensor-core kernels (which take the shapes TMA can address and leave the rest
+    to the strided kernel) within tolerance; sentinels before and after the result stay intact."""
+    sizes = (1, 2, 3, 5, 8, 9, 16, 17, 31, 32, 33)
+    rng = np.random.default_rng(dtype * 7 + kernel)
+    srt.set_tuning(kernel, 0, 0, 0)
+    tdt = {F32: torch.float32, BF16: torch.bfloat16, F16: torch.float16}[dtype]
+    a_all = random_bits(oracle, rng, (33, 33), dtype)
+    b_all = random_bits(oracle, rng, (33, 33), dtype)
+    guard = 32
+    worst = 0.0
+    for M in sizes:
+        for K in sizes:
+            a = np.ascontiguousarray(a_all[:M, :K])
+            da = to_dev(a, dtype)
+            for N in sizes:
+                b = np.ascontiguousarray(b_all[:K, :N])
+                canvas = torch.full((guard + M * N + guard,), 3.0, dtype=tdt, device="cuda:0")
+                out = canvas[guard:guard + M * N].view(M, N)
+                srt.matmul_into(out, da, False, to_dev(b, dtype), False)
+                ref = oracle.matmul(a, b, dtype, threads=1)
+                got = from_dev(out, dtype)
+                if kernel == SIMT:
+                    assert np.array_equal(got, ref), (M, N, K)
+                else:
+                    err = oracle.rel_frobenius(oracle.decode(got, dtype), oracle.decode(ref, dtype))
+                    worst = max(worst, err)
+                    assert err <= TOL[dtype], (M, N, K, err)
+                assert bool((canvas[:guard] == 3.0).all()) and bool((canvas[guard + M * N:] == 3.0).all()), (M, N, K)
+    assert srt.check_status() == 0
