@@ -354,12 +354,14 @@ __device__ __forceinline__ void drain_finish(uint32_t lane)
 // InT / OutT: element type of the inputs and of the output (float, __half, __nv_bfloat16).
 // BN: tile width (64, 128 or 256).  fp32 inputs are multiplied as TF32.
 // OutT differs from T only for split-K partial sums (16-bit inputs, fp32 workspace).
-template <typename T, uint32_t BN, typename OutT = T>
+// GATHER: the epilogue also delivers every tile to the peers (see drain_accumulator).
+template <typename T, uint32_t BN, typename OutT = T, bool GATHER = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_out,
-                    const __grid_constant__ GemmParams p)
+                    const __grid_constant__ GemmParams p,
+                    const __grid_constant__ typename PeerArgOf<GATHER>::type peer_maps)
 {
     constexpr uint32_t kBTileBytes = BN * kRowBytes;
     constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
@@ -490,8 +492,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            drain_accumulator<OutT, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
-                                               (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
+            if constexpr (GATHER)
+                drain_accumulator<OutT, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+                                                            (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
+                                                            0, &peer_maps);
+            else
+                drain_accumulator<OutT, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
+                                                      (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));

@@ -553,16 +553,28 @@ cudaError_t ensure_smem_attr(Kernel kernel, std::atomic<uint64_t>& done, size_t 
     return cudaSuccess;
 }
 
-template <typename T, uint32_t BN, typename OutT = T>
+template <typename T, uint32_t BN, typename OutT = T, bool GATHER = false>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp, uint32_t ctas, size_t smem,
-                      cudaStream_t stream)
+                      cudaStream_t stream, const typename PeerArgOf<GATHER>::type& peers = typename PeerArgOf<GATHER>::type())
 {
-    auto kernel = gemm_tcgen05_kernel<T, BN, OutT>;
+    auto kernel = gemm_tcgen05_kernel<T, BN, OutT, GATHER>;
     static std::atomic<uint64_t> attr_done{0};
     cudaError_t e = ensure_smem_attr(kernel, attr_done, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<ctas, kGemmThreads, smem, stream>>>(ma, mb, mo, gp);
+    kernel<<<ctas, kGemmThreads, smem, stream>>>(ma, mb, mo, gp, peers);
     return cudaGetLastError();
+}
+
+// The gathering form of the one-CTA kernel.
+template <typename T>
+cudaError_t launch_tc_gather_bn(uint32_t bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const GemmParams& gp,
+                                uint32_t ctas, size_t smem, cudaStream_t stream, const PeerMaps& peers)
+{
+    switch (bn) {
+    case 64: return launch_tc<T, 64, T, true>(ma, mb, mo, gp, ctas, smem, stream, peers);
+    case 128: return launch_tc<T, 128, T, true>(ma, mb, mo, gp, ctas, smem, stream, peers);
+    default: return launch_tc<T, 256, T, true>(ma, mb, mo, gp, ctas, smem, stream, peers);
+    }
 }
 
 template <typename T, typename OutT = T>
@@ -1678,7 +1690,8 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
         if (e != cudaSuccess) return e;
         e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, ent.pr) : prepare_tc(plan, ent.pr);
         if (e != cudaSuccess) return e;
-        ent.fused = plan.pub.kernel == srtMatmulKernelTcgen05Pair && ent.pr.splits <= 1 && ent.pr.gp.out_tma;
+        ent.fused = (plan.pub.kernel == srtMatmulKernelTcgen05Pair || plan.pub.kernel == srtMatmulKernelTcgen05) &&
+                    ent.pr.splits <= 1 && ent.pr.gp.out_tma;
         if (ent.fused) {
             // the planner may have transposed the problem (column-order output): peers hold the same view
             memset(&ent.maps, 0, sizeof ent.maps);
@@ -1692,8 +1705,8 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
             const bool ok = ent.fused && (plan.Q.N * plan.Q.elem) % 16 == 0 && reinterpret_cast<uintptr_t>(multicastOut) % 16 == 0;
             if (!ok)
                 return fail(cudaErrorNotSupported,
-                            "srtMatmulAllGatherMulticast: this product does not run on the CTA-pair kernel with a 16-byte aligned, "
-                            "row-contiguous output whose row length is a multiple of 16 bytes; use srtMatmulAllGather");
+                            "srtMatmulAllGatherMulticast: this product does not run on a 16-bit tensor-core kernel with a 16-byte "
+                            "aligned, row-contiguous output whose row length is a multiple of 16 bytes; use srtMatmulAllGather");
             ent.maps.multicast = multicastOut;
             ent.pr.gp.multicast = 1;
         }
@@ -1706,10 +1719,18 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
         return copy_view_to_peers(P, oDesc, out, peerCount, peerOut, stream);
     }
     const Prepared& pr = ent.pr;
-    switch (pr.type) {
-    case real32F: e = launch_pair_gather_bn<float>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
-    case real16F: e = launch_pair_gather_bn<__half>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
-    default: e = launch_pair_gather_bn<__nv_bfloat16>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+    if (pr.kernel == srtMatmulKernelTcgen05Pair) {
+        switch (pr.type) {
+        case real32F: e = launch_pair_gather_bn<float>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+        case real16F: e = launch_pair_gather_bn<__half>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+        default: e = launch_pair_gather_bn<__nv_bfloat16>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+        }
+    } else {
+        switch (pr.type) {
+        case real32F: e = launch_tc_gather_bn<float>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+        case real16F: e = launch_tc_gather_bn<__half>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+        default: e = launch_tc_gather_bn<__nv_bfloat16>(pr.bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream, ent.maps); break;
+        }
     }
     if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     return e;

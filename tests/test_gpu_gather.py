@@ -31,9 +31,10 @@ def _full_buffers(n, shape, dtype):
 
 @pytest.mark.parametrize("dtype,M,N,K,expect_fused", [
     (BF16, 512, 1024, 2048, True),        # CTA-pair kernel: tiles stored to every buffer by the epilogue
+    (F16, 384, 256, 512, None),           # one CTA per tile
     (F16, 768, 520, 1024, None),          # ragged right edge, clipped by the tensor maps
     (F32, 384, 512, 1024, None),          # Float32 runs the 3xTF32 kernel: product, then copies
-    (BF16, 96, 200, 64, None),           # small: one-CTA kernel, then copies
+    (BF16, 96, 200, 64, None),           # small: one CTA per tile, the same fused epilogue
     (F32, 33, 17, 9, None),              # strided SIMT kernel, then copies
 ])
 def test_block_lands_in_every_buffer(srt, oracle, dtype, M, N, K, expect_fused):
@@ -48,7 +49,8 @@ def test_block_lands_in_every_buffer(srt, oracle, dtype, M, N, K, expect_fused):
         srt.set_tuning(srt.KERNEL_TCGEN05_PAIR)           # few tiles: the planner alone would take one CTA per tile
     try:
         plan = srt.query_plan(a, b, views[0])
-        fused = plan["kernel"] == srt.KERNEL_TCGEN05_PAIR and plan["splitK"] <= 1 and (N * a.element_size()) % 16 == 0
+        fused = (plan["kernel"] in (srt.KERNEL_TCGEN05_PAIR, srt.KERNEL_TCGEN05) and plan["splitK"] <= 1 and
+                 (N * a.element_size()) % 16 == 0)
         if expect_fused:
             assert fused, plan
         before = srt.launch_count()
