@@ -186,7 +186,7 @@ def _side_streams(dev: torch.device):
 
 def matmul_host(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,
                 bias: torch.Tensor | None = None, activation: ActivationType | None = None,
-                device="cuda:0", out_host: torch.Tensor | None = None, chunks: int = 8) -> torch.Tensor:
+                device="cuda:0", out_host: torch.Tensor | None = None, chunks: int = 16) -> torch.Tensor:
     """The same operator for HOST tensors: inputs are copied to `device`, multiplied there and the
     result is copied back; the call returns when the result is in host memory.  This is what the
     reference's storage does around a queue call (host replicas migrate on deviceRead,
