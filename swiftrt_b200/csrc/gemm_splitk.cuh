@@ -25,6 +25,9 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const ReduceParams p)
 {
+    // launched as a programmatic dependent of the partial-sum kernel: scheduled early, held here until
+    // that kernel has completed and its partial sums are visible
+    grid_dependency_wait();
     const unsigned long long groups = p.slice / VEC;
     const T* const bias = static_cast<const T*>(p.bias);
     T* const out = static_cast<T*>(p.out);

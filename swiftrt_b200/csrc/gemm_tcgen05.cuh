@@ -382,6 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t stages = p.stages;
+    if (p.k_splits > 1) launch_dependents();      // lets the reduce pass be scheduled while this grid runs
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -766,6 +767,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t stages = p.stages;
+    if (p.k_splits > 1) launch_dependents();      // lets the reduce pass be scheduled while this grid runs
 
     if (threadIdx.x == 0) {
         abort_flag = 0;

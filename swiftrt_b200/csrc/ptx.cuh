@@ -183,6 +183,14 @@ __device__ __forceinline__ void multimem_st_16(void* mc_ptr, const uint4& v)
                    "f"(__uint_as_float(v.w)) : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may be scheduled while its predecessor in the stream still runs, once every CTA of the
+// predecessor has executed launch_dependents (or exited); it must execute grid_dependency_wait
+// before touching anything the predecessor writes (the wait returns when the predecessor has
+// completed and its writes are visible).  Both are no-ops in launches without the attribute.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Same load issued by one CTA of a cta_group::2 pair: the data lands in this CTA's shared
 // memory, the byte count is signalled on `bar_cluster`, a shared::cluster address that may
 // name the barrier of either CTA of the pair (see map_to_cta).  Not a multicast: one

@@ -861,28 +861,37 @@ cudaError_t prepare_simt(const Plan& plan, Prepared& pr)
     return cudaSuccess;
 }
 
+template <typename T, int VEC>
+cudaError_t launch_reduce_as_dependent(const ReduceParams& rp, unsigned blocks, cudaStream_t stream)
+{
+    // programmatic dependent launch: the reduce grid is scheduled while the partial-sum kernel still
+    // runs and waits inside the kernel (grid_dependency_wait) for its completion
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<T, VEC>, rp);
+}
+
 cudaError_t launch_reduce(const Prepared& pr, cudaStream_t stream)
 {
     const ReduceParams& rp = pr.rp;
     const unsigned blocks = pr.reduce_blocks;
+    const bool v4 = pr.reduce_vec == 4;
     switch (pr.type) {
-    case real32F:
-        if (pr.reduce_vec == 4) splitk_reduce_kernel<float, 4><<<blocks, 256, 0, stream>>>(rp);
-        else                    splitk_reduce_kernel<float, 1><<<blocks, 256, 0, stream>>>(rp);
-        break;
-    case real16F:
-        if (pr.reduce_vec == 4) splitk_reduce_kernel<__half, 4><<<blocks, 256, 0, stream>>>(rp);
-        else                    splitk_reduce_kernel<__half, 1><<<blocks, 256, 0, stream>>>(rp);
-        break;
-    default:
-        if (pr.reduce_vec == 4) splitk_reduce_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>(rp);
-        else                    splitk_reduce_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, stream>>>(rp);
-        break;
+    case real32F: return v4 ? launch_reduce_as_dependent<float, 4>(rp, blocks, stream) : launch_reduce_as_dependent<float, 1>(rp, blocks, stream);
+    case real16F: return v4 ? launch_reduce_as_dependent<__half, 4>(rp, blocks, stream) : launch_reduce_as_dependent<__half, 1>(rp, blocks, stream);
+    default: return v4 ? launch_reduce_as_dependent<__nv_bfloat16, 4>(rp, blocks, stream)
+                       : launch_reduce_as_dependent<__nv_bfloat16, 1>(rp, blocks, stream);
     }
-    return cudaGetLastError();
 }
 
-// `pr` is mutable because a split-K launch may have to re-point it at a new workspace.
 cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
 {
     cudaError_t e;
@@ -1266,7 +1275,8 @@ cudaError_t srtMatmulTune(const void* a, const srtTensorDescriptor* aDesc, bool 
     } else {
         for (int32_t tn : {64, 128, 256}) {
             cands.push_back(Choice{srtMatmulKernelTcgen05, tn, 0, 0, 0});
-            cands.push_back(Choice{srtMatmulKernelTcgen05, tn, 0, 0, 1});        // the same without split-K
+            // the same without split-K and with fixed numbers of parts (few tiles, long reductions)
+            for (int32_t sk : {1, 2, 4, 8, 16}) cands.push_back(Choice{srtMatmulKernelTcgen05, tn, 0, 0, sk});
         }
         for (int32_t tn : {128, 256}) cands.push_back(Choice{srtMatmulKernelTcgen05Pair, tn, 0, 0, 0});
     }
