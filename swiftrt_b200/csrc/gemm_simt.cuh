@@ -27,18 +27,21 @@ struct SimtParams {
 };
 
 constexpr int kSimtTile = 64;       // default tile edge; 32 when a 64-tile grid would leave most SMs idle
-constexpr int kSimtK = 16;
+constexpr int kSimtK = 16;          // k-tile of the 64 x 64 kernel; the 32 x 32 kernel takes 32 (half as many block-wide syncs)
 
 // TILE x TILE outputs per 256-thread block, (TILE/16)^2 per thread.  The global loads of k-tile
 // t + 1 are issued into registers before k-tile t is multiplied, so their latency overlaps the math.
+// Small tiles are bound by the latency of one k-tile round trip (load, sync, multiply, sync), so
+// they take a k-tile twice as deep.
 template <typename T, int TILE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const SimtParams p)
 {
+    constexpr int KT = TILE == 32 ? 32 : kSimtK;   // k-tile depth
     constexpr int R = TILE / 16;                   // outputs per thread along each axis
-    constexpr int LD = TILE * kSimtK / 256;        // elements of each operand tile a thread loads
-    __shared__ float As[kSimtK][TILE + 1];
-    __shared__ float Bs[kSimtK][TILE + 1];
+    constexpr int LD = TILE * KT / 256;            // elements of each operand tile a thread loads
+    __shared__ float As[KT][TILE + 1];
+    __shared__ float Bs[KT][TILE + 1];
 
     const uint32_t tid = threadIdx.x;
     const uint32_t tx = tid & 15, ty = tid >> 4;
@@ -58,8 +61,8 @@ gemm_simt_kernel(const SimtParams p)
 #pragma unroll
     for (int i = 0; i < LD; ++i) {
         const uint32_t e = tid + i * 256;
-        if (p.a_k_fast) { a_kk[i] = e & 15; a_mm[i] = e >> 4; } else { a_mm[i] = e % TILE; a_kk[i] = e / TILE; }
-        if (p.b_n_fast) { b_nn[i] = e % TILE; b_kk[i] = e / TILE; } else { b_kk[i] = e & 15; b_nn[i] = e >> 4; }
+        if (p.a_k_fast) { a_kk[i] = e % KT; a_mm[i] = e / KT; } else { a_mm[i] = e % TILE; a_kk[i] = e / TILE; }
+        if (p.b_n_fast) { b_nn[i] = e % TILE; b_kk[i] = e / TILE; } else { b_kk[i] = e % KT; b_nn[i] = e / KT; }
     }
     auto fetch = [&](uint32_t k0, float (&ra)[LD], float (&rb)[LD]) {
 #pragma unroll
@@ -75,15 +78,15 @@ gemm_simt_kernel(const SimtParams p)
 
     float ra[LD], rb[LD];
     fetch(0, ra, rb);
-    for (uint32_t k0 = 0; k0 < p.K; k0 += kSimtK) {
+    for (uint32_t k0 = 0; k0 < p.K; k0 += KT) {
 #pragma unroll
         for (int i = 0; i < LD; ++i) {
             As[a_kk[i]][a_mm[i]] = ra[i];
             Bs[b_kk[i]][b_nn[i]] = rb[i];
         }
         __syncthreads();
-        if (k0 + kSimtK < p.K) fetch(k0 + kSimtK, ra, rb);
-        const uint32_t kmax = min(static_cast<uint32_t>(kSimtK), p.K - k0);
+        if (k0 + KT < p.K) fetch(k0 + KT, ra, rb);
+        const uint32_t kmax = min(static_cast<uint32_t>(KT), p.K - k0);
         for (uint32_t kk = 0; kk < kmax; ++kk) {
             float av[R], bv[R];
 #pragma unroll

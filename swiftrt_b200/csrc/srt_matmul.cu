@@ -361,7 +361,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         plan.bias_mode = P.bias ? 1 : 0;
         plan.pub.kernel = srtMatmulKernelSimt;
         const uint32_t st = simt_tile_for(P.M, P.N, P.batch, dev.sms);
-        plan.pub.tileM = (int32_t)st; plan.pub.tileN = (int32_t)st; plan.pub.tileK = kSimtK;
+        plan.pub.tileM = (int32_t)st; plan.pub.tileN = (int32_t)st; plan.pub.tileK = st == 32 ? 32 : kSimtK;
         plan.pub.stages = 1;
         const uint64_t tm = (P.M + st - 1) / st, tn = (P.N + st - 1) / st;
         plan.pub.tiles = (int32_t)(tm * tn * P.batch);
@@ -455,7 +455,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
                 plan.Q = P; plan.swapped = false; plan.bias_mode = P.bias ? 1 : 0;
                 plan.pub.kernel = srtMatmulKernelSimt;
                 const uint32_t st = simt_tile_for(P.M, P.N, P.batch, dev.sms);
-                plan.pub.tileM = (int32_t)st; plan.pub.tileN = (int32_t)st; plan.pub.tileK = kSimtK;
+                plan.pub.tileM = (int32_t)st; plan.pub.tileN = (int32_t)st; plan.pub.tileK = st == 32 ? 32 : kSimtK;
                 plan.pub.stages = 1;
                 plan.pub.tiles = (int32_t)(((P.M + st - 1) / st) * ((P.N + st - 1) / st) * P.batch);
                 plan.pub.ctas = plan.pub.tiles;
