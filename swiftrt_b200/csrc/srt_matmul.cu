@@ -311,7 +311,11 @@ struct Plan {
     uint32_t splits = 1, kb_per_split = 0;   // split-K: partial sums in an fp32 workspace + a reduce pass
 };
 
-void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
+// `skinny_swap`: plan the transposed problem out^T = op(b)^T . op(a)^T although `out` is row-major, so
+// that the wide dimension fills the 128 rows of the MMA and the few rows of `out` become its N.  Only
+// valid when the plan ends up with split-K, whose reduce pass writes through any output strides;
+// returns false (plan unusable) otherwise.
+bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool skinny_swap)
 {
     memset(&plan.pub, 0, sizeof plan.pub);
     plan.Q = P;
@@ -325,9 +329,9 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     // as out^T = op(b)^T . op(a)^T, which is the same memory
     Problem Q = P;
     if (tc) {
-        if (P.o_n == 1 || P.N == 1) {
+        if (!skinny_swap && (P.o_n == 1 || P.N == 1)) {
             // as is
-        } else if (P.o_m == 1 || P.M == 1) {
+        } else if (skinny_swap || P.o_m == 1 || P.M == 1) {
             Q.M = P.N; Q.N = P.M;
             Q.a = P.b; Q.a_b = P.b_b; Q.a_m = P.b_n; Q.a_k = P.b_k;
             Q.b = P.a; Q.b_b = P.a_b; Q.b_k = P.a_k; Q.b_n = P.a_m;
@@ -342,7 +346,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         plan.ta = classify(Q.a, Q.M, Q.K, Q.batch, Q.a_m, Q.a_k, Q.a_b, Q.elem);
         plan.tb = classify(Q.b, Q.N, Q.K, Q.batch, Q.b_n, Q.b_k, Q.b_b, Q.elem);
         if (!plan.ta.ok || !plan.tb.ok) tc = false;
-        if (Q.N > 1 && Q.o_m < (long long)Q.N && Q.M > 1) tc = false;   // overlapping output rows
+        if (!skinny_swap && Q.N > 1 && Q.o_m < (long long)Q.N && Q.M > 1) tc = false;   // overlapping output rows
     }
     // Float32 runs on the tensor cores as 3 x TF32 once the problem is large enough to pay for
     // it; below that the strided kernel is as fast and keeps the reference's exact arithmetic
@@ -367,7 +371,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
         plan.pub.tiles = (int32_t)(tm * tn * P.batch);
         plan.pub.ctas = plan.pub.tiles;
         plan.pub.dynamicSmemBytes = 0;
-        return;
+        return !skinny_swap;
     }
 
     plan.Q = Q;
@@ -459,7 +463,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
                 plan.pub.stages = 1;
                 plan.pub.tiles = (int32_t)(((P.M + st - 1) / st) * ((P.N + st - 1) / st) * P.batch);
                 plan.pub.ctas = plan.pub.tiles;
-                return;
+                return !skinny_swap;
             }
             splits = 1; kb_per_split = k_blocks;
         }
@@ -484,6 +488,22 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     plan.pub.splitK = (int32_t)splits;
     plan.pub.workspaceBytes = splits > 1 ? (size_t)splits * Q.batch * Q.M * Q.N * 4 : 0;
     plan.pub.dynamicSmemBytes = (size_t)stages * stage_bytes + kEpilogueStagingBytes + 1024;
+    // the transposed plan of a row-major result needs the reduce pass to place the elements
+    return !skinny_swap || (plan.pub.kernel == srtMatmulKernelTcgen05 && splits > 1);
+}
+
+void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
+{
+    // A few rows against a wide operand (a small batch through a Dense layer): as given, the rows
+    // occupy a fraction of the MMA's 128 and every 64 columns cost a whole tile.  Transposed, the
+    // wide dimension is tiled 128 at a time and the rows are the MMA's N (64): half the MMA
+    // instructions per unit of work at the same number of units.
+    const Choice choice = effective_choice(P);
+    const bool untuned = choice.force == 0 && choice.tile_n == 0 && choice.stages == 0 && choice.max_ctas == 0 && choice.split_k == 0;
+    if (untuned && dev.sm100 && P.type != real32F && P.batch == 1 && P.M >= 1 && P.M <= 64 && P.N >= 512 && P.K >= 1024 &&
+        P.o_n == 1 && make_plan_impl(P, dev, plan, true))
+        return;
+    make_plan_impl(P, dev, plan, false);
 }
 
 // ------------------------------------------------------------------ tensor maps
@@ -879,9 +899,33 @@ cudaError_t launch_reduce_as_dependent(const ReduceParams& rp, unsigned blocks, 
     return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<T, VEC>, rp);
 }
 
+template <typename T>
+cudaError_t launch_reduce_transposed(const ReduceParams& rp, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((rp.N + 31) / 32, (rp.M + 31) / 32, rp.batch);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_transposed_kernel<T>, rp);
+}
+
 cudaError_t launch_reduce(const Prepared& pr, cudaStream_t stream)
 {
     const ReduceParams& rp = pr.rp;
+    // output contiguous along M: reduce through a shared-memory transpose (grid.y and grid.z limits permitting)
+    if (rp.o_m == 1 && rp.o_n != 1 && rp.M > 1 && (rp.M + 31) / 32 <= 65535 && rp.batch <= 65535) {
+        switch (pr.type) {
+        case real32F: return launch_reduce_transposed<float>(rp, stream);
+        case real16F: return launch_reduce_transposed<__half>(rp, stream);
+        default: return launch_reduce_transposed<__nv_bfloat16>(rp, stream);
+        }
+    }
     const unsigned blocks = pr.reduce_blocks;
     const bool v4 = pr.reduce_vec == 4;
     switch (pr.type) {

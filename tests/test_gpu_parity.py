@@ -552,3 +552,31 @@ def test_small_shape_sweep_with_guard_bands(srt, oracle, dtype, kernel):
                     assert err <= TOL[dtype], (M, N, K, err)
                 assert bool((canvas[:guard] == 3.0).all()) and bool((canvas[guard + M * N:] == 3.0).all()), (M, N, K)
     assert srt.check_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [BF16, F16])
+@pytest.mark.parametrize("M,K,N,transposed", [(1, 1024, 512, False), (1, 4096, 4096, True), (8, 4096, 4096, True),
+                                              (33, 2048, 1000, True), (64, 4096, 4096, True), (64, 1024, 8192, False)])
+def test_small_batch_runs_transposed_with_split_k(srt, oracle, dtype, M, K, N, transposed):
+    """A few rows against a wide weight are planned as the transposed problem (the wide dimension
+    fills the MMA's 128 rows) with split-K, whose reduce pass writes the row-major result; bias and
+    activation follow the columns of the result as usual."""
+    rng = np.random.default_rng(M + K + N + dtype)
+    a, b = random_bits(oracle, rng, (M, K), dtype, scale=0.5), random_bits(oracle, rng, (K, N), dtype, scale=0.5)
+    bias = random_bits(oracle, rng, (N,), dtype)
+    ref = oracle.matmul(a, b, dtype, bias=bias, activation="relu")
+    da, db, dbias = to_dev(a, dtype), to_dev(b, dtype), to_dev(bias, dtype)
+    canvas = torch.full((M + 2, N), 9.0, dtype=da.dtype, device="cuda:0")
+    out = canvas[1:M + 1]
+    srt.matmul_into(out, da, False, db, False, dbias, srt.ActivationType.relu)
+    plan = srt.query_plan(da, db, out)
+    if transposed:
+        assert plan["kernel"] == TC and plan["swapped"] == 1 and plan["splitK"] > 1 and plan["tileN"] == 64, plan
+    else:
+        assert plan["swapped"] == 0, plan          # too short a reduction to split: the given orientation
+    err = oracle.rel_frobenius(oracle.decode(from_dev(out, dtype), dtype), oracle.decode(ref, dtype))
+    assert err <= 2e-3, err
+    assert bool((canvas[0] == 9.0).all()) and bool((canvas[M + 1] == 9.0).all())
+    # 65 rows and more, or a weight that is not wide, keep the given orientation
+    big = torch.zeros((65, K), dtype=da.dtype, device="cuda:0")
+    assert srt.query_plan(big, db, torch.zeros((65, N), dtype=da.dtype, device="cuda:0"))["swapped"] == 0
