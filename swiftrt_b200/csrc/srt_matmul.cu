@@ -315,6 +315,8 @@ struct Plan {
 // that the wide dimension fills the 128 rows of the MMA and the few rows of `out` become its N.  Only
 // valid when the plan ends up with split-K, whose reduce pass writes through any output strides;
 // returns false (plan unusable) otherwise.
+constexpr uint64_t kSkinnyRows = 256;     // up to this many rows the transposed plan is tried
+
 bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool skinny_swap)
 {
     memset(&plan.pub, 0, sizeof plan.pub);
@@ -403,6 +405,9 @@ bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool sk
     } else if (force == srtMatmulKernelTcgen05Pair) {
         pair = true;
         if (bn != 128 && bn != 256) bn = Q.N <= 128 ? 128 : 256;
+    } else if (skinny_swap) {
+        pair = false;
+        bn = Q.N <= 64 ? 64 : Q.N <= 128 ? 128 : 256;                   // one column tile holds all the rows of the result
     } else if (bn == 64 || bn == 128 || bn == 256) {
         pair = false;                                                   // explicit single-CTA tile width
     } else {
@@ -500,7 +505,7 @@ void make_plan(const Problem& P, const DeviceInfo& dev, Plan& plan)
     // instructions per unit of work at the same number of units.
     const Choice choice = effective_choice(P);
     const bool untuned = choice.force == 0 && choice.tile_n == 0 && choice.stages == 0 && choice.max_ctas == 0 && choice.split_k == 0;
-    if (untuned && dev.sm100 && P.type != real32F && P.batch == 1 && P.M >= 1 && P.M <= 64 && P.N >= 512 && P.K >= 1024 &&
+    if (untuned && dev.sm100 && P.type != real32F && P.batch == 1 && P.M >= 1 && P.M <= kSkinnyRows && P.N >= 512 && P.K >= 1024 &&
         P.o_n == 1 && make_plan_impl(P, dev, plan, true))
         return;
     make_plan_impl(P, dev, plan, false);

@@ -556,7 +556,8 @@ def test_small_shape_sweep_with_guard_bands(srt, oracle, dtype, kernel):
 
 @pytest.mark.parametrize("dtype", [BF16, F16])
 @pytest.mark.parametrize("M,K,N,transposed", [(1, 1024, 512, False), (1, 4096, 4096, True), (8, 4096, 4096, True),
-                                              (33, 2048, 1000, True), (64, 4096, 4096, True), (64, 1024, 8192, False)])
+                                              (33, 2048, 1000, True), (64, 4096, 4096, True), (64, 1024, 8192, False),
+                                              (100, 4096, 2048, True), (256, 4096, 4096, True)])
 def test_small_batch_runs_transposed_with_split_k(srt, oracle, dtype, M, K, N, transposed):
     """A few rows against a wide weight are planned as the transposed problem (the wide dimension
     fills the MMA's 128 rows) with split-K, whose reduce pass writes the row-major result; bias and
@@ -571,12 +572,13 @@ def test_small_batch_runs_transposed_with_split_k(srt, oracle, dtype, M, K, N, t
     srt.matmul_into(out, da, False, db, False, dbias, srt.ActivationType.relu)
     plan = srt.query_plan(da, db, out)
     if transposed:
-        assert plan["kernel"] == TC and plan["swapped"] == 1 and plan["splitK"] > 1 and plan["tileN"] == 64, plan
+        assert plan["kernel"] == TC and plan["swapped"] == 1 and plan["splitK"] > 1, plan
+        assert plan["tileN"] == (64 if M <= 64 else 128 if M <= 128 else 256), plan
     else:
         assert plan["swapped"] == 0, plan          # too short a reduction to split: the given orientation
     err = oracle.rel_frobenius(oracle.decode(from_dev(out, dtype), dtype), oracle.decode(ref, dtype))
     assert err <= 2e-3, err
     assert bool((canvas[0] == 9.0).all()) and bool((canvas[M + 1] == 9.0).all())
-    # 65 rows and more, or a weight that is not wide, keep the given orientation
-    big = torch.zeros((65, K), dtype=da.dtype, device="cuda:0")
-    assert srt.query_plan(big, db, torch.zeros((65, N), dtype=da.dtype, device="cuda:0"))["swapped"] == 0
+    # more than 256 rows keep the given orientation
+    big = torch.zeros((257, K), dtype=da.dtype, device="cuda:0")
+    assert srt.query_plan(big, db, torch.zeros((257, N), dtype=da.dtype, device="cuda:0"))["swapped"] == 0
