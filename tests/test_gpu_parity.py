@@ -582,3 +582,17 @@ def test_small_batch_runs_transposed_with_split_k(srt, oracle, dtype, M, K, N, t
     # more than 256 rows keep the given orientation
     big = torch.zeros((257, K), dtype=da.dtype, device="cuda:0")
     assert srt.query_plan(big, db, torch.zeros((257, N), dtype=da.dtype, device="cuda:0"))["swapped"] == 0
+
+
+@pytest.mark.parametrize("ta,tb", TRANSPOSES)
+def test_small_batch_transposed_plan_all_transposes(srt, oracle, ta, tb):
+    rng = np.random.default_rng(5 + 2 * ta + tb)
+    M, K, N = 24, 2048, 1536
+    ash, bsh = _shapes(M, N, K, ta, tb)
+    a, b = random_bits(oracle, rng, ash, BF16, scale=0.5), random_bits(oracle, rng, bsh, BF16, scale=0.5)
+    bias = random_bits(oracle, rng, (N,), BF16)
+    got, ref = _run(srt, oracle, BF16, a, b, ta, tb, bias=bias, act="gelu")
+    assert oracle.rel_frobenius(oracle.decode(got, BF16), oracle.decode(ref, BF16)) <= 2e-3
+    da, db = to_dev(a, BF16), to_dev(b, BF16)
+    plan = srt.query_plan(da, db, torch.empty((M, N), dtype=torch.bfloat16, device="cuda:0"), ta, tb)
+    assert plan["swapped"] == 1 and plan["splitK"] > 1, plan
