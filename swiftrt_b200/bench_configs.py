@@ -167,6 +167,32 @@ def run_lstm(dev, iters: int, flush: torch.Tensor, peaks: dict, batch: int = 409
     return rec
 
 
+def run_small_batch(dev, iters: int, flush: torch.Tensor, peaks: dict) -> list:
+    """s1: a few rows through a 4096 x 4096 Dense layer (bias + ReLU), bf16, cold L2; the same with
+    torch.addmm + ReLU (cuBLAS) beside it."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf16 = torch.bfloat16
+    w = _uniform((4096, 4096), bf16, dev, g, -0.5, 0.5)
+    b = _uniform((4096,), bf16, dev, g, -0.5, 0.5)
+    out = []
+    for rows in (1, 8, 32, 64, 128, 256):
+        x = _uniform((rows, 4096), bf16, dev, g, -0.5, 0.5)
+        y = torch.empty((rows, 4096), dtype=bf16, device=dev)
+        op = srt.MatmulOp(y, x, False, w, False, b, srt.ActivationType.relu)
+        plan = srt.query_plan(x, w, y)
+        med, best = _time_cold(op, iters, flush)
+        t_med, _ = _time_cold(lambda: torch.relu_(torch.addmm(b, x, w)), iters, flush)
+        nbytes = (x.numel() + w.numel() + y.numel() + b.numel()) * 2
+        rec = {"config": "s1", "what": f"Dense bf16 [{rows}x4096].[4096x4096] + bias, ReLU", "kernel": KERNEL_NAMES[plan["kernel"]],
+               "tile": [plan["tileM"], plan["tileN"], plan["tileK"]], "transposed_plan": bool(plan["swapped"]), "splitK": plan["splitK"],
+               "ms_median": med, "ms_best": best, "algorithmic_bytes": nbytes, "gbs": nbytes / med / 1e6, "bound": "hbm",
+               "torch_addmm_relu_ms": t_med}
+        if "hbm_gbs" in peaks:
+            rec["frac_of_measured"] = rec["gbs"] / peaks["hbm_gbs"]
+        out.append(rec)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
@@ -181,11 +207,14 @@ def main():
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
     peaks = measured_peaks()
     only = args.only.split(",") if args.only else []
-    # the callers either side of the product are measured on request only (--only f1,f4)
+    # the callers either side of the product and the small-batch Dense shapes are measured on request only (--only f1,f4,s1)
     if "f1" in only:
         print(json.dumps(run_backward(dev, args.iters, flush, peaks)), flush=True)
     if "f4" in only:
         print(json.dumps(run_lstm(dev, args.iters, flush, peaks)), flush=True)
+    if "s1" in only:
+        for rec in run_small_batch(dev, args.iters, flush, peaks):
+            print(json.dumps(rec), flush=True)
     for make in configs(dev):
         if only and make.__name__ not in only:
             continue
