@@ -279,6 +279,19 @@ cudaError_t srtLstmCell(
     void* newHidden, const srtTensorDescriptor* newHiddenDesc,
     cudaStream_t stream);
 
+/* srtRnnCell: one time step of BasicRNNCell (Sources/SwiftRTLayers/Recurrent.swift:110-161):
+ *     newHidden = tanh(matmul(concatenate(input, hidden, axis: 1), weight) + bias)
+ * weight [(inputSize + hiddenSize) x hiddenSize]; bias [hiddenSize] or, as the reference stores it,
+ * [1 x hiddenSize]; NULL for none.  Two launches: the concatenation and the product with its fused
+ * bias + tanh epilogue. */
+cudaError_t srtRnnCell(
+    const void* input, const srtTensorDescriptor* inputDesc,
+    const void* hidden, const srtTensorDescriptor* hiddenDesc,
+    const void* weight, const srtTensorDescriptor* weightDesc,
+    const void* bias, const srtTensorDescriptor* biasDesc,
+    void* newHidden, const srtTensorDescriptor* newHiddenDesc,
+    cudaStream_t stream);
+
 /* ---- several GPUs of one machine, one process per GPU -----------------------------------------
  *
  * The reference has no multi-GPU path: its only data-parallel construct partitions axis 0 of a

@@ -40,7 +40,7 @@ class MatmulPlan(ctypes.Structure):
 # every symbol include/srt_matmul_api.h declares
 EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString",
-           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell",
+           "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell", "srtRnnCell",
            "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear"]
 
 if not os.path.exists(SO):
@@ -96,6 +96,8 @@ lib.srtPeerMemFree.argtypes = [_P]
 
 lib.srtLstmCell.restype = ctypes.c_int
 lib.srtLstmCell.argtypes = [_P, _D] * 7 + [_P]
+lib.srtRnnCell.restype = ctypes.c_int
+lib.srtRnnCell.argtypes = [_P, _D] * 5 + [_P]
 lib.srtMatmulTune.restype = ctypes.c_int
 lib.srtMatmulTune.argtypes = [_P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_int, _P, _D, _P,
                               ctypes.POINTER(MatmulPlan), ctypes.POINTER(ctypes.c_float)]

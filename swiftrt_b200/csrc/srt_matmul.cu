@@ -1581,6 +1581,67 @@ cudaError_t srtLstmCell(const void* input, const srtTensorDescriptor* inputDesc,
                              : launch_lstm_elementwise<__nv_bfloat16>(nullptr, &gp, stream);
 }
 
+// ------------------------------------------------------------------ srtRnnCell
+cudaError_t srtRnnCell(const void* input, const srtTensorDescriptor* inputDesc, const void* hidden,
+                       const srtTensorDescriptor* hiddenDesc, const void* weight, const srtTensorDescriptor* weightDesc,
+                       const void* bias, const srtTensorDescriptor* biasDesc, void* newHidden,
+                       const srtTensorDescriptor* newHiddenDesc, cudaStream_t stream)
+{
+    if (!input || !hidden || !weight || !newHidden || !inputDesc)
+        return fail(cudaErrorInvalidValue, "srtRnnCell: null tensor");
+    const srtDataType type = inputDesc->type;
+    if (type != real32F && type != real16F && type != real16BF)
+        return fail(cudaErrorNotSupported, "srtRnnCell: element type %d is outside this library", (int)type);
+    uint64_t rows, nx, r2, nh, wk, wn, r3, c3;
+    long long x_m, x_n, h_m, h_n, w_m, w_n, o_m, o_n;
+    cudaError_t e;
+    if ((e = view2(inputDesc, "input", type, rows, nx, x_m, x_n)) != cudaSuccess) return e;
+    if ((e = view2(hiddenDesc, "hidden", type, r2, nh, h_m, h_n)) != cudaSuccess) return e;
+    if ((e = view2(weightDesc, "weight", type, wk, wn, w_m, w_n)) != cudaSuccess) return e;
+    if ((e = view2(newHiddenDesc, "newHidden", type, r3, c3, o_m, o_n)) != cudaSuccess) return e;
+    if (r2 != rows || r3 != rows || c3 != nh || wk != nx + nh || wn != nh)
+        return fail(cudaErrorInvalidValue, "srtRnnCell: weight must be [(inputSize + hiddenSize) x hiddenSize], states [batch x hiddenSize]");
+    // the reference keeps the bias as a [1 x hiddenSize] matrix (Recurrent.swift:139); a vector is accepted too
+    srtTensorDescriptor bias1;
+    size_t b_shape[1], b_strides[1];
+    if (bias) {
+        if (!biasDesc || biasDesc->type != type || !biasDesc->shape || !biasDesc->strides)
+            return fail(cudaErrorInvalidValue, "srtRnnCell: bias without a matching descriptor");
+        const bool vec = biasDesc->rank == 1 && biasDesc->shape[0] == nh;
+        const bool row = biasDesc->rank == 2 && biasDesc->shape[0] == 1 && biasDesc->shape[1] == nh;
+        if (!vec && !row) return fail(cudaErrorInvalidValue, "srtRnnCell: bias must be [hiddenSize] or [1 x hiddenSize]");
+        bias1 = *biasDesc;
+        bias1.rank = 1;
+        b_shape[0] = (size_t)nh;
+        b_strides[0] = vec ? biasDesc->strides[0] : biasDesc->strides[1];
+        bias1.shape = b_shape; bias1.strides = b_strides; bias1.logicalStrides = b_strides;
+        bias1.count = (size_t)nh; bias1.spanCount = 1 + (size_t)(nh - 1) * b_strides[0];
+    }
+    if (rows == 0 || nh == 0) return cudaSuccess;
+    if (rows > 0xffffffffull || nx + nh > 0xffffffffull) return fail(cudaErrorNotSupported, "srtRnnCell: extents beyond 32 bits");
+    const size_t elem = type == real32F ? 4 : 2;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    void* gate_in = nullptr;
+    if ((e = workspace_for(dev, stream, (size_t)rows * (nx + nh) * elem, &gate_in, 1)) != cudaSuccess) return e;
+    ConcatParams cp;
+    cp.x = input; cp.h = hidden; cp.out = gate_in;
+    cp.x_m = x_m; cp.x_n = x_n; cp.h_m = h_m; cp.h_n = h_n;
+    cp.rows = (uint32_t)rows; cp.nx = (uint32_t)nx; cp.nh = (uint32_t)nh;
+    e = type == real32F ? launch_lstm_elementwise<float>(&cp, nullptr, stream)
+        : type == real16F ? launch_lstm_elementwise<__half>(&cp, nullptr, stream)
+                          : launch_lstm_elementwise<__nv_bfloat16>(&cp, nullptr, stream);
+    if (e != cudaSuccess) return e;
+    size_t g_shape[2] = {(size_t)rows, (size_t)(nx + nh)}, g_strides[2] = {(size_t)(nx + nh), 1};
+    srtTensorDescriptor gd;
+    memset(&gd, 0, sizeof gd);
+    gd.type = type; gd.rank = 2; gd.order = srtOrderRow; gd.count = g_shape[0] * g_shape[1]; gd.spanCount = gd.count;
+    gd.shape = g_shape; gd.strides = g_strides; gd.logicalStrides = g_strides;
+    // newState = tanh(matmul(concatenate(input, state), weight) + bias): the fused epilogue does the rest
+    return srtMatmulBiasActivation(gate_in, &gd, false, weight, weightDesc, false, bias, bias ? &bias1 : nullptr, srtActivationTanh,
+                                   newHidden, newHiddenDesc, stream);
+}
+
 // ------------------------------------------------------------------ srtMatmulNoAlloc
 // Scratch of the entry point below.  It is part of the library image: every device that loads
 // the library carries these 16 MiB from then until the process ends, whether or not the entry

@@ -61,6 +61,35 @@ class LSTMCell:
         return LSTMState(new_cell, new_hidden)
 
 
+class BasicRNNCell:
+    """BasicRNNCell (Recurrent.swift:110-161): weight [(inputSize + hiddenSize) x hiddenSize], bias
+    [1 x hiddenSize] (or a vector); newState = tanh(matmul(concatenate(input, state), weight) + bias)."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None):
+        if weight.dim() != 2:
+            raise ValueError("weight must be [(inputSize + hiddenSize) x hiddenSize]")
+        self.weight = weight
+        self.bias = bias
+        self.hidden_size = int(weight.shape[1])
+
+    def zero_state(self, input: torch.Tensor) -> torch.Tensor:
+        """zeroState(for:) (Recurrent.swift:146-150)."""
+        return torch.zeros((input.shape[0], self.hidden_size), dtype=input.dtype, device=input.device)
+
+    def __call__(self, input: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        new_state = torch.empty_like(state, memory_format=torch.contiguous_format)
+        tensors = (input, state, self.weight, self.bias, new_state)
+        descs = [_descriptor(t) if t is not None else None for t in tensors]
+        args = []
+        for t, d in zip(tensors, descs):
+            args += [t.data_ptr() if t is not None else None, d.ref() if d is not None else None]
+        with torch.cuda.device(input.device):
+            rc = lib.srtRnnCell(*args, torch.cuda.current_stream(input.device).cuda_stream)
+        if rc != _lib.cudaSuccess:
+            raise MatmulError(rc, _lib.last_error())
+        return new_state
+
+
 def run_sequence(cell: LSTMCell, inputs: Sequence[torch.Tensor], initial_state: LSTMState | None = None) -> list[LSTMState]:
     """RecurrentLayer.callAsFunction(_:initialState:) (Recurrent.swift:356-370): the cell applied to
     every time step in order, each step's state feeding the next; returns the state after every step."""

@@ -169,3 +169,27 @@ def test_sequence_captured_in_a_cuda_graph(srt, kat):
     t_graph = wall(lambda: graphed.graph.replay())
     print(f"4-step LSTM sequence: eager {t_eager:.1f} us, graph replay {t_graph:.1f} us")
     assert t_graph < t_eager
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16, F16])
+@pytest.mark.parametrize("batch,nx,nh,bias_rank", [(3, 5, 7, 2), (64, 96, 128, 1), (32, 1024, 1024, 2)])
+def test_basic_rnn_cell_matches_oracle(srt, oracle, dtype, batch, nx, nh, bias_rank):
+    """BasicRNNCell (Recurrent.swift:110-161): tanh(matmul(concatenate(input, state), weight) + bias) with the
+    bias as the reference keeps it ([1 x hiddenSize]) or as a vector."""
+    rng = np.random.default_rng(batch + nx + nh + dtype)
+    x = random_bits(oracle, rng, (batch, nx), dtype)
+    h = random_bits(oracle, rng, (batch, nh), dtype)
+    w = random_bits(oracle, rng, (nx + nh, nh), dtype, scale=1.0 / np.sqrt(nx + nh))
+    b = random_bits(oracle, rng, (nh,), dtype, scale=0.5)
+    ref = oracle.matmul(np.ascontiguousarray(np.concatenate([x, h], axis=1)), w, dtype, bias=b, activation="tanh")
+    dbias = to_dev(b, dtype)
+    cell = srt.BasicRNNCell(to_dev(w, dtype), dbias.reshape(1, nh) if bias_rank == 2 else dbias)
+    before = srt.launch_count()
+    out = cell(to_dev(x, dtype), to_dev(h, dtype))
+    torch.cuda.synchronize()
+    assert srt.check_status() == 0 and 2 <= srt.launch_count() - before <= 3
+    err = oracle.rel_frobenius(oracle.decode(from_dev(out, dtype), dtype), oracle.decode(ref, dtype))
+    assert err <= TOL[dtype], err
+    assert cell.zero_state(to_dev(x, dtype)).shape == (batch, nh)
+    with pytest.raises(srt.MatmulError):
+        srt.BasicRNNCell(to_dev(w, dtype), to_dev(b[:-1].copy(), dtype))(to_dev(x, dtype), to_dev(h, dtype))
