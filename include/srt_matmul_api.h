@@ -175,7 +175,7 @@ typedef struct {
     int32_t stages;        /* shared-memory pipeline depth */
     int32_t ctas;          /* grid size (persistent CTAs) */
     int32_t tiles;         /* output tiles over all batch items */
-    int32_t swapped;       /* 1 when computed as out^T = op(b)^T . op(a)^T (col-order out) */
+    int32_t swapped;       /* 1 when computed as out^T = op(b)^T . op(a)^T (col-order out; a few rows against a wide operand) */
     int32_t aMajor, bMajor;/* 0 = K-major, 1 = MN-major operand as the kernel sees it */
     int32_t fp32Split;     /* 1 when fp32 runs as 3 x TF32 on the tensor cores */
     int32_t splitK;        /* > 1: the reduction is cut into this many parts, summed by a second kernel */
