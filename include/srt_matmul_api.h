@@ -267,6 +267,9 @@ cudaError_t srtMatmulNoAlloc(
  * input [batch x inputSize], hidden / cell / newCell / newHidden [batch x hiddenSize], fusedWeight
  * [(inputSize + hiddenSize) x 4 hiddenSize], fusedBias [4 hiddenSize] (may be NULL); all of one element
  * type, rank 2 (bias rank 1), any strides.  newCell may alias cell and newHidden may alias hidden.
+ * hidden may be NULL when `input` is the concatenation already, [batch x (inputSize + hiddenSize)] (a caller
+ * that keeps the hidden state inside its gate-input buffer saves the concatenation; newHidden may then be a
+ * view into the next step's gate input).
  * Three launches on `stream`: a concatenation, the product (srtMatmulBiasActivation) and the gate
  * pass; the two intermediates live in the library's per-(device, stream) workspace. */
 cudaError_t srtLstmCell(

@@ -1514,16 +1514,24 @@ cudaError_t srtLstmCell(const void* input, const srtTensorDescriptor* inputDesc,
                         const srtTensorDescriptor* biasDesc, void* newCell, const srtTensorDescriptor* newCellDesc,
                         void* newHidden, const srtTensorDescriptor* newHiddenDesc, cudaStream_t stream)
 {
-    if (!input || !hidden || !cell || !fusedWeight || !newCell || !newHidden || !inputDesc)
+    if (!input || !cell || !fusedWeight || !newCell || !newHidden || !inputDesc)
         return fail(cudaErrorInvalidValue, "srtLstmCell: null tensor");
     const srtDataType type = inputDesc->type;
     if (type != real32F && type != real16F && type != real16BF)
         return fail(cudaErrorNotSupported, "srtLstmCell: element type %d is outside this library", (int)type);
     uint64_t rows, nx, r2, nh, r3, c3, wk, wn, r4, c4, r5, c5;
-    long long x_m, x_n, h_m, h_n, c_m, c_n, w_m, w_n, nc_m, nc_n, nh_m, nh_n;
+    long long x_m, x_n, h_m = 0, h_n = 0, c_m, c_n, w_m, w_n, nc_m, nc_n, nh_m, nh_n;
     cudaError_t e;
     if ((e = view2(inputDesc, "input", type, rows, nx, x_m, x_n)) != cudaSuccess) return e;
-    if ((e = view2(hiddenDesc, "hidden", type, r2, nh, h_m, h_n)) != cudaSuccess) return e;
+    // hidden == NULL: `input` is the gate input already, [batch x (inputSize + hiddenSize)], and nothing is concatenated
+    const bool preconcatenated = hidden == nullptr;
+    if (preconcatenated) {
+        if ((e = view2(cellDesc, "cell", type, r2, nh, c_m, c_n)) != cudaSuccess) return e;
+        if (nx < nh) return fail(cudaErrorInvalidValue, "srtLstmCell: a gate input has at least hiddenSize columns");
+        nx -= nh;
+    } else if ((e = view2(hiddenDesc, "hidden", type, r2, nh, h_m, h_n)) != cudaSuccess) {
+        return e;
+    }
     if ((e = view2(cellDesc, "cell", type, r3, c3, c_m, c_n)) != cudaSuccess) return e;
     if ((e = view2(weightDesc, "fusedWeight", type, wk, wn, w_m, w_n)) != cudaSuccess) return e;
     if ((e = view2(newCellDesc, "newCell", type, r4, c4, nc_m, nc_n)) != cudaSuccess) return e;
@@ -1546,26 +1554,30 @@ cudaError_t srtLstmCell(const void* input, const srtTensorDescriptor* inputDesc,
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     void* ws = nullptr;
     if ((e = workspace_for(dev, stream, gate_bytes + fused_bytes, &ws, 1)) != cudaSuccess) return e;
-    void* gate_in = ws;
+    const void* gate_in = preconcatenated ? input : ws;
     void* fused = static_cast<char*>(ws) + gate_bytes;
 
-    ConcatParams cp;
-    cp.x = input; cp.h = hidden; cp.out = gate_in;
-    cp.x_m = x_m; cp.x_n = x_n; cp.h_m = h_m; cp.h_n = h_n;
-    cp.rows = (uint32_t)rows; cp.nx = (uint32_t)nx; cp.nh = (uint32_t)nh;
-    e = type == real32F ? launch_lstm_elementwise<float>(&cp, nullptr, stream)
-        : type == real16F ? launch_lstm_elementwise<__half>(&cp, nullptr, stream)
-                          : launch_lstm_elementwise<__nv_bfloat16>(&cp, nullptr, stream);
-    if (e != cudaSuccess) return e;
+    if (!preconcatenated) {
+        ConcatParams cp;
+        cp.x = input; cp.h = hidden; cp.out = ws;
+        cp.x_m = x_m; cp.x_n = x_n; cp.h_m = h_m; cp.h_n = h_n;
+        cp.rows = (uint32_t)rows; cp.nx = (uint32_t)nx; cp.nh = (uint32_t)nh;
+        e = type == real32F ? launch_lstm_elementwise<float>(&cp, nullptr, stream)
+            : type == real16F ? launch_lstm_elementwise<__half>(&cp, nullptr, stream)
+                              : launch_lstm_elementwise<__nv_bfloat16>(&cp, nullptr, stream);
+        if (e != cudaSuccess) return e;
+    }
 
     // fused = gateInput . fusedWeight + fusedBias, rounded to the element type (what matmul(bias:) returns)
-    size_t g_shape[2] = {(size_t)rows, (size_t)(nx + nh)}, g_strides[2] = {(size_t)(nx + nh), 1};
+    size_t g_shape[2] = {(size_t)rows, (size_t)(nx + nh)};
+    size_t g_strides[2] = {preconcatenated ? (size_t)x_m : (size_t)(nx + nh), preconcatenated ? (size_t)x_n : (size_t)1};
     size_t f_shape[2] = {(size_t)rows, (size_t)(4 * nh)}, f_strides[2] = {(size_t)(4 * nh), 1};
     srtTensorDescriptor gd, fd;
     memset(&gd, 0, sizeof gd);
     gd.type = type; gd.rank = 2; gd.order = srtOrderRow; gd.count = g_shape[0] * g_shape[1]; gd.spanCount = gd.count;
     gd.shape = g_shape; gd.strides = g_strides; gd.logicalStrides = g_strides;
     fd = gd;
+    fd.strides = f_strides; fd.logicalStrides = f_strides;
     fd.count = f_shape[0] * f_shape[1]; fd.spanCount = fd.count;
     fd.shape = f_shape; fd.strides = f_strides; fd.logicalStrides = f_strides;
     e = srtMatmulBiasActivation(gate_in, &gd, false, fusedWeight, weightDesc, false, fusedBias, biasDesc, srtActivationIdentity,

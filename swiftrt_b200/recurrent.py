@@ -61,6 +61,43 @@ class LSTMCell:
         return LSTMState(new_cell, new_hidden)
 
 
+def _lstm_call(cell: "LSTMCell", input, hidden, cell_state, new_cell, new_hidden) -> None:
+    tensors = (input, hidden, cell_state, cell.fused_weight, cell.fused_bias, new_cell, new_hidden)
+    descs = [_descriptor(t) if t is not None else None for t in tensors]
+    args = []
+    for t, d in zip(tensors, descs):
+        args += [t.data_ptr() if t is not None else None, d.ref() if d is not None else None]
+    with torch.cuda.device(input.device):
+        rc = lib.srtLstmCell(*args, torch.cuda.current_stream(input.device).cuda_stream)
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+
+
+def run_sequence_preconcatenated(cell: "LSTMCell", inputs: Sequence[torch.Tensor],
+                                 initial_state: "LSTMState | None" = None) -> list:
+    """run_sequence without the per-step concatenation: one buffer [T][batch][inputSize + hiddenSize]
+    holds every step's gate input, the inputs are copied into its left columns once, and each
+    step writes its hidden state straight into the right columns of the next step's row block
+    (srtLstmCell with hidden = NULL).  Two launches per step instead of three; the returned hidden
+    states are views into that buffer."""
+    if not inputs:
+        return []
+    x0 = inputs[0]
+    batch, nx, nh, steps = x0.shape[0], x0.shape[1], cell.hidden_size, len(inputs)
+    state = initial_state if initial_state is not None else cell.zero_state(x0)
+    gate = torch.empty((steps, batch, nx + nh), dtype=x0.dtype, device=x0.device)
+    gate[:, :, :nx].copy_(torch.stack(list(inputs)))
+    gate[0, :, nx:].copy_(state.hidden)
+    outputs, c = [], state.cell
+    for t in range(steps):
+        new_cell = torch.empty_like(c, memory_format=torch.contiguous_format)
+        new_hidden = gate[t + 1, :, nx:] if t + 1 < steps else torch.empty((batch, nh), dtype=x0.dtype, device=x0.device)
+        _lstm_call(cell, gate[t], None, c, new_cell, new_hidden)
+        outputs.append(LSTMState(new_cell, new_hidden))
+        c = new_cell
+    return outputs
+
+
 class BasicRNNCell:
     """BasicRNNCell (Recurrent.swift:110-161): weight [(inputSize + hiddenSize) x hiddenSize], bias
     [1 x hiddenSize] (or a vector); newState = tanh(matmul(concatenate(input, state), weight) + bias)."""

@@ -193,3 +193,30 @@ def test_basic_rnn_cell_matches_oracle(srt, oracle, dtype, batch, nx, nh, bias_r
     assert cell.zero_state(to_dev(x, dtype)).shape == (batch, nh)
     with pytest.raises(srt.MatmulError):
         srt.BasicRNNCell(to_dev(w, dtype), to_dev(b[:-1].copy(), dtype))(to_dev(x, dtype), to_dev(h, dtype))
+
+
+def test_sequence_without_per_step_concatenation(srt, kat, oracle):
+    """The hidden state lives inside the next step's gate input: same results, two launches per step."""
+    cell = srt.LSTMCell(_t(kat["fused_weight"]), _t(kat["fused_bias"]))
+    state = srt.LSTMState(_t([kat["initial_cell"]]), _t([kat["initial_hidden"]]))
+    inputs = [_t([x]) for x in kat["inputs"]]
+    eager = srt.run_sequence(cell, inputs, state)
+    before = srt.launch_count()
+    fused = srt.run_sequence_preconcatenated(cell, inputs, state)
+    torch.cuda.synchronize()
+    assert srt.launch_count() - before == 4 * 2
+    for a, b in zip(eager, fused):
+        assert torch.equal(a.cell, b.cell) and torch.equal(a.hidden, b.hidden)
+    # a larger bf16 case through the tensor-core kernels, strided gate input and hidden views included
+    rng = np.random.default_rng(3)
+    batch, nx, nh, steps = 128, 256, 512, 3
+    w = to_dev(random_bits(oracle, rng, (nx + nh, 4 * nh), BF16, scale=0.04), BF16)
+    b = to_dev(random_bits(oracle, rng, (4 * nh,), BF16, scale=0.5), BF16)
+    cell2 = srt.LSTMCell(w, b)
+    xs = [to_dev(random_bits(oracle, rng, (batch, nx), BF16), BF16) for _ in range(steps)]
+    ref = srt.run_sequence(cell2, xs)
+    got = srt.run_sequence_preconcatenated(cell2, xs)
+    torch.cuda.synchronize()
+    assert srt.check_status() == 0
+    for a, c in zip(ref, got):
+        assert torch.equal(a.cell, c.cell) and torch.equal(a.hidden, c.hidden)
