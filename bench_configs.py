@@ -1,7 +1,7 @@
 """Times the five named configurations of the matmul path on one GPU and prints one JSON record
 per configuration (shape, kernel, ms, algorithmic TFLOP/s and GB/s, roofline fractions).
 
-    python -m swiftrt_b200.bench_configs [--iters 20] [--only c3]
+    python bench_configs.py [--iters 20] [--only c3]
 
 Inputs are seeded synthetic draws with the shapes and value distributions of the configurations;
 between timed launches a buffer larger than the L2 cache is read (not written: dirty lines would
@@ -16,9 +16,12 @@ import argparse
 import json
 import os
 
+import sys
+
 import torch
 
-import swiftrt_b200 as srt
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import swiftrt_b200 as srt  # noqa: E402
 
 NOMINAL = {"bf16_tflops": 2250.0, "hbm_gbs": 8000.0}
 KERNEL_NAMES = {1: "gemm_simt_kernel", 2: "gemm_tcgen05_kernel", 3: "gemm_tcgen05_pair_kernel",
@@ -26,7 +29,7 @@ KERNEL_NAMES = {1: "gemm_simt_kernel", 2: "gemm_tcgen05_kernel", 3: "gemm_tcgen0
 
 
 def measured_peaks() -> dict:
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             return json.load(f)

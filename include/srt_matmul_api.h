@@ -6,7 +6,13 @@
  *                       void* out, const srtTensorDescriptor* oDesc, cudaStream_t stream);
  * (Modules/SwiftRTCuda/math_api.h:75-87).  Pointers are device addresses of the first
  * element of the view; descriptors and their arrays only need to live for the call;
- * work is enqueued on `stream` and the call returns without synchronising.
+ * work is enqueued on `stream` and the call returns without synchronising (a split-K
+ * workspace that has to grow is replaced without waiting: the old buffer is freed in stream
+ * order).  Every call works on the device that `stream` belongs to, whatever device is
+ * current on the calling thread (it is made current for the duration of the call and the
+ * caller's device restored): the reference's queues launch on their stream without selecting
+ * a device (platform/cuda/functions/CudaMath.swift:117-125), and so may callers of this
+ * library.  The legacy and per-thread default streams mean the current device.
  * cudaErrorNotSupported means "this dtype / layout is outside this library" (the Swift
  * caller then takes its own CPU route, cuda/device/CudaPlatform.swift:135-144); any
  * other non-zero code is an error.  The library has no CPU fallback and calls no
@@ -144,8 +150,12 @@ cudaError_t srtMatmulBiasActivation(
  * (MathDerivatives.swift:460-482): dX = dz . W^T, dW = X^T . dz.
  * dy, y, dz: rank 2 [M x N] or rank 3 [batch x M x N], same type and shape, any strides.  y may
  * be NULL for srtActivationIdentity; dz or dbias may be NULL when not wanted; dz may alias dy.
- * identity, relu, sigmoid and tanh are computed; gelu and the coefficient activations return
- * cudaErrorNotSupported.  The column sums use the library's per-(device, stream) workspace.
+ * identity, relu, sigmoid and tanh take the forward output in `y`.  GELU is not a function of its
+ * own output: for srtActivationGelu and srtActivationGeluTanh `y` must hold the PRE-activation
+ * values z = op(a).op(b) + bias (the result of srtMatmulBiasActivation with
+ * srtActivationIdentity; srtActivationForward then gives the layer's output), and
+ * dz = dy * gelu'(z).  The coefficient activations return cudaErrorNotSupported.  The column sums
+ * use the library's per-(device, stream) workspace.
  */
 cudaError_t srtBiasActivationBackward(
     const void* dy, const srtTensorDescriptor* dyDesc,
@@ -153,6 +163,17 @@ cudaError_t srtBiasActivationBackward(
     srtActivationType activation,
     void* dz, const srtTensorDescriptor* dzDesc,
     void* dbias, const srtTensorDescriptor* dbiasDesc,
+    cudaStream_t stream);
+
+/* srtActivationForward: y = activation(z), elementwise, one rounding.  z, y: rank 2 or 3, same
+ * type and shape, any strides; y may alias z.  For layers that keep their pre-activation values for
+ * the backward pass (GELU): the product runs with srtActivationIdentity into z, this call produces
+ * the layer's output, and srtBiasActivationBackward receives z.  Stands in for the reference's
+ * separate activation call (platform/cuda/layers/CudaActivation.swift:61-83). */
+cudaError_t srtActivationForward(
+    const void* z, const srtTensorDescriptor* zDesc,
+    srtActivationType activation,
+    void* y, const srtTensorDescriptor* yDesc,
     cudaStream_t stream);
 
 /* ---------------------------------------------------------------------------------------
@@ -227,6 +248,14 @@ cudaError_t srtMatmulPlanCacheClear(void);
  * keeps per (device, stream) and grows on demand with cudaMalloc. */
 cudaError_t srtMatmulSetSplitK(int32_t splits);
 
+/* Frees the per-(device, stream) workspaces (split-K partial sums, column-sum partials, the
+ * recurrent cells' intermediates) after synchronising their devices; later calls allocate again.
+ * A workspace that was handed out while its stream was being captured is part of a CUDA graph that
+ * may still be replayed: it is kept unless `includeCaptured` is true (pass true only when those
+ * graphs will not run again).  Stands in for MatmulPreferences.maxWorkspaceSize = 0
+ * (platform/cuda/cublaslt/MatmulPreferences.swift:85-254) as the way to give scratch back. */
+cudaError_t srtMatmulReleaseWorkspaces(bool includeCaptured);
+
 /* srtMatmulNoAlloc: srtMatmul for callers that must not allocate device memory.
  *
  * This entry point has no counterpart in the reference.  It exists for hosts that cannot call
@@ -245,6 +274,12 @@ cudaError_t srtMatmulSetSplitK(int32_t splits);
  *  - the first call on a device looks up the scratch array's device address
  *    (cudaGetSymbolAddress, with that device current); make that first call outside any stream
  *    capture;
+ *  - "allocates nothing" holds once the kernels a call launches are resident: under CUDA's lazy
+ *    module loading the first launch of each kernel variant (per element type, tile width and
+ *    reduce pass) loads its code, which takes device memory inside the driver.  Make the first
+ *    call for each shape class where that is allowed (at start-up), as with the capture note;
+ *  - repeated calls with the same arguments reuse the prepared launch (no planning, no tensor-map
+ *    encoding), like srtMatmul;
  *  - all calls on a device share the one array: two split-K calls that overlap on the GPU (on
  *    different streams) corrupt each other's partial sums.  Calls on one stream are safe.  The
  *    array keeps what the last call wrote; no call depends on its previous contents.
@@ -292,6 +327,27 @@ cudaError_t srtRnnCell(
     const void* hidden, const srtTensorDescriptor* hiddenDesc,
     const void* weight, const srtTensorDescriptor* weightDesc,
     const void* bias, const srtTensorDescriptor* biasDesc,
+    void* newHidden, const srtTensorDescriptor* newHiddenDesc,
+    cudaStream_t stream);
+
+/* srtGruCell: one time step of a GRU cell (Sources/SwiftRTLayers/Recurrent.swift:328-337), with the
+ * reference's six products fused into two:
+ *     [reset | update] = sigmoid(concatenate(input, hidden) . gateWeight + gateBias)
+ *     output           = tanh(concatenate(input, reset * hidden) . outputWeight + outputBias)
+ *     newHidden        = (1 - update) * hidden + (1 - update) * output      (as the reference writes it)
+ * gateWeight [(inputSize + hiddenSize) x 2 hiddenSize] holds [[resetWeight1 | updateWeight1],
+ * [resetWeight2 | updateWeight2]], gateBias [2 hiddenSize] = [resetBias | updateBias]; outputWeight
+ * [(inputSize + hiddenSize) x hiddenSize] = [[outputWeight1], [outputWeight2]], outputBias [hiddenSize].
+ * Biases may be NULL.  Five launches on `stream`: the concatenation, two products with fused bias +
+ * sigmoid / tanh epilogues and two elementwise passes; intermediates live in the library's workspace.
+ * newHidden may alias hidden. */
+cudaError_t srtGruCell(
+    const void* input, const srtTensorDescriptor* inputDesc,
+    const void* hidden, const srtTensorDescriptor* hiddenDesc,
+    const void* gateWeight, const srtTensorDescriptor* gateWeightDesc,
+    const void* gateBias, const srtTensorDescriptor* gateBiasDesc,
+    const void* outputWeight, const srtTensorDescriptor* outputWeightDesc,
+    const void* outputBias, const srtTensorDescriptor* outputBiasDesc,
     void* newHidden, const srtTensorDescriptor* newHiddenDesc,
     cudaStream_t stream);
 
@@ -357,7 +413,62 @@ cudaError_t srtMatmulAllGatherMulticast(
     void* multicastOut,
     cudaStream_t stream);
 
-/* Device-side status of the last tensor-core launches on the current device: 0 = all
+/* Which dimension of the result the GPUs divide among themselves. */
+typedef enum {
+    srtShardBatch = 0,   /* batch items (dimension 0 of rank-3 tensors) */
+    srtShardM     = 1,   /* rows of op(a) and of the result */
+    srtShardN     = 2    /* columns of op(b) and of the result (bias entries with them) */
+} srtShardAxis;
+
+/* Balanced contiguous [start, stop) of `total` items for `rank` of `world`; block boundaries are
+ * multiples of `align` (0 or 1: none), the last block takes the remainder.  The arithmetic of the
+ * reference's pmap partitions (Sources/SwiftRTCore/platform/common/pmap.swift:26-72). */
+cudaError_t srtShardRange(size_t total, int32_t world, int32_t rank, size_t align, size_t* start, size_t* stop);
+
+/* srtMatmulSharded: one rank's share of a product divided over `world` GPUs, one process (or one
+ * stream) per GPU.  The descriptors describe the FULL logical tensors; a, b, bias and out point at
+ * this GPU's copies of them (only the owned slices of the sharded operand are read).  The call
+ * narrows the operands and the result to block `rank` along `axis` (srtShardRange; column blocks of
+ * the N axis are aligned to 16 bytes) and runs srtMatmulBiasActivation on the views, writing this
+ * rank's block into its place in `out`.  peerOut[i] (peerCount <= 7, may be 0) is the first element
+ * of the FULL result buffer of another GPU mapped into this process, multicastOut (may be NULL) the
+ * first element of the full result in an NVLink multicast mapping: with either, the block is also
+ * delivered there (srtMatmulAllGather / srtMatmulAllGatherMulticast; a product the multicast form
+ * does not take goes peer by peer when peers are given).  A rank without a block (more ranks than
+ * items) launches nothing.  No collective and no wait for another GPU; completion as for
+ * srtMatmulAllGather.  The GPU form of the reference's pmap (pmap.swift:26-72). */
+cudaError_t srtMatmulSharded(
+    srtShardAxis axis, int32_t world, int32_t rank,
+    const void* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* bias, const srtTensorDescriptor* biasDesc,
+    srtActivationType activation,
+    void* out, const srtTensorDescriptor* oDesc,
+    int32_t peerCount, void* const* peerOut, void* multicastOut,
+    cudaStream_t stream);
+
+/* srtMatmulShardedDevices: the same from ONE process that drives several GPUs (one SwiftRT queue
+ * per device): streams[i] belongs to device i of the call, a[i], b[i], bias[i] (bias may be NULL)
+ * and out[i] are that device's copies of the full tensors.  Block i is enqueued on streams[i]; with
+ * `gather` every block is also stored into the other devices' result buffers (peer access is
+ * enabled on demand), so that after all streams have drained every out[i] holds the whole result.
+ * At most 8 devices.  Returns after enqueuing; synchronise every stream before reading. */
+cudaError_t srtMatmulShardedDevices(
+    srtShardAxis axis, int32_t nDevices, const cudaStream_t* streams,
+    const void* const* a, const srtTensorDescriptor* aDesc, bool transA,
+    const void* const* b, const srtTensorDescriptor* bDesc, bool transB,
+    const void* const* bias, const srtTensorDescriptor* biasDesc,
+    srtActivationType activation,
+    void* const* out, const srtTensorDescriptor* oDesc,
+    bool gather);
+
+/* Wall-clock limit of every pipeline wait inside the tensor-core kernels of the current device, in
+ * nanoseconds (0 restores the default of 2 s).  A wait that runs out ends its kernel in an orderly
+ * way and sets the status word below; the result of that launch is invalid.  For tests of that
+ * path: production code has no reason to change the limit. */
+cudaError_t srtMatmulSetWaitLimit(uint64_t nanoseconds);
+
+/* Device-side status of the last tensor-core launches on the device of `stream`: 0 = all
  * pipeline waits completed; non-zero = a bounded wait gave up (the code says which) and
  * the result of that launch is invalid.  Synchronises `stream` and resets the status. */
 cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status);

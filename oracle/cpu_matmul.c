@@ -389,7 +389,9 @@ int oracle_bias_activation_unfused(int dtype, void* y, size_t rows, size_t cols,
  *   dz = dy * act'(y)   elementwise in the Value type, stored in the element type, with the
  *        derivative written in terms of the forward OUTPUT y, as cuDNN's activation backward
  *        does (platform/cuda/layers/CudaActivation.swift:101-127): relu: y > 0 ? dy : 0,
- *        sigmoid: dy*y*(1-y), tanh: dy*(1-y*y), identity: dy;
+ *        sigmoid: dy*y*(1-y), tanh: dy*(1-y*y), identity: dy; GELU is not a function of its own
+ *        output, so for gelu / geluTanh `y` holds the PRE-activation values z and
+ *        dz = dy * (Phi(z) + z phi(z)), resp. the derivative of 0.5 z (1 + tanh(u(z)));
  *   dbias[n] = sum over rows m = 0..M-1, in order, of dz[m][n]   -- cpu_sum along axis 0
  *        (platform/cpu/functions/CpuReduce.swift:69-96).  The reference's loop keeps the running
  *        sum in the OUTPUT tensor, i.e. rounds it to the element type after every row
@@ -412,6 +414,19 @@ int oracle_bias_activation_backward(int dtype, const void* dy, const void* y, si
             case ORACLE_ACT_RELU: d = o > 0.0f ? g : 0.0f; break;
             case ORACLE_ACT_SIGMOID: { float t = o * (1.0f - o); d = g * t; break; }
             case ORACLE_ACT_TANH: { float t = o * o; t = 1.0f - t; d = g * t; break; }
+            case ORACLE_ACT_GELU: {
+                const float cdf = 0.5f * (1.0f + erff(o * 0.70710678118654752440f));
+                const float pdf = 0.39894228040143267794f * expf(-0.5f * o * o);
+                d = g * (cdf + o * pdf);
+                break;
+            }
+            case ORACLE_ACT_GELU_TANH: {
+                const float u = 0.7978845608028654f * (o + 0.044715f * o * o * o);
+                const float t = tanhf(u);
+                const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * o * o);
+                d = g * (0.5f * (1.0f + t) + 0.5f * o * (1.0f - t * t) * du);
+                break;
+            }
             default: d = g; break;
             }
             store_value(dtype, dz, m * N + n, d);
@@ -425,6 +440,14 @@ int oracle_bias_activation_backward(int dtype, const void* dy, const void* y, si
     if (!stepwise)
         for (size_t n = 0; n < N; ++n) store_value(dtype, dbias, n, acc[n]);
     free(acc);
+    return 0;
+}
+
+/* y = act(z) elementwise over `count` dense elements, one rounding to the element type. */
+int oracle_activation_forward(int dtype, const void* z, void* y, size_t count, int act)
+{
+    if (dtype != ORACLE_F32 && dtype != ORACLE_F16 && dtype != ORACLE_BF16) return -2;
+    for (size_t i = 0; i < count; ++i) store_value(dtype, y, i, activate(act, load_value(dtype, z, i)));
     return 0;
 }
 

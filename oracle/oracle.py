@@ -51,6 +51,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_bias_activation_backward.restype = ctypes.c_int
         L.oracle_bias_activation_backward.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, sz, sz, ctypes.c_int,
                                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        L.oracle_activation_forward.restype = ctypes.c_int
+        L.oracle_activation_forward.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, sz, ctypes.c_int]
         L.oracle_max_threads.restype = ctypes.c_int
         _LIB = L
     return _LIB
@@ -149,6 +151,36 @@ def bias_activation_backward(dy: np.ndarray, y: np.ndarray, dtype: int, activati
     if rc != 0:
         raise ValueError(f"oracle_bias_activation_backward failed with code {rc}")
     return dz, dbias
+
+
+def activation_forward(z: np.ndarray, dtype: int, activation: str) -> np.ndarray:
+    """y = activation(z) on stored bits, fp32 arithmetic, one rounding."""
+    z = np.ascontiguousarray(z)
+    y = np.empty_like(z)
+    rc = lib().oracle_activation_forward(dtype, z.ctypes.data, y.ctypes.data, z.size, ACT[activation])
+    if rc != 0:
+        raise ValueError(f"oracle_activation_forward failed with code {rc}")
+    return y
+
+
+def gru_cell(x: np.ndarray, hidden: np.ndarray, w: dict, dtype: int) -> np.ndarray:
+    """One step of GRUCell.callAsFunction (Sources/SwiftRTLayers/Recurrent.swift:328-337) on stored
+    bits, composed operator by operator as the reference does (every operator result rounded to the
+    element type):
+        reset  = sigmoid(matmul(x, resetW1) + matmul(h, resetW2, bias: resetB))
+        update = sigmoid(matmul(x, updateW1) + matmul(h, updateW2, bias: updateB))
+        output = tanh(matmul(x, outputW1, bias: outputB) + matmul(reset * h, outputW2))
+        new    = (1 - update) * h + (1 - update) * output
+    `w` maps resetW1, resetW2, resetB, updateW1, ... to stored bits.  Returns the new state's bits."""
+    rnd = lambda v: decode(encode(v.astype(np.float32), dtype), dtype)          # noqa: E731
+    mm = lambda a, b, bias=None: decode(matmul(np.ascontiguousarray(a), np.ascontiguousarray(b), dtype, bias=bias), dtype)   # noqa: E731
+    h = decode(hidden, dtype)
+    reset = rnd(_sigmoid32(rnd(mm(x, w["resetW1"]) + mm(hidden, w["resetW2"], w["resetB"]))))
+    update = rnd(_sigmoid32(rnd(mm(x, w["updateW1"]) + mm(hidden, w["updateW2"], w["updateB"]))))
+    rh = encode(rnd(reset * h), dtype)
+    output = rnd(np.tanh(rnd(mm(x, w["outputW1"], w["outputB"]) + mm(rh, w["outputW2"])), dtype=np.float32))
+    keep = rnd(np.float32(1) - update)
+    return encode(rnd(keep * h) + rnd(keep * output), dtype)
 
 
 def _sigmoid32(x: np.ndarray) -> np.ndarray:

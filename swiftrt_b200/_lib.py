@@ -41,7 +41,9 @@ class MatmulPlan(ctypes.Structure):
 EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMatmulSetTuning", "srtMatmulSetSplitK", "srtMatmulNoAlloc", "srtBiasActivationBackward",
            "srtMatmulCheckStatus", "srtMatmulLaunchCount", "srtMatmulGetLastErrorString",
            "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell", "srtRnnCell",
-           "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear"]
+           "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear",
+           "srtActivationForward", "srtMatmulReleaseWorkspaces", "srtGruCell", "srtShardRange", "srtMatmulSharded",
+           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -107,6 +109,28 @@ lib.srtMatmulPlanCacheLoad.restype = ctypes.c_int
 lib.srtMatmulPlanCacheLoad.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32)]
 lib.srtMatmulPlanCacheClear.restype = ctypes.c_int
 lib.srtMatmulPlanCacheClear.argtypes = []
+
+
+lib.srtActivationForward.restype = ctypes.c_int
+lib.srtActivationForward.argtypes = [_P, _D, ctypes.c_int, _P, _D, _P]
+lib.srtMatmulReleaseWorkspaces.restype = ctypes.c_int
+lib.srtMatmulReleaseWorkspaces.argtypes = [ctypes.c_bool]
+lib.srtGruCell.restype = ctypes.c_int
+lib.srtGruCell.argtypes = [_P, _D] * 7 + [_P]
+lib.srtShardRange.restype = ctypes.c_int
+lib.srtShardRange.argtypes = [ctypes.c_size_t, ctypes.c_int32, ctypes.c_int32, ctypes.c_size_t,
+                              ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+lib.srtMatmulSharded.restype = ctypes.c_int
+lib.srtMatmulSharded.argtypes = [ctypes.c_int, ctypes.c_int32, ctypes.c_int32, _P, _D, ctypes.c_bool, _P, _D, ctypes.c_bool,
+                                 _P, _D, ctypes.c_int, _P, _D, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p), _P, _P]
+lib.srtMatmulShardedDevices.restype = ctypes.c_int
+lib.srtMatmulShardedDevices.argtypes = [ctypes.c_int, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p),
+                                        ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool,
+                                        ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool,
+                                        ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_int,
+                                        ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool]
+lib.srtMatmulSetWaitLimit.restype = ctypes.c_int
+lib.srtMatmulSetWaitLimit.argtypes = [ctypes.c_uint64]
 
 
 def last_error() -> str:

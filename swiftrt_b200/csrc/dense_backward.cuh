@@ -9,7 +9,12 @@
 //           rounding to the element type.
 // The derivative uses the forward OUTPUT y (relu: y > 0, sigmoid: y (1 - y), tanh: 1 - y^2),
 // as cuDNN's activation backward does in the reference
-// (Sources/SwiftRTCore/platform/cuda/layers/CudaActivation.swift:101-127).
+// (Sources/SwiftRTCore/platform/cuda/layers/CudaActivation.swift:101-127).  GELU is not a function
+// of its own output, so for gelu / geluTanh the second tensor is the PRE-activation value z and the
+// derivative is evaluated there:
+//     gelu'(z)     = Phi(z) + z phi(z)                      (Phi, phi: standard normal cdf / pdf)
+//     geluTanh'(z) = (1 + t) / 2 + z (1 - t^2) u'(z) / 2,   t = tanh(u), u = sqrt(2/pi) (z + 0.044715 z^3)
+// activation_forward_kernel is the matching forward pass y = act(z) for layers that keep z.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -32,6 +37,17 @@ __device__ __forceinline__ float activation_grad(uint32_t act, float g, float o)
     case kActRelu: return o > 0.0f ? g : 0.0f;
     case kActSigmoid: return __fmul_rn(g, __fmul_rn(o, __fsub_rn(1.0f, o)));
     case kActTanh: return __fmul_rn(g, __fsub_rn(1.0f, __fmul_rn(o, o)));
+    case kActGelu: {
+        const float cdf = 0.5f * (1.0f + erff(o * 0.70710678118654752440f));
+        const float pdf = 0.39894228040143267794f * expf(-0.5f * o * o);
+        return g * (cdf + o * pdf);
+    }
+    case kActGeluTanh: {
+        const float u = 0.7978845608028654f * (o + 0.044715f * o * o * o);
+        const float t = tanhf(u);
+        const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * o * o);
+        return g * (0.5f * (1.0f + t) + 0.5f * o * (1.0f - t * t) * du);
+    }
     default: return g;
     }
 }
@@ -123,6 +139,34 @@ dense_backward_finish_kernel(const float* partial, uint32_t chunks, uint32_t N, 
     float s = partial[n];
     for (uint32_t c = 1; c < chunks; ++c) s = __fadd_rn(s, partial[static_cast<unsigned long long>(c) * N + n]);
     dbias[static_cast<long long>(n) * dbias_stride] = from_float<T>(s);
+}
+
+// y = act(z), elementwise over a rank-2/3 view (any strides; VEC as above).  Reuses
+// DenseBackwardParams: dy = z (input), dz = y (output).
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+activation_forward_kernel(const DenseBackwardParams p)
+{
+    const unsigned long long cols = (p.N + VEC - 1) / VEC;
+    const unsigned long long total = static_cast<unsigned long long>(p.batch) * p.M * cols;
+    const T* z = static_cast<const T*>(p.dy);
+    T* y = static_cast<T*>(p.dz);
+    for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total; i += gridDim.x * 256ull) {
+        const uint32_t c = static_cast<uint32_t>(i % cols) * VEC;
+        const unsigned long long r = i / cols;
+        const uint32_t b = static_cast<uint32_t>(r / p.M), m = static_cast<uint32_t>(r % p.M);
+        const long long o_in = b * p.dy_b + m * p.dy_m + static_cast<long long>(c) * p.dy_n;
+        const long long o_out = b * p.dz_b + m * p.dz_m + static_cast<long long>(c) * p.dz_n;
+        if constexpr (VEC > 1) {
+            __align__(16) T v[VEC];
+            *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(z + o_in);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[j] = from_float<T>(apply_activation(p.act, to_float<T>(v[j])));
+            *reinterpret_cast<uint4*>(y + o_out) = *reinterpret_cast<const uint4*>(v);
+        } else {
+            y[o_out] = from_float<T>(apply_activation(p.act, to_float<T>(z[o_in])));
+        }
+    }
 }
 
 }  // namespace srt

@@ -39,14 +39,6 @@ enum : uint32_t {
 // Status word of the tensor-core kernels, one per device that loads the module.
 __device__ uint32_t g_gemm_status;
 
-// Development aid: with -DSRT_TRACE the epilogue of CTA 0 records clock64() at a few points.
-#ifdef SRT_TRACE
-__device__ long long g_trace[8192];
-#define SRT_TRACE_POINT(cond, idx) do { if ((cond) && blockIdx.x == 0 && (idx) < 8192) g_trace[(idx)] = clock64(); } while (0)
-#else
-#define SRT_TRACE_POINT(cond, idx) do { } while (0)
-#endif
-
 struct OperandParams {
     uint32_t mn_major;      // 0: K contiguous, 1: M/N contiguous
     uint32_t chunks;        // TMA boxes per stage (1 for K-major)
@@ -254,7 +246,6 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
     for (uint32_t bx = part; bx < kBoxes; bx += PARTS) {
         const uint32_t box_col = n0 + bx * kColsPerBox;
         if (box_col >= p.N) break;                              // uniform over the warp
-        SRT_TRACE_POINT(quarter == 2 && part == 0 && lane == 0, (bx + 0) * 8 + 0);
         uint32_t packed[32];                                    // 128 bytes of this thread's output row
 #pragma unroll
         for (uint32_t h = 0; h < kLoadsPerBox; ++h) {

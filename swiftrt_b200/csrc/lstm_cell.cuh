@@ -112,4 +112,55 @@ lstm_gates_kernel(const LstmGateParams p)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// GRU cell (Sources/SwiftRTLayers/Recurrent.swift:328-337), around two fused products:
+//     [reset | update] = sigmoid([x | h] . [[resetW1 | updateW1], [resetW2 | updateW2]] + [resetB | updateB])
+//     gateInput2       = [x | reset * h]                                   gru_reset_kernel (in place)
+//     output           = tanh(gateInput2 . [[outputW1], [outputW2]] + outputB)
+//     newState         = (1 - update) * h + (1 - update) * output          gru_state_kernel
+// (the last line is the reference's formula as written: both terms carry 1 - update).
+struct GruParams {
+    void* gate_in;                   // dense [rows x (nx + nh)]: x | h, the h half is overwritten with reset * h
+    const void* gates;               // dense [rows x 2 nh]: reset | update (after the sigmoid)
+    const void* output;              // dense [rows x nh]: after the tanh
+    const void* hidden; void* new_hidden;
+    long long h_m, h_n, nh_m, nh_n;  // element strides
+    uint32_t rows, nx, nh;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gru_reset_kernel(const GruParams p)
+{
+    T* cat = static_cast<T*>(p.gate_in);
+    const T* gates = static_cast<const T*>(p.gates);
+    const unsigned long long total = static_cast<unsigned long long>(p.rows) * p.nh;
+    for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total; i += gridDim.x * 256ull) {
+        const uint32_t r = static_cast<uint32_t>(i / p.nh), j = static_cast<uint32_t>(i % p.nh);
+        T* h = cat + static_cast<unsigned long long>(r) * (p.nx + p.nh) + p.nx + j;
+        const float reset = to_float<T>(gates[static_cast<unsigned long long>(r) * 2 * p.nh + j]);
+        *h = from_float<T>(__fmul_rn(reset, to_float<T>(*h)));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gru_state_kernel(const GruParams p)
+{
+    const T* gates = static_cast<const T*>(p.gates);
+    const T* output = static_cast<const T*>(p.output);
+    const T* hidden = static_cast<const T*>(p.hidden);
+    T* new_hidden = static_cast<T*>(p.new_hidden);
+    const unsigned long long total = static_cast<unsigned long long>(p.rows) * p.nh;
+    for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total; i += gridDim.x * 256ull) {
+        const uint32_t r = static_cast<uint32_t>(i / p.nh), j = static_cast<uint32_t>(i % p.nh);
+        const float update = to_float<T>(gates[static_cast<unsigned long long>(r) * 2 * p.nh + p.nh + j]);
+        const float h = to_float<T>(hidden[static_cast<long long>(r) * p.h_m + static_cast<long long>(j) * p.h_n]);
+        const float o = to_float<T>(output[i]);
+        const float keep = __fsub_rn(1.0f, update);
+        new_hidden[static_cast<long long>(r) * p.nh_m + static_cast<long long>(j) * p.nh_n] =
+            from_float<T>(__fadd_rn(__fmul_rn(keep, h), __fmul_rn(keep, o)));
+    }
+}
+
 }  // namespace srt

@@ -100,8 +100,11 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     return done != 0;
 }
 
-// Wall-clock limit of one pipeline wait.  A healthy wait lasts microseconds.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Wall-clock limit of one pipeline wait, in nanoseconds.  A healthy wait lasts microseconds.  A
+// device variable rather than a constant so that a test can shorten it (srtMatmulSetWaitLimit) and
+// see a wait give up on a valid product; it is read only after a first try_wait has failed.
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
+__device__ unsigned long long g_wait_limit_ns = kDefaultWaitLimitNs;
 
 // Waits for the phase with the given parity.  Returns false when the limit ran out or
 // when another role of this CTA already gave up (*abort_flag != 0).  Each failed try_wait has
@@ -114,7 +117,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag != 0) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        if (global_timer_ns() - t0 > g_wait_limit_ns) return false;
     }
 }
 
@@ -125,7 +128,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     for (;;) {
         if (mbar_try_wait_cluster(bar, parity)) return true;
         if (*abort_flag != 0) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        if (global_timer_ns() - t0 > g_wait_limit_ns) return false;
     }
 }
 

@@ -41,6 +41,46 @@ cudaError_t fail(cudaError_t code, const char* fmt, ...)
     return code;
 }
 
+// ------------------------------------------------------------------ the device of a call
+// Every entry point that takes a stream works on THAT stream's device, whatever device is current
+// on the calling thread: the reference's queues never select a device before they enqueue
+// (Sources/SwiftRTCore/platform/cuda/functions/CudaMath.swift:117-125 launches on `stream` with no
+// device call; nothing calls CudaQueue.selectDevice, cuda/device/CudaQueue.swift:77).  The scope
+// resolves the stream's device, makes it current for the duration of the call when it differs and
+// restores the caller's device afterwards; per-device state (workspaces, kernel attributes, the
+// status word, the static scratch) is keyed by `device`.  The legacy and per-thread default
+// streams belong to whatever device is current.
+struct DeviceScope {
+    int device = -1;
+    int previous = -1;
+    cudaError_t status = cudaSuccess;
+    explicit DeviceScope(cudaStream_t stream)
+    {
+        int cur = 0;
+        status = cudaGetDevice(&cur);
+        if (status != cudaSuccess) return;
+        int dev = cur;
+        if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+            status = cudaStreamGetDevice(stream, &dev);
+            if (status != cudaSuccess) {
+                fail(status, "cannot resolve the device of the stream: %s", cudaGetErrorString(status));
+                return;
+            }
+        }
+        device = dev;
+        if (dev != cur) {
+            status = cudaSetDevice(dev);
+            if (status == cudaSuccess) previous = cur;
+        }
+    }
+    ~DeviceScope()
+    {
+        if (previous >= 0) cudaSetDevice(previous);
+    }
+    DeviceScope(const DeviceScope&) = delete;
+    DeviceScope& operator=(const DeviceScope&) = delete;
+};
+
 // ------------------------------------------------------------------ problem description
 struct Problem {
     srtDataType type;
@@ -422,8 +462,7 @@ bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool sk
         }
     }
     const uint32_t tile_m = pair ? 2 * kTileM : kTileM;
-    static const bool tf32_single = getenv("SRT_MATMUL_TF32_SINGLE") != nullptr;   // experiment knob: 1 x TF32
-    const bool split3 = split && !tf32_single;
+    const bool split3 = split;
     const uint32_t stage_bytes = (kATileBytes + (pair ? bn / 2 : bn) * kRowBytes) * (split3 ? 2 : 1);
     uint32_t stages = (uint32_t)choice.stages;
     uint32_t max_stages = (227u * 1024u - 2048u - kEpilogueStagingBytes) / stage_bytes;
@@ -697,6 +736,7 @@ struct Prepared {
     uint32_t splits = 1;
     size_t ws_bytes = 0;
     void* ws_bound = nullptr;        // workspace the output tensor map and gp.out currently point at
+    bool static_scratch = false;     // split-K partial sums go to the library's static array (srtMatmulNoAlloc)
     ReduceParams rp;
     uint32_t reduce_vec = 1, reduce_blocks = 0;
 };
@@ -744,11 +784,6 @@ cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
     gp.k_blocks = (uint32_t)((Q.K + gp.kb_elems - 1) / gp.kb_elems);
     gp.kb_per_split = plan.splits > 1 ? plan.kb_per_split : gp.k_blocks;
     gp.group_m = pair ? 8 : 16;                           // 2048 rows of A per group either way
-    {
-        // experiment knob (not part of the ABI): rows of tiles per rasterisation group
-        static const int env_group = [] { const char* e = getenv("SRT_MATMUL_GROUP_M"); return e ? atoi(e) : 0; }();
-        if (env_group > 0) gp.group_m = (uint32_t)env_group;
-    }
     gp.stages = (uint32_t)plan.pub.stages;
     gp.stage_tx_bytes = kATileBytes + b_rows * kRowBytes;
     // instruction descriptor: fp32 accumulator, input format, majorness, N >> 3, M >> 4
@@ -776,6 +811,7 @@ cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
     pr.splits = plan.splits;
     pr.ws_bytes = 0;
     pr.ws_bound = nullptr;
+    pr.static_scratch = false;
     if (plan.splits > 1) {
         // first pass: raw fp32 partial sums into the workspace (bound at launch); bias,
         // activation, rounding and the output view belong to the reduce pass
@@ -823,37 +859,86 @@ cudaError_t bind_workspace(Prepared& pr, void* ws)
     return cudaSuccess;
 }
 
-// Workspaces of split-K launches: one buffer per (device, stream), grown on demand, kept until
-// the process exits.  Kernels of one stream run in order, so a stream never races with itself.
-// `slot` separates buffers that are alive at the same time on one stream (slot 0: split-K partial
-// sums and column-sum partials; slot 1: the LSTM cell's gate input and fused product).
-struct Workspace { int device; cudaStream_t stream; int slot; void* ptr; size_t bytes; };
+// Workspaces of split-K launches: one buffer per (device, stream), grown on demand.  Kernels of
+// one stream run in order, so a stream never races with itself.  `slot` separates buffers that are
+// alive at the same time on one stream (slot 0: split-K partial sums and column-sum partials;
+// slot 1: the recurrent cells' gate input and fused product).
+//
+// Growth never waits for the GPU: the new buffer is allocated beside the old one and the old one is
+// freed in stream order (cudaFreeAsync on the same stream, behind the kernels that still use it).
+// A buffer that was handed out while its stream was being captured is baked into a CUDA graph that
+// may be replayed at any later time: it is marked `captured` and, when a later call on the same
+// stream handle needs more, it is kept alive (moved to the retained list) instead of freed.
+// srtMatmulReleaseWorkspaces gives the memory back.
+struct Workspace { int device; cudaStream_t stream; int slot; void* ptr; size_t bytes; bool captured; };
+struct Retained { int device; void* ptr; bool captured; };
 std::mutex g_ws_mutex;
 std::vector<Workspace> g_workspaces;
+std::vector<Retained> g_retained;
 
 cudaError_t workspace_for(int device, cudaStream_t stream, size_t bytes, void** out, int slot = 0)
 {
-    std::lock_guard<std::mutex> lock(g_ws_mutex);
-    for (Workspace& w : g_workspaces) {
-        if (w.device != device || w.stream != stream || w.slot != slot) continue;
-        if (w.bytes < bytes) {
-            cudaError_t e = cudaStreamSynchronize(stream);     // the old buffer may still be in use
-            if (e != cudaSuccess) return e;
-            cudaFree(w.ptr);
-            w.ptr = nullptr; w.bytes = 0;
-            e = cudaMalloc(&w.ptr, bytes);
-            if (e != cudaSuccess) return e;
-            w.bytes = bytes;
-        }
-        *out = w.ptr;
-        return cudaSuccess;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
+        cap = cudaStreamCaptureStatusNone;
+        (void)cudaGetLastError();
     }
-    Workspace w{device, stream, slot, nullptr, 0};
-    cudaError_t e = cudaMalloc(&w.ptr, bytes);
-    if (e != cudaSuccess) return e;
-    w.bytes = bytes;
-    g_workspaces.push_back(w);
-    *out = w.ptr;
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    Workspace* w = nullptr;
+    for (Workspace& c : g_workspaces)
+        if (c.device == device && c.stream == stream && c.slot == slot) { w = &c; break; }
+    if (!w) {
+        g_workspaces.push_back(Workspace{device, stream, slot, nullptr, 0, false});
+        w = &g_workspaces.back();
+    }
+    if (w->bytes < bytes) {
+        if (capturing)
+            return fail(cudaErrorStreamCaptureUnsupported,
+                        "the workspace of this stream would have to grow (%zu -> %zu bytes) during stream capture; run the same "
+                        "call once before capturing", w->bytes, bytes);
+        void* fresh = nullptr;
+        cudaError_t e = cudaMalloc(&fresh, bytes);
+        if (e != cudaSuccess) return fail(e, "cudaMalloc of a %zu-byte workspace failed: %s", bytes, cudaGetErrorString(e));
+        if (w->ptr) {
+            if (w->captured) {
+                g_retained.push_back(Retained{device, w->ptr, true});
+            } else if (cudaFreeAsync(w->ptr, stream) != cudaSuccess) {
+                (void)cudaGetLastError();
+                g_retained.push_back(Retained{device, w->ptr, false});       // freed by srtMatmulReleaseWorkspaces
+            }
+        }
+        w->ptr = fresh;
+        w->bytes = bytes;
+        w->captured = false;
+    }
+    if (capturing) w->captured = true;
+    *out = w->ptr;
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ static scratch (srtMatmulNoAlloc)
+// Part of the library image: every device that loads the library carries these 16 MiB from then
+// until the process ends, whether or not the entry point is ever called.  In host code the name is
+// only a handle for cudaGetSymbolAddress; the device address it yields is what the kernels receive.
+constexpr size_t kNoAllocScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[kNoAllocScratchBytes];
+
+std::mutex g_no_alloc_mutex;
+void* g_no_alloc_ptr[64] = {};
+
+// Device address of the scratch array on device `dev` (which must be current), looked up once per device.
+cudaError_t no_alloc_scratch(int dev, void** out)
+{
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (dev < 0 || dev >= 64) return fail(cudaErrorInvalidDevice, "device ordinal %d out of range", dev);
+    if (!g_no_alloc_ptr[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+        if (e != cudaSuccess) return fail(e, "cudaGetSymbolAddress of the static scratch failed: %s", cudaGetErrorString(e));
+        g_no_alloc_ptr[dev] = ptr;
+    }
+    *out = g_no_alloc_ptr[dev];
     return cudaSuccess;
 }
 
@@ -883,6 +968,7 @@ cudaError_t prepare_simt(const Plan& plan, Prepared& pr)
     pr.splits = 1;
     pr.ws_bytes = 0;
     pr.ws_bound = nullptr;
+    pr.static_scratch = false;
     return cudaSuccess;
 }
 
@@ -950,7 +1036,7 @@ cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
         e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
         void* ws = nullptr;
-        e = workspace_for(dev, stream, pr.ws_bytes, &ws);
+        e = pr.static_scratch ? no_alloc_scratch(dev, &ws) : workspace_for(dev, stream, pr.ws_bytes, &ws);
         if (e != cudaSuccess) return e;
         if (ws != pr.ws_bound) {
             e = bind_workspace(pr, ws);
@@ -1021,7 +1107,7 @@ struct CallKey {
     int32_t force, tile_n, stages, max_ctas, split_k;
     int32_t device;
     uint32_t plan_epoch;
-    uint32_t pad;
+    uint32_t no_alloc;              // 1: srtMatmulNoAlloc (split-K scratch = the static array)
 };
 
 constexpr int kCallCacheSize = 64;
@@ -1215,6 +1301,58 @@ cudaError_t launch_lstm_elementwise(const ConcatParams* cp, const LstmGateParams
     return e;
 }
 
+// ------------------------------------------------------------------ one product
+// Parses, plans (or finds the prepared launch of an identical earlier call) and enqueues.
+// `no_alloc`: split-K partial sums go to the static scratch array; products whose partial sums do
+// not fit there are refused before anything is launched.
+cudaError_t run_matmul(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
+                       const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                       const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                       const srtTensorDescriptor* oDesc, cudaStream_t stream, bool no_alloc)
+{
+    CallKey key;
+    memset(&key, 0, sizeof key);                 // padding bytes are part of the hashed key
+    Problem& P = key.P;
+    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
+    if (e != cudaSuccess) return e;
+    if (is_empty(P)) return cudaSuccess;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    key.force = g_tuning.force_kernel.load(std::memory_order_relaxed);
+    key.tile_n = g_tuning.tile_n.load(std::memory_order_relaxed);
+    key.stages = g_tuning.stages.load(std::memory_order_relaxed);
+    key.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
+    key.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
+    key.device = scope.device;
+    key.plan_epoch = g_plan_epoch.load(std::memory_order_relaxed);
+    key.no_alloc = no_alloc ? 1u : 0u;
+    if (!t_cache) t_cache.reset(new CallCache());
+    const int slot = (int)(hash_key(key) % kCallCacheSize);
+    if (t_cache->valid[slot] && memcmp(&t_cache->key[slot], &key, sizeof key) == 0)
+        return launch_prepared(t_cache->value[slot], stream);
+
+    Plan plan;
+    e = plan_for(P, plan);
+    if (e != cudaSuccess) return e;
+    if (no_alloc && plan.splits > 1 && plan.pub.workspaceBytes > kNoAllocScratchBytes)
+        return fail(cudaErrorInvalidValue,
+                    "srtMatmulNoAlloc: this product needs %zu bytes of scratch (%u partial results of %llu x %llu x %llu "
+                    "fp32 values) but the static scratch holds %zu; use srtMatmul, or srtMatmulSetSplitK(1)",
+                    (size_t)plan.pub.workspaceBytes, plan.splits, (unsigned long long)plan.Q.batch,
+                    (unsigned long long)plan.Q.M, (unsigned long long)plan.Q.N, kNoAllocScratchBytes);
+    Prepared& pr = t_cache->value[slot];
+    t_cache->valid[slot] = false;
+    e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, pr) : prepare_tc(plan, pr);
+    if (e != cudaSuccess) return e;
+    pr.static_scratch = no_alloc && pr.splits > 1;
+    e = launch_prepared(pr, stream);
+    if (e == cudaSuccess) {
+        t_cache->key[slot] = key;
+        t_cache->valid[slot] = true;
+    }
+    return e;
+}
+
 }  // namespace
 
 // ===================================================================== exported entry points
@@ -1225,40 +1363,7 @@ cudaError_t srtMatmulBiasActivation(const void* a, const srtTensorDescriptor* aD
                                     const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
                                     const srtTensorDescriptor* oDesc, cudaStream_t stream)
 {
-    CallKey key;
-    memset(&key, 0, sizeof key);                 // padding bytes are part of the hashed key
-    Problem& P = key.P;
-    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
-    if (e != cudaSuccess) return e;
-    if (is_empty(P)) return cudaSuccess;
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    key.force = g_tuning.force_kernel.load(std::memory_order_relaxed);
-    key.tile_n = g_tuning.tile_n.load(std::memory_order_relaxed);
-    key.stages = g_tuning.stages.load(std::memory_order_relaxed);
-    key.max_ctas = g_tuning.max_ctas.load(std::memory_order_relaxed);
-    key.split_k = g_tuning.split_k.load(std::memory_order_relaxed);
-    key.device = dev;
-    key.plan_epoch = g_plan_epoch.load(std::memory_order_relaxed);
-    if (!t_cache) t_cache.reset(new CallCache());
-    const int slot = (int)(hash_key(key) % kCallCacheSize);
-    if (t_cache->valid[slot] && memcmp(&t_cache->key[slot], &key, sizeof key) == 0)
-        return launch_prepared(t_cache->value[slot], stream);
-
-    Plan plan;
-    e = plan_for(P, plan);
-    if (e != cudaSuccess) return e;
-    Prepared& pr = t_cache->value[slot];
-    t_cache->valid[slot] = false;
-    e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, pr) : prepare_tc(plan, pr);
-    if (e != cudaSuccess) return e;
-    e = launch_prepared(pr, stream);
-    if (e == cudaSuccess) {
-        t_cache->key[slot] = key;
-        t_cache->valid[slot] = true;
-    }
-    return e;
+    return run_matmul(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, activation, out, oDesc, stream, false);
 }
 
 cudaError_t srtMatmul(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
@@ -1315,6 +1420,8 @@ cudaError_t srtMatmulTune(const void* a, const srtTensorDescriptor* aDesc, bool 
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
     if (e != cudaSuccess) return e;
     if (is_empty(P)) return fail(cudaErrorInvalidValue, "srtMatmulTune: empty result");
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
     // candidates: the cost model's own choice first, then every kernel / tile width the type allows
     std::vector<Choice> cands;
     cands.push_back(Choice{0, 0, 0, 0, 0});
@@ -1405,6 +1512,8 @@ cudaError_t srtMatmulPlanCacheClear(void)
 cudaError_t srtMatmulCheckStatus(cudaStream_t stream, uint32_t* status)
 {
     if (!status) return fail(cudaErrorInvalidValue, "null status");
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
     cudaError_t e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return e;
     uint32_t v = 0;
@@ -1434,13 +1543,14 @@ cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor*
     if (elem == 0) return fail(cudaErrorNotSupported, "element type %d is not computed by this library", (int)type);
     switch ((int)activation) {
     case srtActivationIdentity: case srtActivationRelu: case srtActivationSigmoid: case srtActivationTanh: break;
-    case srtActivationGelu: case srtActivationGeluTanh: case srtActivationClippedRelu: case srtActivationElu:
-        return fail(cudaErrorNotSupported, "this activation's derivative needs the pre-activation values, which the forward pass does not keep");
+    case srtActivationGelu: case srtActivationGeluTanh: break;       // `y` carries the pre-activation values
+    case srtActivationClippedRelu: case srtActivationElu:
+        return fail(cudaErrorNotSupported, "clippedRelu and elu need coefficients that this entry point does not carry");
     default: return fail(cudaErrorInvalidValue, "unknown activation %d", (int)activation);
     }
     const bool need_y = activation != srtActivationIdentity;
     if (need_y) {
-        if (!y) return fail(cudaErrorInvalidValue, "the forward output y is needed for this activation's derivative");
+        if (!y) return fail(cudaErrorInvalidValue, "the forward output y (the pre-activation values for gelu) is needed for this activation's derivative");
         e = view3(yDesc, "y", vy);
         if (e != cudaSuccess) return e;
         if (yDesc->type != type || vy.batch != vg.batch || vy.M != vg.M || vy.N != vg.N)
@@ -1462,9 +1572,9 @@ cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor*
     if (vg.M == 0 || vg.N == 0 || vg.batch == 0 || vg.M > 0x7fffffffull || vg.N > 0x7fffffffull || vg.batch > 0x7fffffffull)
         return fail(cudaErrorInvalidValue, "dimension outside the supported range");
     g_error[0] = 0;
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    const int dev = scope.device;
     DeviceInfo info;
     e = device_info(dev, info);
     if (e != cudaSuccess) return e;
@@ -1505,6 +1615,99 @@ cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor*
     case real16F: return launch_dense_backward<__half>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
     default: return launch_dense_backward<__nv_bfloat16>(bp, vec, (uint32_t)chunks, dbias, dbias_stride, stream);
     }
+}
+
+// ------------------------------------------------------------------ srtActivationForward
+cudaError_t srtActivationForward(const void* z, const srtTensorDescriptor* zDesc, srtActivationType activation, void* y,
+                                 const srtTensorDescriptor* yDesc, cudaStream_t stream)
+{
+    if (!z || !y || !zDesc || !yDesc) return fail(cudaErrorInvalidValue, "srtActivationForward: null tensor");
+    View3 vz, vy;
+    cudaError_t e = view3(zDesc, "z", vz);
+    if (e != cudaSuccess) return e;
+    if ((e = view3(yDesc, "y", vy)) != cudaSuccess) return e;
+    const srtDataType type = zDesc->type;
+    const uint32_t elem = elem_size(type);
+    if (elem == 0) return fail(cudaErrorNotSupported, "element type %d is not computed by this library", (int)type);
+    if (yDesc->type != type || vy.batch != vz.batch || vy.M != vz.M || vy.N != vz.N)
+        return fail(cudaErrorInvalidValue, "y must have the type and shape of z");
+    switch ((int)activation) {
+    case srtActivationIdentity: case srtActivationRelu: case srtActivationSigmoid: case srtActivationTanh:
+    case srtActivationGelu: case srtActivationGeluTanh: break;
+    case srtActivationClippedRelu: case srtActivationElu:
+        return fail(cudaErrorNotSupported, "clippedRelu and elu need coefficients that this entry point does not carry");
+    default: return fail(cudaErrorInvalidValue, "unknown activation %d", (int)activation);
+    }
+    if (vz.M == 0 || vz.N == 0 || vz.batch == 0) return cudaSuccess;
+    if (vz.M > 0x7fffffffull || vz.N > 0x7fffffffull || vz.batch > 0x7fffffffull)
+        return fail(cudaErrorInvalidValue, "dimension outside the supported range");
+    g_error[0] = 0;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    DenseBackwardParams bp;
+    memset(&bp, 0, sizeof bp);
+    bp.dy = z; bp.dz = y;
+    bp.dy_b = vz.s_b; bp.dy_m = vz.s_m; bp.dy_n = vz.s_n;
+    bp.dz_b = vy.s_b; bp.dz_m = vy.s_m; bp.dz_n = vy.s_n;
+    bp.M = (uint32_t)vz.M; bp.N = (uint32_t)vz.N; bp.batch = (uint32_t)vz.batch;
+    bp.act = (uint32_t)activation;
+    const uint32_t vecw = 16 / elem;
+    auto vec_ok = [&](const void* ptr, const View3& v) {
+        return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (v.s_n == 1 || v.N == 1) && (v.s_m * (long long)elem) % 16 == 0 &&
+               (v.s_b * (long long)elem) % 16 == 0;
+    };
+    const bool vec = vz.N % vecw == 0 && vec_ok(z, vz) && vec_ok(y, vy);
+    const unsigned long long work = vz.batch * vz.M * ((vz.N + (vec ? vecw : 1) - 1) / (vec ? vecw : 1));
+    unsigned long long blocks = (work + 255) / 256;
+    if (blocks > 148ull * 16) blocks = 148ull * 16;
+    const unsigned grid = (unsigned)blocks;
+    switch (type) {
+    case real32F:
+        if (vec) activation_forward_kernel<float, 4><<<grid, 256, 0, stream>>>(bp);
+        else     activation_forward_kernel<float, 1><<<grid, 256, 0, stream>>>(bp);
+        break;
+    case real16F:
+        if (vec) activation_forward_kernel<__half, 8><<<grid, 256, 0, stream>>>(bp);
+        else     activation_forward_kernel<__half, 1><<<grid, 256, 0, stream>>>(bp);
+        break;
+    default:
+        if (vec) activation_forward_kernel<__nv_bfloat16, 8><<<grid, 256, 0, stream>>>(bp);
+        else     activation_forward_kernel<__nv_bfloat16, 1><<<grid, 256, 0, stream>>>(bp);
+        break;
+    }
+    e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
+// ------------------------------------------------------------------ srtMatmulReleaseWorkspaces
+cudaError_t srtMatmulReleaseWorkspaces(bool includeCaptured)
+{
+    int cur = 0;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    cudaError_t first = cudaSuccess;
+    auto release = [&](int device, void* ptr) {
+        cudaError_t r = cudaSetDevice(device);
+        if (r == cudaSuccess) r = cudaDeviceSynchronize();      // nothing enqueued may still use the buffer
+        if (r == cudaSuccess) r = cudaFree(ptr);
+        if (r != cudaSuccess && first == cudaSuccess) first = r;
+    };
+    std::vector<Workspace> keep_ws;
+    for (const Workspace& w : g_workspaces) {
+        if (w.ptr && (includeCaptured || !w.captured)) release(w.device, w.ptr);
+        else if (w.ptr) keep_ws.push_back(w);
+    }
+    g_workspaces.swap(keep_ws);
+    std::vector<Retained> keep_rt;
+    for (const Retained& r : g_retained) {
+        if (includeCaptured || !r.captured) release(r.device, r.ptr);
+        else keep_rt.push_back(r);
+    }
+    g_retained.swap(keep_rt);
+    cudaSetDevice(cur);
+    return first == cudaSuccess ? cudaSuccess : fail(first, "srtMatmulReleaseWorkspaces: %s", cudaGetErrorString(first));
 }
 
 // ------------------------------------------------------------------ srtLstmCell
@@ -1548,10 +1751,12 @@ cudaError_t srtLstmCell(const void* input, const srtTensorDescriptor* inputDesc,
         return fail(cudaErrorNotSupported, "srtLstmCell: extents beyond 32 bits");
 
     const size_t elem = type == real32F ? 4 : 2;
-    const size_t gate_bytes = ((size_t)rows * (nx + nh) * elem + 255) & ~(size_t)255;
+    // the gate input is staged in the workspace only when the library concatenates it
+    const size_t gate_bytes = preconcatenated ? 0 : (((size_t)rows * (nx + nh) * elem + 255) & ~(size_t)255);
     const size_t fused_bytes = (size_t)rows * 4 * nh * elem;
-    int dev = 0;
-    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    const int dev = scope.device;
     void* ws = nullptr;
     if ((e = workspace_for(dev, stream, gate_bytes + fused_bytes, &ws, 1)) != cudaSuccess) return e;
     const void* gate_in = preconcatenated ? input : ws;
@@ -1632,8 +1837,9 @@ cudaError_t srtRnnCell(const void* input, const srtTensorDescriptor* inputDesc, 
     if (rows == 0 || nh == 0) return cudaSuccess;
     if (rows > 0xffffffffull || nx + nh > 0xffffffffull) return fail(cudaErrorNotSupported, "srtRnnCell: extents beyond 32 bits");
     const size_t elem = type == real32F ? 4 : 2;
-    int dev = 0;
-    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    const int dev = scope.device;
     void* gate_in = nullptr;
     if ((e = workspace_for(dev, stream, (size_t)rows * (nx + nh) * elem, &gate_in, 1)) != cudaSuccess) return e;
     ConcatParams cp;
@@ -1654,82 +1860,279 @@ cudaError_t srtRnnCell(const void* input, const srtTensorDescriptor* inputDesc, 
                                    newHidden, newHiddenDesc, stream);
 }
 
-// ------------------------------------------------------------------ srtMatmulNoAlloc
-// Scratch of the entry point below.  It is part of the library image: every device that loads
-// the library carries these 16 MiB from then until the process ends, whether or not the entry
-// point is ever called.  In host code the name is only a handle for cudaGetSymbolAddress; the
-// device address it yields is what the kernels receive.
-constexpr size_t kNoAllocScratchBytes = 16u << 20;
-static __device__ __align__(256) unsigned char g_no_alloc_scratch[kNoAllocScratchBytes];
-
-std::mutex g_no_alloc_mutex;
-void* g_no_alloc_ptr[64] = {};
-
-// Device address of the scratch array on the current device, looked up once per device.
-cudaError_t no_alloc_scratch(int dev, void** out)
+// ------------------------------------------------------------------ srtGruCell
+cudaError_t srtGruCell(const void* input, const srtTensorDescriptor* inputDesc, const void* hidden,
+                       const srtTensorDescriptor* hiddenDesc, const void* gateWeight, const srtTensorDescriptor* gateWeightDesc,
+                       const void* gateBias, const srtTensorDescriptor* gateBiasDesc, const void* outputWeight,
+                       const srtTensorDescriptor* outputWeightDesc, const void* outputBias,
+                       const srtTensorDescriptor* outputBiasDesc, void* newHidden, const srtTensorDescriptor* newHiddenDesc,
+                       cudaStream_t stream)
 {
-    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
-    if (dev < 0 || dev >= 64) return fail(cudaErrorInvalidDevice, "device ordinal %d out of range", dev);
-    if (!g_no_alloc_ptr[dev]) {
-        void* ptr = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
-        if (e != cudaSuccess) return fail(e, "cudaGetSymbolAddress of the static scratch failed: %s", cudaGetErrorString(e));
-        g_no_alloc_ptr[dev] = ptr;
+    if (!input || !hidden || !gateWeight || !outputWeight || !newHidden || !inputDesc)
+        return fail(cudaErrorInvalidValue, "srtGruCell: null tensor");
+    const srtDataType type = inputDesc->type;
+    if (type != real32F && type != real16F && type != real16BF)
+        return fail(cudaErrorNotSupported, "srtGruCell: element type %d is outside this library", (int)type);
+    uint64_t rows, nx, r2, nh, gk, gn, ok, on, r3, c3;
+    long long x_m, x_n, h_m, h_n, g_m, g_n, o_m, o_n, nh_m, nh_n;
+    cudaError_t e;
+    if ((e = view2(inputDesc, "input", type, rows, nx, x_m, x_n)) != cudaSuccess) return e;
+    if ((e = view2(hiddenDesc, "hidden", type, r2, nh, h_m, h_n)) != cudaSuccess) return e;
+    if ((e = view2(gateWeightDesc, "gateWeight", type, gk, gn, g_m, g_n)) != cudaSuccess) return e;
+    if ((e = view2(outputWeightDesc, "outputWeight", type, ok, on, o_m, o_n)) != cudaSuccess) return e;
+    if ((e = view2(newHiddenDesc, "newHidden", type, r3, c3, nh_m, nh_n)) != cudaSuccess) return e;
+    if (r2 != rows || r3 != rows || c3 != nh || gk != nx + nh || gn != 2 * nh || ok != nx + nh || on != nh)
+        return fail(cudaErrorInvalidValue,
+                    "srtGruCell: gateWeight must be [(inputSize + hiddenSize) x 2 hiddenSize], outputWeight [(inputSize + hiddenSize) x "
+                    "hiddenSize], states [batch x hiddenSize]");
+    if (gateBias && (!gateBiasDesc || gateBiasDesc->rank != 1 || gateBiasDesc->shape[0] != 2 * nh || gateBiasDesc->type != type))
+        return fail(cudaErrorInvalidValue, "srtGruCell: gateBias must be rank 1 with 2 hiddenSize elements");
+    if (outputBias && (!outputBiasDesc || outputBiasDesc->rank != 1 || outputBiasDesc->shape[0] != nh || outputBiasDesc->type != type))
+        return fail(cudaErrorInvalidValue, "srtGruCell: outputBias must be rank 1 with hiddenSize elements");
+    if (rows == 0 || nh == 0) return cudaSuccess;
+    if (rows > 0xffffffffull || nx + nh > 0xffffffffull || 2 * nh > 0xffffffffull)
+        return fail(cudaErrorNotSupported, "srtGruCell: extents beyond 32 bits");
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+
+    const size_t elem = type == real32F ? 4 : 2;
+    auto pad = [](size_t n) { return (n + 255) & ~(size_t)255; };
+    const size_t cat_bytes = pad((size_t)rows * (nx + nh) * elem), gates_bytes = pad((size_t)rows * 2 * nh * elem);
+    const size_t out_bytes = (size_t)rows * nh * elem;
+    void* ws = nullptr;
+    if ((e = workspace_for(scope.device, stream, cat_bytes + gates_bytes + out_bytes, &ws, 1)) != cudaSuccess) return e;
+    void* cat = ws;
+    void* gates = static_cast<char*>(ws) + cat_bytes;
+    void* outv = static_cast<char*>(gates) + gates_bytes;
+
+    ConcatParams cp;
+    cp.x = input; cp.h = hidden; cp.out = cat;
+    cp.x_m = x_m; cp.x_n = x_n; cp.h_m = h_m; cp.h_n = h_n;
+    cp.rows = (uint32_t)rows; cp.nx = (uint32_t)nx; cp.nh = (uint32_t)nh;
+    e = type == real32F ? launch_lstm_elementwise<float>(&cp, nullptr, stream)
+        : type == real16F ? launch_lstm_elementwise<__half>(&cp, nullptr, stream)
+                          : launch_lstm_elementwise<__nv_bfloat16>(&cp, nullptr, stream);
+    if (e != cudaSuccess) return e;
+
+    size_t c_shape[2] = {(size_t)rows, (size_t)(nx + nh)}, c_strides[2] = {(size_t)(nx + nh), 1};
+    size_t g_shape[2] = {(size_t)rows, (size_t)(2 * nh)}, g_strides[2] = {(size_t)(2 * nh), 1};
+    size_t o_shape[2] = {(size_t)rows, (size_t)nh}, o_strides[2] = {(size_t)nh, 1};
+    auto dense2 = [&](size_t* shape, size_t* strides) {
+        srtTensorDescriptor d;
+        memset(&d, 0, sizeof d);
+        d.type = type; d.rank = 2; d.order = srtOrderRow; d.count = shape[0] * shape[1]; d.spanCount = d.count;
+        d.shape = shape; d.strides = strides; d.logicalStrides = strides;
+        return d;
+    };
+    const srtTensorDescriptor cd = dense2(c_shape, c_strides), gd = dense2(g_shape, g_strides), od = dense2(o_shape, o_strides);
+    // reset | update = sigmoid([x | h] . gateWeight + gateBias)
+    e = srtMatmulBiasActivation(cat, &cd, false, gateWeight, gateWeightDesc, false, gateBias, gateBiasDesc, srtActivationSigmoid,
+                                gates, &gd, stream);
+    if (e != cudaSuccess) return e;
+    GruParams gp;
+    gp.gate_in = cat; gp.gates = gates; gp.output = outv; gp.hidden = hidden; gp.new_hidden = newHidden;
+    gp.h_m = h_m; gp.h_n = h_n; gp.nh_m = nh_m; gp.nh_n = nh_n;
+    gp.rows = (uint32_t)rows; gp.nx = (uint32_t)nx; gp.nh = (uint32_t)nh;
+    unsigned long long blocks64 = ((unsigned long long)rows * nh + 255) / 256;
+    const unsigned blocks = (unsigned)(blocks64 < 148ull * 16 ? blocks64 : 148ull * 16);
+    switch (type) {
+    case real32F: gru_reset_kernel<float><<<blocks, 256, 0, stream>>>(gp); break;
+    case real16F: gru_reset_kernel<__half><<<blocks, 256, 0, stream>>>(gp); break;
+    default: gru_reset_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gp); break;
     }
-    *out = g_no_alloc_ptr[dev];
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    // output = tanh([x | reset * h] . outputWeight + outputBias)
+    e = srtMatmulBiasActivation(cat, &cd, false, outputWeight, outputWeightDesc, false, outputBias, outputBiasDesc, srtActivationTanh,
+                                outv, &od, stream);
+    if (e != cudaSuccess) return e;
+    switch (type) {
+    case real32F: gru_state_kernel<float><<<blocks, 256, 0, stream>>>(gp); break;
+    case real16F: gru_state_kernel<__half><<<blocks, 256, 0, stream>>>(gp); break;
+    default: gru_state_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gp); break;
+    }
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaSuccess;
 }
 
+// ------------------------------------------------------------------ sharding over GPUs
+cudaError_t srtShardRange(size_t total, int32_t world, int32_t rank, size_t align, size_t* start, size_t* stop)
+{
+    if (!start || !stop) return fail(cudaErrorInvalidValue, "srtShardRange: null result");
+    if (world < 1 || rank < 0 || rank >= world) return fail(cudaErrorInvalidValue, "srtShardRange: rank %d outside a world of %d", rank, world);
+    if (align == 0) align = 1;
+    const size_t units = (total + align - 1) / align;
+    const size_t base = units / (size_t)world, extra = units % (size_t)world;
+    const size_t r = (size_t)rank;
+    const size_t start_u = r * base + (r < extra ? r : extra);
+    const size_t stop_u = start_u + base + (r < extra ? 1 : 0);
+    *start = start_u * align < total ? start_u * align : total;
+    *stop = stop_u * align < total ? stop_u * align : total;
+    return cudaSuccess;
+}
+
+namespace {
+
+// A descriptor with its own copies of the shape / stride arrays, narrowed along one dimension.
+struct SlicedTensor {
+    srtTensorDescriptor desc;
+    size_t shape[3], strides[3];
+    const char* ptr = nullptr;
+    void init(const void* base, const srtTensorDescriptor* d)
+    {
+        desc = *d;
+        for (uint32_t i = 0; i < d->rank && i < 3; ++i) { shape[i] = d->shape[i]; strides[i] = d->strides[i]; }
+        desc.shape = shape; desc.strides = strides; desc.logicalStrides = strides;
+        ptr = static_cast<const char*>(base);
+    }
+    void narrow(uint32_t dim, size_t lo, size_t hi, size_t elem)
+    {
+        ptr += lo * strides[dim] * elem;
+        shape[dim] = hi - lo;
+        size_t count = 1, span = 1;
+        for (uint32_t i = 0; i < desc.rank; ++i) { count *= shape[i]; span += (shape[i] ? shape[i] - 1 : 0) * strides[i]; }
+        desc.count = count;
+        desc.spanCount = count ? span : 0;
+    }
+};
+
+}  // namespace
+
+cudaError_t srtMatmulSharded(srtShardAxis axis, int32_t world, int32_t rank, const void* a, const srtTensorDescriptor* aDesc,
+                             bool transA, const void* b, const srtTensorDescriptor* bDesc, bool transB, const void* bias,
+                             const srtTensorDescriptor* biasDesc, srtActivationType activation, void* out,
+                             const srtTensorDescriptor* oDesc, int32_t peerCount, void* const* peerOut, void* multicastOut,
+                             cudaStream_t stream)
+{
+    if (!aDesc || !bDesc || !oDesc || !aDesc->shape || !bDesc->shape || !oDesc->shape || !aDesc->strides || !bDesc->strides ||
+        !oDesc->strides)
+        return fail(cudaErrorInvalidValue, "srtMatmulSharded: null descriptor");
+    if (aDesc->rank < 2 || aDesc->rank > 3 || bDesc->rank < 2 || bDesc->rank > 3 || oDesc->rank < 2 || oDesc->rank > 3)
+        return fail(cudaErrorNotSupported, "srtMatmulSharded: tensors of rank 2 or 3 expected");
+    if (peerCount < 0 || peerCount > (int32_t)kMaxPeers || (peerCount > 0 && !peerOut))
+        return fail(cudaErrorInvalidValue, "srtMatmulSharded: peerCount %d outside 0..%u, or null peerOut", peerCount, kMaxPeers);
+    const size_t elem = elem_size(oDesc->type);
+    if (elem == 0) return fail(cudaErrorNotSupported, "element type %d is not computed by this library", (int)oDesc->type);
+    SlicedTensor sa, sb, so, sbias;
+    sa.init(a, aDesc); sb.init(b, bDesc); so.init(out, oDesc);
+    const uint32_t aq = aDesc->rank - 2, bq = bDesc->rank - 2, oq = oDesc->rank - 2;
+    size_t total = 0, align = 1;
+    switch (axis) {
+    case srtShardBatch:
+        if (oDesc->rank != 3) return fail(cudaErrorInvalidValue, "srtMatmulSharded: batch sharding needs a rank-3 result");
+        total = oDesc->shape[0];
+        break;
+    case srtShardM: total = oDesc->shape[oq]; break;
+    case srtShardN: total = oDesc->shape[oq + 1]; align = 16 / elem; break;       // column blocks stay 16-byte aligned
+    default: return fail(cudaErrorInvalidValue, "srtMatmulSharded: unknown axis %d", (int)axis);
+    }
+    size_t lo = 0, hi = 0;
+    cudaError_t e = srtShardRange(total, world, rank, align, &lo, &hi);
+    if (e != cudaSuccess) return e;
+    if (hi <= lo) return cudaSuccess;                                              // more ranks than blocks: nothing for this one
+    const void* bias_ptr = bias;
+    const srtTensorDescriptor* bias_desc = biasDesc;
+    uint32_t odim = 0;
+    if (axis == srtShardBatch) {
+        if (aDesc->rank == 3 && aDesc->shape[0] != 1) sa.narrow(0, lo, hi, elem);
+        if (bDesc->rank == 3 && bDesc->shape[0] != 1) sb.narrow(0, lo, hi, elem);
+        odim = 0;
+    } else if (axis == srtShardM) {
+        sa.narrow(aq + (transA ? 1 : 0), lo, hi, elem);
+        odim = oq;
+    } else {
+        sb.narrow(bq + (transB ? 0 : 1), lo, hi, elem);
+        odim = oq + 1;
+        if (bias) {
+            if (!biasDesc || biasDesc->rank != 1 || !biasDesc->shape || !biasDesc->strides)
+                return fail(cudaErrorInvalidValue, "srtMatmulSharded: bias must be rank 1");
+            sbias.init(bias, biasDesc);
+            sbias.narrow(0, lo, hi, elem);
+            bias_ptr = sbias.ptr;
+            bias_desc = &sbias.desc;
+        }
+    }
+    const size_t out_offset = lo * so.strides[odim] * elem;
+    so.narrow(odim, lo, hi, elem);
+    void* peers[kMaxPeers];
+    for (int32_t i = 0; i < peerCount; ++i) {
+        if (!peerOut[i]) return fail(cudaErrorInvalidValue, "srtMatmulSharded: peerOut[%d] is null", i);
+        peers[i] = static_cast<char*>(peerOut[i]) + out_offset;
+    }
+    void* mc = multicastOut ? static_cast<char*>(multicastOut) + out_offset : nullptr;
+    void* out_view = const_cast<char*>(so.ptr);
+    if (mc) {
+        e = srtMatmulAllGatherMulticast(sa.ptr, &sa.desc, transA, sb.ptr, &sb.desc, transB, bias_ptr, bias_desc, activation, out_view,
+                                        &so.desc, mc, stream);
+        if (e != cudaErrorNotSupported || peerCount == 0) return e;             // not eligible: peer by peer instead
+    }
+    if (peerCount > 0)
+        return srtMatmulAllGather(sa.ptr, &sa.desc, transA, sb.ptr, &sb.desc, transB, bias_ptr, bias_desc, activation, out_view,
+                                  &so.desc, peerCount, peers, stream);
+    return srtMatmulBiasActivation(sa.ptr, &sa.desc, transA, sb.ptr, &sb.desc, transB, bias_ptr, bias_desc, activation, out_view,
+                                   &so.desc, stream);
+}
+
+cudaError_t srtMatmulShardedDevices(srtShardAxis axis, int32_t nDevices, const cudaStream_t* streams, const void* const* a,
+                                    const srtTensorDescriptor* aDesc, bool transA, const void* const* b,
+                                    const srtTensorDescriptor* bDesc, bool transB, const void* const* bias,
+                                    const srtTensorDescriptor* biasDesc, srtActivationType activation, void* const* out,
+                                    const srtTensorDescriptor* oDesc, bool gather)
+{
+    if (nDevices < 1 || nDevices > (int32_t)kMaxPeers + 1 || !streams || !a || !b || !out)
+        return fail(cudaErrorInvalidValue, "srtMatmulShardedDevices: 1..%u devices with their streams and buffers expected", kMaxPeers + 1);
+    int devices[kMaxPeers + 1];
+    for (int32_t i = 0; i < nDevices; ++i) {
+        DeviceScope scope(streams[i]);
+        if (scope.status != cudaSuccess) return scope.status;
+        devices[i] = scope.device;
+    }
+    if (gather && nDevices > 1) {
+        // every device stores into every other device's result buffer: one process, so plain peer access
+        for (int32_t i = 0; i < nDevices; ++i) {
+            DeviceScope scope(streams[i]);
+            for (int32_t j = 0; j < nDevices; ++j) {
+                if (devices[j] == devices[i]) continue;
+                int can = 0;
+                cudaError_t e = cudaDeviceCanAccessPeer(&can, devices[i], devices[j]);
+                if (e != cudaSuccess) return e;
+                if (!can) return fail(cudaErrorNotSupported, "srtMatmulShardedDevices: device %d cannot address device %d", devices[i], devices[j]);
+                e = cudaDeviceEnablePeerAccess(devices[j], 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+                else if (e != cudaSuccess) return fail(e, "cudaDeviceEnablePeerAccess(%d -> %d) failed: %s", devices[i], devices[j], cudaGetErrorString(e));
+            }
+        }
+    }
+    for (int32_t i = 0; i < nDevices; ++i) {
+        void* peers[kMaxPeers];
+        int32_t count = 0;
+        if (gather)
+            for (int32_t j = 0; j < nDevices; ++j)
+                if (j != i) peers[count++] = out[j];
+        cudaError_t e = srtMatmulSharded(axis, nDevices, i, a[i], aDesc, transA, b[i], bDesc, transB, bias ? bias[i] : nullptr, biasDesc,
+                                         activation, out[i], oDesc, count, peers, nullptr, streams[i]);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t srtMatmulSetWaitLimit(uint64_t nanoseconds)
+{
+    const unsigned long long v = nanoseconds ? (unsigned long long)nanoseconds : (unsigned long long)srt::kDefaultWaitLimitNs;
+    const cudaError_t e = cudaMemcpyToSymbol(srt::g_wait_limit_ns, &v, sizeof v);
+    return e == cudaSuccess ? e : fail(e, "srtMatmulSetWaitLimit: %s", cudaGetErrorString(e));
+}
+
+// ------------------------------------------------------------------ srtMatmulNoAlloc
 cudaError_t srtMatmulNoAlloc(const void* a, const srtTensorDescriptor* aDesc, bool transA, const void* b,
                              const srtTensorDescriptor* bDesc, bool transB, void* out, const srtTensorDescriptor* oDesc,
                              cudaStream_t stream)
 {
-    Problem P;
-    memset(&P, 0, sizeof P);
-    cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out, oDesc, P);
-    if (e != cudaSuccess) return e;
-    if (is_empty(P)) return cudaSuccess;
-    Plan plan;
-    e = plan_for(P, plan);
-    if (e != cudaSuccess) return e;
-    Prepared pr;
-    e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, pr) : prepare_tc(plan, pr);
-    if (e != cudaSuccess) return e;
-    if (pr.splits <= 1) return launch_prepared(pr, stream);      // this plan has no scratch to place
-
-    if (pr.ws_bytes > kNoAllocScratchBytes)
-        return fail(cudaErrorInvalidValue,
-                    "srtMatmulNoAlloc: this product needs %zu bytes of scratch (%u partial results of %llu x %llu x %llu "
-                    "fp32 values) but the static scratch holds %zu; use srtMatmul, or srtMatmulSetSplitK(1)",
-                    pr.ws_bytes, pr.splits, (unsigned long long)plan.Q.batch, (unsigned long long)plan.Q.M,
-                    (unsigned long long)plan.Q.N, kNoAllocScratchBytes);
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    void* scratch = nullptr;
-    e = no_alloc_scratch(dev, &scratch);
-    if (e != cudaSuccess) return e;
-    e = bind_workspace(pr, scratch);
-    if (e != cudaSuccess) return e;
-    // first pass: every element of every partial-sum slice is written before the second pass reads
-    // it, so nothing in the scratch has to start at zero and what an earlier call left is harmless
-    const uint32_t bn = pr.bn;
-    if (pr.kernel == srtMatmulKernelTcgen05Split) {
-        e = bn == 64    ? launch_split<64>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream)
-            : bn == 128 ? launch_split<128>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream)
-                        : launch_split<256>(pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
-    } else if (pr.type == real16F) {
-        e = launch_tc_bn<__half, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
-    } else if (pr.type == real16BF) {
-        e = launch_tc_bn<__nv_bfloat16, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
-    } else {
-        e = launch_tc_bn<float, float>(bn, pr.ma, pr.mb, pr.mo, pr.gp, pr.ctas, pr.smem, stream);
-    }
-    if (e != cudaSuccess) return e;
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    e = launch_reduce(pr, stream);
-    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
-    return e;
+    // The same planning, call cache and launches as srtMatmul.  A split-K plan binds its partial sums
+    // to the static array: the first pass writes every element of every slice before the second pass
+    // reads it, so nothing in the array has to start at zero and what an earlier call left is harmless.
+    return run_matmul(a, aDesc, transA, b, bDesc, transB, nullptr, nullptr, srtActivationIdentity, out, oDesc, stream, true);
 }
 
 // ------------------------------------------------------------------ srtMatmulAllGather
@@ -1797,9 +2200,9 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
     cudaError_t e = parse(a, aDesc, transA, b, bDesc, transB, bias, biasDesc, (int)activation, out, oDesc, P);
     if (e != cudaSuccess) return e;
     if (is_empty(P)) return cudaSuccess;
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    const int dev = scope.device;
     key.call.force = g_tuning.force_kernel.load(std::memory_order_relaxed);
     key.call.tile_n = g_tuning.tile_n.load(std::memory_order_relaxed);
     key.call.stages = g_tuning.stages.load(std::memory_order_relaxed);
@@ -1936,10 +2339,6 @@ cudaError_t srtPeerMemFree(void* ptr)
     cudaError_t e = cudaFree(ptr);
     return e == cudaSuccess ? e : fail(e, "srtPeerMemFree: %s", cudaGetErrorString(e));
 }
-
-#ifdef SRT_TRACE
-cudaError_t srtMatmulDebugTrace(long long* dst) { return cudaMemcpyFromSymbol(dst, srt::g_trace, sizeof(long long) * 8192); }
-#endif
 
 uint64_t srtMatmulLaunchCount(void) { return g_launches.load(); }
 

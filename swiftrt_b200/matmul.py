@@ -328,5 +328,21 @@ def check_status(device=None) -> int:
     return status.value
 
 
+def release_workspaces(include_captured: bool = False) -> None:
+    """Frees the library's per-(device, stream) scratch buffers (srtMatmulReleaseWorkspaces)."""
+    rc = lib.srtMatmulReleaseWorkspaces(bool(include_captured))
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+
+
+def set_wait_limit(nanoseconds: int = 0, device=None) -> None:
+    """Limit of every pipeline wait inside the tensor-core kernels of `device` (0 = the default)."""
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(dev):
+        rc = lib.srtMatmulSetWaitLimit(int(nanoseconds))
+    if rc != _lib.cudaSuccess:
+        raise MatmulError(rc, _lib.last_error())
+
+
 def launch_count() -> int:
     return int(lib.srtMatmulLaunchCount())

@@ -2,8 +2,8 @@
 loop of RecurrentLayer (Sources/SwiftRTLayers/Recurrent.swift:165-266, 346-370).
 
 Only what sits on the matmul path is mirrored: the cell step (concatenate, matmul(bias:), gates)
-runs as srtLstmCell; parameter initialisers, the derivative plumbing and the GRU cell, whose
-reference weights are [inputSize x 1] placeholders (Recurrent.swift:311-323), are not."""
+runs as srtLstmCell, the GRU step as srtGruCell; parameter initialisers and the derivative plumbing
+are not mirrored."""
 from __future__ import annotations
 
 from typing import NamedTuple, Sequence
@@ -122,6 +122,38 @@ class BasicRNNCell:
             args += [t.data_ptr() if t is not None else None, d.ref() if d is not None else None]
         with torch.cuda.device(input.device):
             rc = lib.srtRnnCell(*args, torch.cuda.current_stream(input.device).cuda_stream)
+        if rc != _lib.cudaSuccess:
+            raise MatmulError(rc, _lib.last_error())
+        return new_state
+
+
+class GRUCell:
+    """GRUCell (Recurrent.swift:271-342) with weights of the sizes its formulas need (the
+    reference's initialiser allocates [inputSize x 1] placeholders, Recurrent.swift:311-323):
+    reset / update / output Weight1 [inputSize x hiddenSize], Weight2 [hiddenSize x hiddenSize],
+    biases [hiddenSize].  The six products of callAsFunction (Recurrent.swift:328-337) are fused
+    into two at construction: gate weight [[resetW1 | updateW1], [resetW2 | updateW2]] and output
+    weight [[outputW1], [outputW2]]."""
+
+    def __init__(self, reset_w1, reset_w2, reset_bias, update_w1, update_w2, update_bias, output_w1, output_w2, output_bias):
+        self.hidden_size = int(reset_w2.shape[0])
+        self.gate_weight = torch.cat([torch.cat([reset_w1, update_w1], dim=1), torch.cat([reset_w2, update_w2], dim=1)], dim=0).contiguous()
+        self.gate_bias = torch.cat([reset_bias, update_bias]).contiguous() if reset_bias is not None else None
+        self.output_weight = torch.cat([output_w1, output_w2], dim=0).contiguous()
+        self.output_bias = output_bias
+
+    def zero_state(self, input: torch.Tensor) -> torch.Tensor:
+        return torch.zeros((input.shape[0], self.hidden_size), dtype=input.dtype, device=input.device)
+
+    def __call__(self, input: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        new_state = torch.empty_like(state, memory_format=torch.contiguous_format)
+        tensors = (input, state, self.gate_weight, self.gate_bias, self.output_weight, self.output_bias, new_state)
+        descs = [_descriptor(t) if t is not None else None for t in tensors]
+        args = []
+        for t, d in zip(tensors, descs):
+            args += [t.data_ptr() if t is not None else None, d.ref() if d is not None else None]
+        with torch.cuda.device(input.device):
+            rc = lib.srtGruCell(*args, torch.cuda.current_stream(input.device).cuda_stream)
         if rc != _lib.cudaSuccess:
             raise MatmulError(rc, _lib.last_error())
         return new_state

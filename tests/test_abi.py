@@ -26,6 +26,37 @@ def test_library_exports_every_declared_symbol():
     assert sorted(srt.EXPORTS) == declared
 
 
+def test_library_exports_nothing_but_its_entry_points():
+    """Every dynamic symbol the library defines is an srt* entry point: helpers and state stay
+    internal, so they can neither collide with nor be interposed by a host program's symbols."""
+    import subprocess
+    import swiftrt_b200 as srt
+    out = subprocess.run(["nm", "-D", "--defined-only", srt.SO], capture_output=True, text=True, check=True).stdout
+    names = [line.split()[-1] for line in out.splitlines() if line.strip()]
+    own = [n for n in names if not n.startswith("_") and not n.startswith("cuda") and not n.startswith("__")]
+    leaked = [n for n in own if not n.startswith("srt")]
+    assert not leaked, leaked
+    assert sorted(n for n in own if n.startswith("srt")) == sorted(srt.EXPORTS)
+
+
+@pytest.mark.parametrize("total,world,align", [(64, 8, 1), (65536, 8, 1), (16384, 8, 8), (10, 4, 1), (100, 8, 8), (3, 8, 1), (0, 2, 1)])
+def test_shard_range_of_the_library_equals_the_host_mirror(total, world, align):
+    """srtShardRange (C) and sharded.shard_range (Python) are one arithmetic; blocks are contiguous,
+    cover everything once and start on multiples of `align`."""
+    from swiftrt_b200 import _lib
+    from swiftrt_b200.sharded import shard_range
+    covered = 0
+    for rank in range(world):
+        lo, hi = ctypes.c_size_t(), ctypes.c_size_t()
+        assert _lib.lib.srtShardRange(total, world, rank, align, ctypes.byref(lo), ctypes.byref(hi)) == 0
+        assert (lo.value, hi.value) == shard_range(total, world, rank, align)
+        assert lo.value == covered and (lo.value % align == 0 or lo.value == total)
+        covered = hi.value
+    assert covered == total
+    lo, hi = ctypes.c_size_t(), ctypes.c_size_t()
+    assert _lib.lib.srtShardRange(8, 2, 2, 1, ctypes.byref(lo), ctypes.byref(hi)) == 1
+
+
 def test_descriptor_layout_matches_reference_struct():
     # srtTensorDescriptor: {int32 type; uint32 rank; int32 order; size_t count, spanCount; 3 pointers}
     # (Modules/SwiftRTCuda/tensor_api.h:70-87) -> 56 bytes, count at offset 16 on LP64

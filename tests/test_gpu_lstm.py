@@ -220,3 +220,35 @@ def test_sequence_without_per_step_concatenation(srt, kat, oracle):
     assert srt.check_status() == 0
     for a, c in zip(ref, got):
         assert torch.equal(a.cell, c.cell) and torch.equal(a.hidden, c.hidden)
+
+
+@pytest.mark.parametrize("dtype,batch,nx,nh", [(F32, 5, 7, 6), (F32, 64, 96, 128), (BF16, 256, 256, 256), (F16, 33, 40, 24)])
+def test_gru_cell_matches_operator_by_operator_composition(srt, oracle, dtype, batch, nx, nh):
+    """srtGruCell (two fused products) against GRUCell.callAsFunction composed operator by operator on
+    the CPU (Sources/SwiftRTLayers/Recurrent.swift:328-337).  The reference holds no GRU test data, so
+    the oracle composition is the pin; the fused products round once where the composition rounds per
+    operator, hence the path's tolerances rather than bit equality."""
+    rng = np.random.default_rng(batch + nx + nh)
+    sc = 1.0 / np.sqrt(nx + nh)
+    w = {name: random_bits(oracle, rng, shape, dtype, scale=sc) for name, shape in (
+        ("resetW1", (nx, nh)), ("resetW2", (nh, nh)), ("updateW1", (nx, nh)), ("updateW2", (nh, nh)),
+        ("outputW1", (nx, nh)), ("outputW2", (nh, nh)))}
+    for name in ("resetB", "updateB", "outputB"):
+        w[name] = random_bits(oracle, rng, (nh,), dtype, scale=0.5)
+    x = random_bits(oracle, rng, (batch, nx), dtype)
+    h = random_bits(oracle, rng, (batch, nh), dtype)
+    want = oracle.gru_cell(x, h, w, dtype)
+    d = {k: to_dev(v, dtype) for k, v in w.items()}
+    cell = srt.GRUCell(d["resetW1"], d["resetW2"], d["resetB"], d["updateW1"], d["updateW2"], d["updateB"],
+                       d["outputW1"], d["outputW2"], d["outputB"])
+    before = srt.launch_count()
+    got = cell(to_dev(x, dtype), to_dev(h, dtype))
+    torch.cuda.synchronize()
+    assert srt.launch_count() - before == 5
+    assert srt.check_status() == 0
+    tol = 1e-5 if dtype == F32 else TOL[dtype]
+    assert oracle.rel_frobenius(oracle.decode(from_dev(got, dtype), dtype), oracle.decode(want, dtype)) <= tol
+    # a second step from the new state, in place (newHidden aliases hidden)
+    want2 = oracle.gru_cell(x, want, w, dtype)
+    got2 = cell(to_dev(x, dtype), got)
+    assert oracle.rel_frobenius(oracle.decode(from_dev(got2, dtype), dtype), oracle.decode(want2, dtype)) <= 2 * tol

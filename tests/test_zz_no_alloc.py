@@ -37,6 +37,8 @@ def _rel(x, ref):
     (torch.bfloat16, 256, 256, 8192, False),       # few tiles, long reduction: split for occupancy
     (torch.float16, 130, 200, 4096, True),         # ragged edges
     (torch.float32, 512, 256, 4096, False),        # Float32 beyond K = 2048: split for accuracy
+    (torch.bfloat16, 32, 1024, 2048, False),       # a few rows against a wide operand: planned transposed,
+                                                   # the reduce pass turns the tile (splitk_reduce_transposed_kernel)
 ])
 def test_no_alloc_matches_regular_entry_point_on_two_calls_in_a_row(dtype, M, N, K, tb):
     import swiftrt_b200 as srt
@@ -50,6 +52,8 @@ def test_no_alloc_matches_regular_entry_point_on_two_calls_in_a_row(dtype, M, N,
         want = srt.matmul(a, b, False, tb)                                   # regular entry point
         plan = srt.query_plan(a, b, want, False, tb)
         assert plan["splitK"] > 1 and plan["workspaceBytes"] <= 16 << 20, plan   # the scratch is really used
+        if M == 32:
+            assert plan["swapped"] == 1, plan
         got = torch.full_like(want, float("nan"))
         torch.cuda.synchronize()
         free_before = torch.cuda.mem_get_info(dev)[0]
@@ -74,10 +78,12 @@ def test_no_alloc_refuses_products_beyond_the_static_scratch():
         a = torch.ones((2048, 4096), dtype=torch.bfloat16, device=dev)
         b = torch.ones((4096, 2048), dtype=torch.bfloat16, device=dev)
         out = torch.zeros((2048, 2048), dtype=torch.bfloat16, device=dev)
+        launches = srt.launch_count()
         rc, err = _no_alloc(srt, out, a, False, b, False)
         assert rc == 1 and "static scratch" in err and "67108864" in err, (rc, err)
+        assert srt.launch_count() == launches           # nothing was launched
         torch.cuda.synchronize()
-        assert float(out.float().abs().sum()) == 0.0  # nothing was launched
+        assert float(out.float().abs().sum()) == 0.0
         # a product that is not split needs no scratch and is never refused for its size
         srt.set_split_k(1)
         rc, err = _no_alloc(srt, out, a, False, b, False)
@@ -87,3 +93,36 @@ def test_no_alloc_refuses_products_beyond_the_static_scratch():
     finally:
         srt.set_tuning(0, 0, 0, 0)
         srt.set_split_k(0)
+
+
+def test_no_alloc_first_call_for_a_kernel_variant_and_second_device():
+    """The very first launch of a kernel variant loads its code (CUDA loads modules lazily), which takes
+    device memory inside the driver: the header asks for that first call to happen where allocation is
+    allowed.  Here srtMatmulNoAlloc is the first to run a shape and element type no other test uses;
+    the memory the cold call took is printed, the warm call must take none, and both must be right.
+    With two GPUs the same is repeated on the second one (its own copy of the scratch array)."""
+    import swiftrt_b200 as srt
+    srt.set_tuning(0, 0, 0, 0)
+    srt.set_split_k(0)
+    for index in range(min(2, torch.cuda.device_count())):
+        dev = torch.device("cuda", index)
+        with torch.cuda.device(dev):
+            g = torch.Generator(device=dev).manual_seed(99 + index)
+            a = (torch.rand((96, 6144), device=dev, generator=g) * 2 - 1).to(torch.float16)
+            b = (torch.rand((6144, 72), device=dev, generator=g) * 2 - 1).to(torch.float16)
+            got = torch.zeros((96, 72), dtype=torch.float16, device=dev)
+            ref = a.double() @ b.double()
+            torch.cuda.synchronize(dev)
+            for attempt in ("cold", "warm"):
+                got.zero_()
+                torch.cuda.synchronize(dev)
+                free_before = torch.cuda.mem_get_info(dev)[0]
+                rc, err = _no_alloc(srt, got, a, False, b, False)
+                assert rc == 0, err
+                torch.cuda.synchronize(dev)
+                taken = free_before - torch.cuda.mem_get_info(dev)[0]
+                print(f"srtMatmulNoAlloc {attempt} call on {dev}: {taken} bytes of device memory taken")
+                if attempt == "warm":
+                    assert taken <= 0, taken
+                assert _rel(got, ref) <= 2e-3
+            assert srt.check_status(dev) == 0
