@@ -1,14 +1,22 @@
 #!/usr/bin/env python
-"""Benchmark of the matmul hot path: GEMM TFLOP/s at the large-square BFloat16 configuration
-(C = A . B, 16384 x 16384 x 16384, row-major, fp32 accumulate, BFloat16 output).
+"""Benchmark of the matmul hot path: GEMM TFLOP/s on the five named configurations.
 
-  python bench.py --gpus N --steps K --warmup W            # this library (one rank per GPU)
-  python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU algorithm
+  python bench.py --gpus N --steps K --warmup W [--workload c5]     # this library (one rank per GPU)
+  python bench.py --impl reference --gpus N --steps K ...           # the reference's CPU algorithm
 
-At N > 1 (launched by torch.distributed.run) the columns of B and C are sharded over the ranks,
-no collective in the data path (strong scaling: the total work is fixed).  A "step" is one
-matmul of the whole problem; `value` counts the algorithmic 2.M.N.K flops of all ranks over the
-max-over-ranks device time.  Rank 0 prints one JSON line.
+Workloads (`--workload`; the default, c5 = bf16_16384, is the one the target is quoted on):
+  c1  Float32 256^3                                        one GPU's worth of work, replicated at N > 1
+  c2  Dense bf16 [1024x4096].[4096x4096] + bias, ReLU      sharded over N (weight columns)
+  c3  fp16 batched 64 x [512x64].[512x64]^T                sharded over the batch
+  c4  Float32 [65536x1024].[1024x256]                      sharded over M
+  c5  bf16 16384^3                                         sharded over N
+
+At N > 1 (launched by torch.distributed.run) every rank computes its block with no collective in
+the data path (strong scaling: the total work is fixed).  A "step" is one product of the whole
+problem; `value` counts the algorithmic 2.M.N.K flops of all ranks over the max-over-ranks device
+time.  Rank 0 prints one JSON line.  Every line carries a `parity` object: seeded rows of the TIMED
+result (what the last timed step left in the output buffer) against the CPU restatement of the
+reference loop, with the tolerance of the element type.
 """
 from __future__ import annotations
 
@@ -23,12 +31,32 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+F32, F16, BF16 = 0, 2, 14
+# name: M, N, K, batch, dtype, trans_b, bias+relu, value range / distribution, shard axis, roofline bound, description
 WORKLOADS = {
-    # name: (M, N, K, dtype, description)
-    "bf16_16384": (16384, 16384, 16384, "bf16", "C = A.B 16384^3 BFloat16, uniform[-1,1), fp32 accumulate, BFloat16 out"),
-    "bf16_8192": (8192, 8192, 8192, "bf16", "C = A.B 8192^3 BFloat16 (reduced size, not the headline)"),
+    "c1": dict(M=256, N=256, K=256, batch=1, dtype="f32", tb=False, dense=False, dist=("uniform", 1.0), axis=None, bound="hbm",
+               desc="C = A.B 256^3 Float32, uniform[-1,1), row-major, no transpose"),
+    "c2": dict(M=1024, N=4096, K=4096, batch=1, dtype="bf16", tb=False, dense=True, dist=("uniform", 0.05), axis="n", bound="tensor",
+               desc="Dense forward X[1024x4096].W[4096x4096] + bias[4096], ReLU, BFloat16 uniform[-0.05,0.05), fp32 accumulate"),
+    "c3": dict(M=512, N=512, K=64, batch=64, dtype="f16", tb=True, dense=False, dist=("normal", 1.0), axis="batch", bound="hbm",
+               desc="strided batched 64 x A[512x64].B[512x64]^T Float16 normal(0,1), fp32 accumulate, Float16 out"),
+    "c4": dict(M=65536, N=256, K=1024, batch=1, dtype="f32", tb=False, dense=False, dist=("uniform", 1.0), axis="m", bound="hbm",
+               desc="tall-skinny C = A[65536x1024].B[1024x256] Float32 uniform[-1,1), fp32 tolerance path"),
+    "c5": dict(M=16384, N=16384, K=16384, batch=1, dtype="bf16", tb=False, dense=False, dist=("uniform", 1.0), axis="n", bound="tensor",
+               desc="C = A.B 16384^3 BFloat16, uniform[-1,1), fp32 accumulate, BFloat16 out"),
+    "bf16_8192": dict(M=8192, N=8192, K=8192, batch=1, dtype="bf16", tb=False, dense=False, dist=("uniform", 1.0), axis="n", bound="tensor",
+                      desc="C = A.B 8192^3 BFloat16 (reduced size for profiler captures, not a headline)"),
 }
+WORKLOADS["bf16_16384"] = WORKLOADS["c5"]
+ELEM = {"f32": 4, "f16": 2, "bf16": 2}
+ORACLE_TYPE = {"f32": F32, "f16": F16, "bf16": BF16}
+TOLERANCE = {"f32": 1e-5, "f16": 1e-2, "bf16": 1e-2}          # relative Frobenius error against the reference CPU loop
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+KERNEL_NAMES = {1: "gemm_simt_kernel", 2: "gemm_tcgen05_kernel", 3: "gemm_tcgen05_pair_kernel", 4: "gemm_tcgen05_split_kernel",
+                5: "gemm_tf32x3_pair_kernel"}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum from one ncu capture, see profiles/), one GPU,
+# default plan: workload -> (kernel id the figure belongs to, bytes)
+MEASURED_TRAFFIC = {"c5": (3, 9.38e9), "c2": (3, 42.08e6), "c3": (2, 8.5e6), "bf16_8192": (3, 1.206e9)}
 
 
 def peaks():
@@ -40,6 +68,22 @@ def peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def algorithmic(w, world=1):
+    """(flops, bytes) of one step of the whole workload, and of one rank's share."""
+    e = ELEM[w["dtype"]]
+    flops = 2.0 * w["batch"] * w["M"] * w["N"] * w["K"]
+    nbytes = e * w["batch"] * (w["M"] * w["K"] + w["K"] * w["N"] + w["M"] * w["N"]) + (e * w["N"] if w["dense"] else 0)
+    if world == 1 or w["axis"] is None:
+        return flops, nbytes, flops, nbytes
+    if w["axis"] == "batch":
+        local_bytes = nbytes / world
+    elif w["axis"] == "m":
+        local_bytes = e * (w["M"] * w["K"] / world + w["K"] * w["N"] + w["M"] * w["N"] / world)
+    else:
+        local_bytes = e * (w["M"] * w["K"] + w["K"] * w["N"] / world + w["M"] * w["N"] / world)
+    return flops, nbytes, flops / world, local_bytes
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -49,7 +93,7 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.proc = None
-        self.lines: list[str] = []
+        self.lines: list = []          # (arrival time, text)
         self.thread = None
 
     def start(self):
@@ -65,7 +109,33 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    @staticmethod
+    def _parse(lines):
+        sm, smax, power, reasons = [], [], [], set()
+        for line in lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return sm, smax, power, reasons
+
+    def window(self, t0: float, t1: float):
+        """Median SM MHz of the samples that arrived in [t0, t1] (None without samples)."""
+        sm, _, _, _ = self._parse([text for t, text in self.lines if t0 <= t <= t1 + 0.03])
+        if not sm:
+            return None
+        sm.sort()
+        return sm[len(sm) // 2]
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -75,64 +145,94 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        for line in self.lines:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+        sm, smax, power, reasons = self._parse([text for _, text in self.lines])
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # the clock under load: median of the upper half of the samples (idle samples drop out)
-        sm.sort()
-        upper = sm[len(sm) // 2:]
-        return {"sm_mhz": upper[len(upper) // 2], "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        # the clock under load: median of the upper half of the samples by power draw (idle samples drop out)
+        order = sorted(range(len(sm)), key=lambda i: power[i])
+        loaded = sorted(sm[i] for i in order[len(order) // 2:])
+        return {"sm_mhz": loaded[len(loaded) // 2], "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
 
 
-# ---------------------------------------------------------------------------------------------
-def cpu_inputs(N, K):
-    """B of the workload as stored BFloat16 bits (seeded, uniform[-1,1)), made once per run."""
+# --------------------------------------------------------------------------------------------- host-side (CPU) legs
+def host_threads() -> int:
+    # every core this process may run on (torchrun sets OMP_NUM_THREADS=1, which is not the machine)
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def host_inputs(w, seed=0, rows=None, only_a=False):
+    """Seeded host operands of the workload as stored bits, generated by numpy (the CPU legs' own
+    inputs: same shapes and value distribution as the device run).  `rows` limits A to that many rows."""
     import numpy as np
     from oracle import oracle
-    rng = np.random.default_rng(0)
-    b = np.empty((K, N), dtype=np.uint16)
-    for r0 in range(0, K, 1024):                      # in slabs: keeps the float32 staging small
-        blk = rng.random((min(1024, K - r0), N), dtype=np.float32) * 2.0 - 1.0
-        b[r0:r0 + blk.shape[0]] = oracle.encode(blk, oracle.BF16)
-    return b
+    dt = ORACLE_TYPE[w["dtype"]]
+    rng = np.random.default_rng(seed)
+    kind, scale = w["dist"]
+
+    def draw(shape):
+        out = np.empty(shape, dtype=oracle.np_dtype(dt))
+        flat = out.reshape(-1, shape[-1])
+        for r0 in range(0, flat.shape[0], 4096):                      # in slabs: keeps the float32 staging small
+            n = min(4096, flat.shape[0] - r0)
+            blk = (rng.standard_normal((n, shape[-1]), dtype=np.float32) * scale if kind == "normal"
+                   else (rng.random((n, shape[-1]), dtype=np.float32) * 2.0 - 1.0) * scale)
+            flat[r0:r0 + n] = oracle.encode(blk, dt)
+        return out
+    m = w["M"] if rows is None else rows
+    lead = (w["batch"],) if w["batch"] > 1 else ()
+    a = draw(lead + (m, w["K"]))
+    if only_a:
+        return a, None, None
+    b = draw(lead + ((w["N"], w["K"]) if w["tb"] else (w["K"], w["N"])))
+    bias = draw((1, w["N"]))[0] if w["dense"] else None
+    return a, b, bias
 
 
-def cpu_sample(M, N, K, b, threads=None, target_s=12.0):
-    """Times the CPU restatement of the reference loop on a bounded row sample of the workload
-    (same seeded value distribution), all host threads.  Returns (tflops, cores, description, seconds)."""
-    import numpy as np
+def cpu_time(w, a, b, bias, mode, threads):
+    """Seconds of one run of the CPU restatement of the reference loop on these operands."""
     from oracle import oracle
-    if threads is None:
-        # every core this process may run on (torchrun sets OMP_NUM_THREADS=1, which is not the machine)
-        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else oracle.lib().oracle_max_threads()
-    rng = np.random.default_rng(1)
-    probe_rows = threads * 8                      # one block of 8 rows per thread
-    a = oracle.encode(rng.random((probe_rows, K), dtype=np.float32) * 2.0 - 1.0, oracle.BF16)
     t0 = time.perf_counter()
-    oracle.matmul(a, b, oracle.BF16, threads=threads)
-    probe = time.perf_counter() - t0
-    rows = int(min(M, max(probe_rows, probe_rows * target_s / max(probe, 1e-6))))
-    rows = max(probe_rows, rows // probe_rows * probe_rows)
-    a = oracle.encode(rng.random((rows, K), dtype=np.float32) * 2.0 - 1.0, oracle.BF16)
-    t0 = time.perf_counter()
-    oracle.matmul(a, b, oracle.BF16, threads=threads)
-    dt = time.perf_counter() - t0
-    tflops = 2.0 * rows * N * K / dt / 1e12
-    desc = f"{rows} of {M} rows of A (all {N} columns, K={K}), k-outer loop order, {threads} OpenMP threads, {dt:.1f} s"
-    return tflops, threads, desc, dt
+    oracle.matmul(a, b, ORACLE_TYPE[w["dtype"]], False, w["tb"], bias=bias, activation="relu" if w["dense"] else None,
+                  mode=mode, threads=threads)
+    return time.perf_counter() - t0
+
+
+_HOST_B: dict = {}
+
+
+def cpu_baseline(w, budget_s: float):
+    """Both CPU variants of the reference algorithm on a bounded sample of the workload:
+    all host threads with the k-outer loop order (bit-identical results), and one thread in the
+    reference's own r, c, k order.  Rows of A are the unit of the sample; rates extrapolate linearly."""
+    threads = host_threads()
+    M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
+    if id(w) not in _HOST_B:                                          # B and the bias once per run
+        _, b0, bias0 = host_inputs(w, seed=1, rows=1)
+        _HOST_B[id(w)] = (b0, bias0)
+    b, bias = _HOST_B[id(w)]
+
+    def leg(mode, nthreads, seconds):
+        probe_rows = min(M, max(8, 8 * nthreads if mode == 1 else 8))
+        a, _, _ = host_inputs(w, seed=3, rows=probe_rows, only_a=True)
+        probe = cpu_time(w, a, b, bias, mode, nthreads)
+        rows = int(min(M, max(probe_rows, probe_rows * seconds / max(probe, 1e-6))))
+        if rows < M:
+            rows = max(probe_rows, rows // probe_rows * probe_rows)
+        if rows > probe_rows:
+            a, _, _ = host_inputs(w, seed=2, rows=rows, only_a=True)
+            dt = cpu_time(w, a, b, bias, mode, nthreads)
+        else:
+            dt = probe
+        tflops = 2.0 * batch * rows * N * K / dt / 1e12
+        order = "k-outer row-blocked loop order" if mode == 1 else "the reference's r, c, k loop order"
+        what = "full size" if rows == M else f"{rows} of {M} rows of A, extrapolated linearly in M"
+        return tflops, f"{what} (all {N} columns, K={K}, batch {batch}), {order}, {nthreads} thread(s), {dt:.2f} s", dt
+
+    all_tf, all_desc, all_dt = leg(1, threads, budget_s * 0.7)
+    one_tf, one_desc, _ = leg(0, 1, budget_s * 0.3)
+    return {"value": all_tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": all_desc,
+            "single_thread": {"value": one_tf, "unit": "TFLOP/s", "cores": 1, "sample": one_desc}}, all_dt
 
 
 def run_reference(args):
@@ -141,65 +241,141 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    M, N, K, dtype, desc = WORKLOADS[args.workload]
+    w = WORKLOADS[args.workload]
     vals, last = [], None
-    b = cpu_inputs(N, K)
     for i in range(args.warmup + args.steps):
-        last = cpu_sample(M, N, K, b, target_s=args.cpu_seconds / max(1, args.warmup + args.steps))
+        last = cpu_baseline(w, args.cpu_seconds / max(1, args.warmup + args.steps))
         if i >= args.warmup:
             vals.append(last)
-    tflops = sum(v[0] for v in vals) / len(vals)
-    ms = sum(v[3] for v in vals) / len(vals) * 1e3
+    tflops = sum(v[0]["value"] for v in vals) / len(vals)
+    ms = sum(v[1] for v in vals) / len(vals) * 1e3
     line = {
         "impl": "reference", "metric": "GEMM TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": desc, "M": M, "N": N, "K": K, "step": "bounded row sample of the workload on the host CPU"},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": last[1], "kind": "port", "sample": last[2]},
+        "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["desc"], "M": w["M"], "N": w["N"], "K": w["K"], "batch": w["batch"],
+                   "step": "bounded row sample of the workload on the host CPU"},
+        "cpu_baseline": last[0],
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     emit(line)
 
 
-def measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier):
-    """End to end: host buffers in, host result out, copies inside the timed region."""
-    import torch
-    import torch.distributed as dist
-    tdt = a.dtype
-    flops = 2.0 * M * N * K
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    ha = a.cpu().pin_memory()
-    hb = b.contiguous().cpu().pin_memory()
-    hc = torch.empty((M, n_local), dtype=tdt).pin_memory()
-    srt.matmul_host(ha, hb, device=dev, out_host=hc)      # warm-up (allocator, pinned pages)
+# --------------------------------------------------------------------------------------------- device legs
+def device_inputs(w, dev, torch):
+    """Full seeded operands on the device (every rank draws the same ones and keeps views of its share)."""
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[w["dtype"]]
+    g = torch.Generator(device=dev).manual_seed(0)
+    kind, scale = w["dist"]
+
+    def draw(shape):
+        if kind == "normal":
+            return (torch.randn(shape, device=dev, generator=g) * scale).to(tdt)
+        return ((torch.rand(shape, device=dev, generator=g) * 2 - 1) * scale).to(tdt)
+    lead = (w["batch"],) if w["batch"] > 1 else ()
+    a = draw(lead + (w["M"], w["K"]))
+    b = draw(lead + ((w["N"], w["K"]) if w["tb"] else (w["K"], w["N"])))
+    bias = draw((w["N"],)) if w["dense"] else None
+    return a, b, bias, tdt
+
+
+def local_views(w, srt, a, b, bias, rank, world):
+    """This rank's operands (views, no copies) and the shape of its result block."""
+    axis = w["axis"] if world > 1 else None
+    lead = (w["batch"],) if w["batch"] > 1 else ()
+    if axis == "batch":
+        lo, hi = srt.shard_range(w["batch"], world, rank, 1)
+        return a[lo:hi], b[lo:hi], bias, (hi - lo, w["M"], w["N"]), (lo, hi)
+    if axis == "m":
+        lo, hi = srt.shard_range(w["M"], world, rank, 1)
+        return a.narrow(-2, lo, hi - lo), b, bias, lead + (hi - lo, w["N"]), (lo, hi)
+    if axis == "n":
+        lo, hi = srt.shard_range(w["N"], world, rank, 16 // ELEM[w["dtype"]])
+        bl = b.narrow(-2, lo, hi - lo) if w["tb"] else b.narrow(-1, lo, hi - lo)
+        return a, bl, (bias[lo:hi] if bias is not None else None), lead + (w["M"], hi - lo), (lo, hi)
+    return a, b, bias, lead + (w["M"], w["N"]), (0, 0)
+
+
+def parity_check(w, torch, a_loc, b_loc, bias_loc, c, seed=1234, rows=32):
+    """Seeded rows of the timed result against the CPU restatement of the reference loop on the same
+    stored bits.  Returns (relative Frobenius error, rows checked)."""
+    import numpy as np
+    from oracle import oracle
+    dt = ORACLE_TYPE[w["dtype"]]
+
+    def bits(t):
+        t = t.detach().contiguous().cpu()
+        return t.numpy() if dt == F32 else t.view(torch.uint16).numpy()
+    g = torch.Generator().manual_seed(seed)
+    if a_loc.dim() == 3:
+        items = torch.randperm(a_loc.shape[0], generator=g)[:max(1, min(2, a_loc.shape[0]))].sort().values.tolist()
+        a_s, b_s, c_s = a_loc[items], b_loc[items], c[items]
+        checked = len(items) * a_loc.shape[1]
+    else:
+        m = a_loc.shape[0]
+        idx = torch.randperm(m, generator=g)[:min(rows, m)].sort().values
+        idx[0], idx[-1] = 0, m - 1                                   # both matrix edges
+        idx = idx.to(a_loc.device)
+        a_s, b_s, c_s = a_loc.index_select(0, idx), b_loc, c.index_select(0, idx)
+        checked = int(idx.numel())
+    threads = max(1, host_threads() // max(1, int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))))
+    want = oracle.matmul(bits(a_s), bits(b_s), dt, False, w["tb"], bias=bits(bias_loc) if bias_loc is not None else None,
+                         activation="relu" if w["dense"] else None, threads=threads)
+    err = oracle.rel_frobenius(oracle.decode(bits(c_s), dt), oracle.decode(want, dt))
+    return float(err), checked
+
+
+def measure_e2e(args, w, srt, torch, dist, a_loc, b_loc, bias_loc, out_shape, rng_lohi, dev, rank, world, barrier):
+    """End to end through the public host-buffer entry: pinned host operands in, host result out,
+    every copy inside the timed region.  At N > 1 every rank holds only its share of the host data."""
+    flops = 2.0 * w["batch"] * w["M"] * w["N"] * w["K"]
+    steps = max(1, min(args.steps, args.e2e_steps))
+    act = srt.ActivationType.relu if w["dense"] else None
+    axis = w["axis"] if world > 1 else None
+    if axis == "n" and w["M"] % world == 0 and a_loc.dim() == 2:
+        mb = w["M"] // world
+        ha = a_loc[rank * mb:(rank + 1) * mb].contiguous().cpu().pin_memory()       # this rank's row block of A
+        how = "each rank uploads its row block of A and its column block of B; A is all-gathered over NVLink"
+    else:
+        ha = a_loc.contiguous().cpu().pin_memory()
+        how = "each rank uploads its own operands"
+        axis = None if axis == "n" else axis
+    hb = b_loc.contiguous().cpu().pin_memory()
+    hbias = bias_loc.contiguous().cpu().pin_memory() if bias_loc is not None else None
+    hc = torch.empty(out_shape, dtype=a_loc.dtype).pin_memory()
+
+    def call():
+        if axis == "n":
+            srt.sharded_matmul_host(ha, hb, False, w["tb"], axis="n", bias=hbias, activation=act, out_host=hc, device=dev)
+        else:
+            srt.matmul_host(ha, hb, False, w["tb"], bias=hbias, activation=act, device=dev, out_host=hc)
+    call()                                                         # warm-up (allocator, pinned pages, NCCL channels)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
-        srt.matmul_host(ha, hb, device=dev, out_host=hc)
+    for _ in range(steps):
+        call()
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
-    h2d = (ha.numel() + hb.numel()) * ha.element_size()
+    ms = float(t.item()) / steps
+    h2d = (ha.numel() + hb.numel() + (hbias.numel() if hbias is not None else 0)) * ha.element_size()
     d2h = hc.numel() * hc.element_size()
     bytes_t = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(bytes_t, op=dist.ReduceOp.SUM)
-    return {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-            "h2d_bytes_per_step": int(bytes_t[0].item()), "d2h_bytes_per_step": int(bytes_t[1].item())}
+    return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+            "h2d_bytes_per_step": int(bytes_t[0].item()), "d2h_bytes_per_step": int(bytes_t[1].item()), "how": how}
 
 
-def measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier):
-    """Full C on every GPU, two ways, same sharding (N over the ranks), device-timed, max over ranks:
-    fused  = srtMatmulAllGather: the product's epilogue stores each tile into every GPU's buffer
-             over NVLink, then a barrier orders the ranks;
-    nccl   = the product, an NCCL all-gather of the column blocks and the copy that places them."""
-    import torch
-    import torch.distributed as dist
+def measure_gather(args, srt, torch, dist, a, b_full, M, N, K, dev, world, barrier):
+    """Full C on every GPU, three ways, same sharding (N over the ranks), device-timed, max over ranks:
+    fused / fused_multicast = the product's epilogue stores each tile into every GPU's buffer over
+    NVLink (per peer, or once through an NVLink multicast mapping), then the ranks are ordered;
+    nccl = the product, an NCCL all-gather of the column blocks and the copy that places them."""
     steps = max(1, min(args.steps, 10))
     flops = 2.0 * M * N * K
     rank = dist.get_rank()
@@ -216,7 +392,6 @@ def measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier):
     def nccl_step():
         srt.sharded_matmul(a, b_full, axis="n", gather=True, out=full)
 
-    # the same through an NVLink multicast mapping: each tile leaves the GPU once, the switch replicates it
     try:
         mbuf = srt.PeerBuffer((M, N), a.dtype, multicast=True)
     except Exception:                 # no symmetric memory on this machine: the per-peer form only
@@ -257,7 +432,6 @@ def measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier):
     return out
 
 
-# ---------------------------------------------------------------------------------------------
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -273,105 +447,143 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    M, N, K, dtype, desc = WORKLOADS[args.workload]
-    tdt = torch.bfloat16
-    lo, hi = srt.shard_range(N, world, rank, 8)
-    n_local = hi - lo
-    g = torch.Generator(device=dev).manual_seed(0)
-    a = (torch.rand((M, K), device=dev, generator=g) * 2 - 1).to(tdt)
-    # every rank draws the same full B and keeps its column block as a strided view
-    b_full = (torch.rand((K, N), device=dev, generator=g) * 2 - 1).to(tdt)
-    b = b_full[:, lo:hi]
-    c = torch.empty((M, n_local), dtype=tdt, device=dev)
+    w = WORKLOADS[args.workload]
+    a, b, bias, tdt = device_inputs(w, dev, torch)
+    a_loc, b_loc, bias_loc, out_shape, lohi = local_views(w, srt, a, b, bias, rank, world)
+    c = torch.empty(out_shape, dtype=tdt, device=dev)
+    act = srt.ActivationType.relu if w["dense"] else None
+    flops, nbytes, flops_local, bytes_local = algorithmic(w, world)
+    # Inputs larger than the 126 MB L2 need no flush between back-to-back steps; smaller workloads get
+    # a cold, clean L2 before every timed step: 256 MiB written (the rule), then 256 MiB read so that
+    # the dirty lines are written back before the timed kernel starts instead of during it.
+    flush_needed = (a_loc.numel() + b_loc.numel()) * a_loc.element_size() < 2 * 126e6
+    flush = torch.zeros((2, 64 * 1024 * 1024), dtype=torch.float32, device=dev) if flush_needed else None
+    sink = torch.zeros((), dtype=torch.float32, device=dev)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step():
-        srt.matmul_into(c, a, False, b, False)
-
     if args.tune:
         srt.set_tuning(*[int(x) for x in args.tune.split(",")])
-    plan = srt.query_plan(a, b, c)
+    op = srt.MatmulOp(c, a_loc, False, b_loc, w["tb"], bias_loc, act)
+    plan = srt.query_plan(a_loc, b_loc, c, False, w["tb"])
+
+    def timed_block(steps):
+        """`steps` launches with one event pair each; returns per-step milliseconds (this rank)."""
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for e0, e1 in ev:
+            if flush is not None:
+                flush[0].zero_()
+                sink.copy_(flush[1].sum())
+            e0.record()
+            op()
+            e1.record()
+        torch.cuda.synchronize()
+        per_step = [e0.elapsed_time(e1) for e0, e1 in ev]
+        # back-to-back steps: the block's time is first record to last record (launch gaps included)
+        total = ev[0][0].elapsed_time(ev[-1][1]) if (flush is None and steps > 0) else sum(per_step)
+        return per_step, total
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()          # nvidia-smi needs ~0.1 s to deliver its first sample: start it early
-    for _ in range(args.warmup):
-        step()
+    timed_block(args.warmup)
     barrier()
     launches0 = srt.launch_count()
-    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    barrier()
-    events[0].record()
-    for i in range(args.steps):
-        step()
-        events[i + 1].record()
-    barrier()
-    total_ms = events[0].elapsed_time(events[-1])
+    t_host0 = time.perf_counter()
+    kernel_ms, total_ms = timed_block(args.steps)
+    t_host1 = time.perf_counter()
     launches = srt.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    barrier()
     status = srt.check_status()
     if status != 0:
         raise SystemExit(f"tensor-core kernel reported pipeline status {status}")
-    kernel_ms = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
     t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
-    flops = 2.0 * M * N * K
     value = flops / (ms_per_step * 1e-3) / 1e12
+
+    # parity of the timed result: every rank checks seeded rows of its own block, the worst error is reported
+    err, checked = parity_check(w, torch, a_loc, b_loc, bias_loc, c)
+    pt = torch.tensor([err], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+    parity = {"rel_frobenius": float(pt.item()), "tolerance": TOLERANCE[w["dtype"]], "ok": bool(float(pt.item()) <= TOLERANCE[w["dtype"]]),
+              "rows_checked_per_rank": checked,
+              "against": "CPU restatement of the reference loop (CpuMath.swift:1141-1186) on the same stored bits; "
+                         "output of the last timed step"}
+
+    # two more blocks of the same length, for the spread under the power cap (not part of `value`)
+    repeats = [{"ms_per_step": ms_per_step, "sm_mhz": sampler.window(t_host0, t_host1) if rank == 0 else None}]
+    for _ in range(max(0, args.repeats - 1)):
+        h0 = time.perf_counter()
+        _, block_ms = timed_block(args.steps)
+        h1 = time.perf_counter()
+        repeats.append({"ms_per_step": block_ms / args.steps, "sm_mhz": sampler.window(h0, h1) if rank == 0 else None})
+    clocks = sampler.stop() if rank == 0 else None
 
     e2e = None
     if not args.no_e2e:
-        e2e = measure_e2e(args, srt, a, b, M, N, K, n_local, dev, world, barrier)
+        e2e = measure_e2e(args, w, srt, torch, dist, a_loc, b_loc, bias_loc, out_shape, lohi, dev, rank, world, barrier)
 
     gather = None
-    if world > 1 and not args.no_gather:
+    if world > 1 and not args.no_gather and w is WORKLOADS["c5"]:
         try:
-            gather = measure_gather(args, srt, a, b_full, M, N, K, dev, world, barrier)
+            gather = measure_gather(args, srt, torch, dist, a, b, w["M"], w["N"], w["K"], dev, world, barrier)
         except Exception as e:        # the headline numbers above stand without this leg
             gather = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     if rank == 0:
         pk, pk_kind = peaks()
         avg_kernel_ms = sum(kernel_ms) / len(kernel_ms)
-        flops_launch = 2.0 * M * n_local * K
-        achieved = flops_launch / (avg_kernel_ms * 1e-3) / 1e12
-        peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-        # DRAM bytes per launch of this kernel on this workload from one ncu capture (dram__bytes_read.sum +
-        # dram__bytes_write.sum, a one-pass metric pair; see profiles/): known for the unsharded 16384^3 case only
-        traffic = 9.38e9 if (world == 1 and args.workload == "bf16_16384" and plan["kernel"] == 3 and not args.tune) else None
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": traffic, "peak_source": f"{pk_kind} cuBLAS bf16 burst", "frac_of_nominal_2250": achieved / 2250.0,
-                    "kernel": {3: "gemm_tcgen05_pair_kernel", 2: "gemm_tcgen05_kernel", 1: "gemm_simt_kernel"}[plan["kernel"]],
-                    "kernel_ms": avg_kernel_ms}
-        # the timed region is back-to-back launches under the power cap: the sustained cuBLAS figure
-        # (seconds-long loop) is the like-for-like companion of the burst one used for `frac`
-        sustained = float(pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
-        roofline["peak_sustained"] = sustained
-        roofline["frac_of_sustained"] = achieved / sustained
+        kernel = KERNEL_NAMES.get(plan["kernel"], str(plan["kernel"]))
+        tflops_launch = flops_local / (avg_kernel_ms * 1e-3) / 1e12
+        gbs_launch = bytes_local / (avg_kernel_ms * 1e-3) / 1e9
+        known = MEASURED_TRAFFIC.get(args.workload if args.workload != "bf16_16384" else "c5")
+        traffic = known[1] if (known and world == 1 and not args.tune and known[0] == plan["kernel"]) else None
+        if w["bound"] == "tensor":
+            peak = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+            sustained = float(pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+            roofline = {"bound": "tensor", "achieved": tflops_launch, "peak": peak, "unit": "TFLOP/s", "frac": tflops_launch / peak,
+                        "traffic": traffic, "peak_source": f"{pk_kind} cuBLAS bf16 burst", "frac_of_nominal_2250": tflops_launch / 2250.0,
+                        "peak_sustained": sustained, "frac_of_sustained": tflops_launch / sustained}
+        else:
+            peak = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+            roofline = {"bound": "hbm", "achieved": gbs_launch, "peak": peak, "unit": "GB/s", "frac": gbs_launch / peak,
+                        "traffic": traffic, "peak_source": f"{pk_kind} HBM copy", "frac_of_nominal_8000": gbs_launch / 8000.0,
+                        "algorithmic_bytes_per_launch": bytes_local, "achieved_tflops": tflops_launch}
+        roofline["kernel"] = kernel
+        roofline["kernel_ms"] = avg_kernel_ms
+        # clock-normalised cost of a step: milliseconds x median SM MHz of the same block (schedule changes show
+        # here even when the power cap moves the clock)
+        for r in repeats:
+            r["tflops"] = flops / (r["ms_per_step"] * 1e-3) / 1e12 * (1 if (w["axis"] or world == 1) else world)
+            r["ms_x_sm_mhz"] = r["ms_per_step"] * r["sm_mhz"] if r["sm_mhz"] else None
+        roofline["kernel_ms_x_sm_mhz"] = repeats[0]["ms_x_sm_mhz"]
+        sharding = "one rank" if world == 1 else (f"{w['axis']} over {world} ranks, no collective" if w["axis"] else f"{world} independent replicas")
         line = {
-            "metric": "GEMM TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-            "config": {"workload": desc, "M": M, "N": N, "K": K, "sharding": f"N over {world} rank(s), no collective",
-                       "l2": "inputs (512 MiB each) larger than the 126 MB L2", "plan": plan},
-            "roofline": roofline,
-            "e2e": e2e,
-            "gpu_launches": int(launches),
-            "gather": gather,
-            "clocks": clocks,
+            "metric": "GEMM TFLOP/s", "value": value if w["axis"] or world == 1 else value * world, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if w["axis"] else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["desc"], "M": w["M"], "N": w["N"], "K": w["K"], "batch": w["batch"], "sharding": sharding,
+                       "l2": ("256 MiB written then 256 MiB read before every timed step (cold, clean L2); per-step events"
+                              if flush is not None else "operands larger than the 126 MB L2, back-to-back steps"),
+                       "plan": plan},
+            "roofline": roofline, "parity": parity, "e2e": e2e, "gpu_launches": int(launches), "gather": gather,
+            "clocks": clocks, "repeats": repeats,
         }
         if world == 1 and not args.no_cpu:
-            tf, cores, sample, _ = cpu_sample(M, N, K, cpu_inputs(N, K), target_s=args.cpu_seconds)
-            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+            line["cpu_baseline"], _ = cpu_baseline(w, args.cpu_seconds)
         emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
 
 
 _RESULT_FD = None
@@ -399,6 +611,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="bf16_16384")
+    ap.add_argument("--repeats", type=int, default=3, help="timed blocks of --steps launches (the first one is the result)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time budget of the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")

@@ -187,7 +187,9 @@ typedef enum {
     srtMatmulKernelSimt    = 1,   /* strided SIMT kernel, fp32 multiply and add in the reference's order */
     srtMatmulKernelTcgen05 = 2,   /* TMA + tcgen05 tensor-core kernel, one CTA per tile */
     srtMatmulKernelTcgen05Pair = 3, /* TMA + tcgen05 cta_group::2 kernel, CTA pair per tile */
-    srtMatmulKernelTcgen05Split = 4 /* Float32 as 3 x TF32 on the tensor cores (hi/lo split in shared memory) */
+    srtMatmulKernelTcgen05Split = 4, /* Float32 as 3 x TF32 on the tensor cores (hi/lo split in shared memory) */
+    srtMatmulKernelTf32x3Pair = 5   /* Float32, CTA pair per tile: one TF32 pass + BFloat16 correction terms; op(a) is
+                                       streamed once, op(b) is pre-split by a pack pass into the workspace */
 } srtMatmulKernel;
 
 typedef struct {
@@ -200,7 +202,7 @@ typedef struct {
     int32_t aMajor, bMajor;/* 0 = K-major, 1 = MN-major operand as the kernel sees it */
     int32_t fp32Split;     /* 1 when fp32 runs as 3 x TF32 on the tensor cores */
     int32_t splitK;        /* > 1: the reduction is cut into this many parts, summed by a second kernel */
-    size_t  workspaceBytes;/* device scratch of a split-K call (fp32 partial sums), else 0 */
+    size_t  workspaceBytes;/* device scratch of the call: fp32 partial sums (split-K) or the pre-split operand (kernel 5), else 0 */
     size_t  dynamicSmemBytes;
 } srtMatmulPlan;
 

@@ -113,6 +113,20 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Low part of an fp32 value for the split-precision kernels: x - hi(x), where hi(x) is x with its low
+// 13 mantissa bits cleared (what a TF32 MMA reads from the word).  Two exceptions keep non-finite
+// inputs on the reference's results: an infinity or NaN is its own low part (so that every term it
+// enters carries it), and a zero low part of a non-zero value is replaced by x 2^-30 -- far below the
+// lo . lo term these kernels drop -- so that infinity times such a value stays an infinity instead of
+// inf . 0 = NaN.  (Values below 2^-96 still lose that tiny stand-in to underflow.)
+__device__ __forceinline__ float tf32_low_part(uint32_t x)
+{
+    const float v = __uint_as_float(x);
+    if ((x & 0x7f800000u) == 0x7f800000u) return v;
+    const float lo = v - __uint_as_float(x & 0xffffe000u);
+    return lo != 0.0f ? lo : v * 9.31322574615478515625e-10f;          // 2^-30
+}
+
 // work unit -> tile coordinates; m-tiles are visited in groups of group_m so that the CTAs running
 // at the same time share A and B tiles in L2.  With split-K, unit u is split u / tiles_total of
 // tile u % tiles_total: it reduces k-blocks [kb0, kb1) and writes partial sums to the slice
@@ -905,15 +919,10 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     uint32_t x0, x1, x2, x3;
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                  : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(hi_base + off));
-                    uint32_t h[4] = {x0 & 0xffffe000u, x1 & 0xffffe000u, x2 & 0xffffe000u, x3 & 0xffffe000u};
                     uint32_t x[4] = {x0, x1, x2, x3};
                     uint32_t l[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float lo = __uint_as_float(x[j]) - __uint_as_float(h[j]);
-                        // infinities and NaNs stay in hi alone
-                        l[j] = ((x[j] & 0x7f800000u) == 0x7f800000u) ? 0u : __float_as_uint(lo);
-                    }
+                    for (int j = 0; j < 4; ++j) l[j] = __float_as_uint(tf32_low_part(x[j]));
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(hi_base + kHalfBytes + off), "r"(l[0]), "r"(l[1]), "r"(l[2]), "r"(l[3]) : "memory");
                 }

@@ -1,0 +1,282 @@
+// Float32 products whose streamed operand is read from HBM exactly once: a CTA-pair kernel
+// (tcgen05 cta_group::2, 256 x 256 tiles) that multiplies
+//     a . b  ~  hi(a) . hi(b)                      one TF32 pass over the raw fp32 tiles
+//             + lo(a) . b16(b) + b16(a) . lo(b)    one BFloat16 pass over "correction" tiles
+// where hi(x) is x with its low 13 mantissa bits cleared (what a TF32 MMA reads from an fp32 word),
+// lo(x) = x - hi(x) (exact, at most 13 significant bits) and b16 is the BFloat16 rounding.  The
+// correction terms are 2^-11 of the product, so 8 significant bits of each factor keep them to
+// 2^-19 of the product, and a BFloat16 MMA costs half a TF32 one: the whole product costs two TF32
+// passes instead of the three of gemm_tcgen05_split_kernel.  The dropped lo . lo term is 2^-22.
+//
+// Operands.  op(a) [M x K] must be K-contiguous; it is streamed by TMA as raw fp32 (the TF32 operand)
+// and four transform warps per CTA write the BFloat16 tile  [ lo(a) | b16(a) ]  (32 + 32 values = one
+// 128-byte swizzled row per A row and k-block) beside it.  op(b) is the small, re-used operand: a
+// pre-pass (tf32x3_pack_kernel) writes it once per call as  Bh = fp32 [N x Kp]  (K-contiguous, zero
+// padded to whole k-blocks) and  Bc = bf16 [N x 2 Kp]  holding  [ b16(b) | lo(b) ]  per k-block, so
+// that both of its tiles arrive by TMA and one K = 64 BFloat16 MMA chain computes both correction
+// terms at once.  Both accumulators (main, corrections) live in TMEM (2 x 256 columns) and are added
+// by the epilogue; keeping the small terms apart matters because the accumulator add truncates.
+//
+//   warp 0      TMA producer (both CTAs): A tile -> own fullA[s]; Bh and Bc half tiles -> the leader's fullB[s]
+//   warp 1      MMA issuer (leader CTA only) and TMEM owner
+//   warps 2-9   epilogue
+//   warps 10-13 transform: fullA[s] -> write [lo | b16] -> arrive on the leader's ready[s] (count 8)
+//   empty[s]    both CTAs, one multicast commit of the leader frees the stage in both
+//
+// Non-finite inputs: lo(x) = x for an infinity or NaN, and a zero low part of a non-zero value is
+// replaced by x 2^-30 (far below the dropped term), so that infinity times a value whose low part
+// vanishes gives the infinity of the reference loop instead of inf . 0 = NaN.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace srt {
+
+constexpr uint32_t kX3TransformWarps = 4;
+constexpr uint32_t kX3Threads = (2 + 8 + kX3TransformWarps) * 32;      // 448
+constexpr uint32_t kX3TileBytes = 128 * kRowBytes;                     // one 128-row, 128-byte-wide tile: 16 KB
+constexpr uint32_t kX3StageBytes = 4 * kX3TileBytes;                   // A raw, A corrections, Bh half, Bc half
+constexpr uint32_t kX3MaxStages = 3;
+
+struct PackParams {
+    const float* b;                 // op(b) element (n, k) at b + batch b_b + n b_n + k b_k
+    long long b_b, b_n, b_k;
+    float* bh;                      // [batch][N][Kp]
+    __nv_bfloat16* bc;              // [batch][N][2 Kp]
+    uint32_t N, K, Kp, batch;
+};
+
+// One thread per (n, 4 consecutive k): reads along whichever of n, k is contiguous in memory.
+__global__ void __launch_bounds__(256)
+tf32x3_pack_kernel(const PackParams p)
+{
+    launch_dependents();          // the product kernel may start its prologue; it waits before reading Bh / Bc
+    const uint32_t kq = p.Kp / 4;
+    const unsigned long long total = static_cast<unsigned long long>(p.batch) * p.N * kq;
+    const bool k_fast = p.b_k == 1 || p.b_n != 1;
+    for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total; i += gridDim.x * 256ull) {
+        uint32_t n, q, bt;
+        if (k_fast) { q = static_cast<uint32_t>(i % kq); n = static_cast<uint32_t>((i / kq) % p.N); bt = static_cast<uint32_t>(i / (static_cast<unsigned long long>(kq) * p.N)); }
+        else        { n = static_cast<uint32_t>(i % p.N); q = static_cast<uint32_t>((i / p.N) % kq); bt = static_cast<uint32_t>(i / (static_cast<unsigned long long>(kq) * p.N)); }
+        const uint32_t k0 = q * 4;
+        float v[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[j] = (k0 + j < p.K) ? p.b[bt * p.b_b + static_cast<long long>(n) * p.b_n + static_cast<long long>(k0 + j) * p.b_k] : 0.0f;
+            lo[j] = tf32_low_part(__float_as_uint(v[j]));
+        }
+        const unsigned long long row = static_cast<unsigned long long>(bt) * p.N + n;
+        *reinterpret_cast<float4*>(p.bh + row * p.Kp + k0) = make_float4(v[0], v[1], v[2], v[3]);
+        // k-block kb of the row: [ b16(b) x 32 | lo(b) x 32 ]
+        const uint32_t kb = k0 / 32, within = k0 % 32;
+        __nv_bfloat16* dst = p.bc + row * (2ull * p.Kp) + kb * 64ull + within;
+        uint2 hi2, lo2;
+        hi2.x = pack2<__nv_bfloat16>(v[0], v[1]); hi2.y = pack2<__nv_bfloat16>(v[2], v[3]);
+        lo2.x = pack2<__nv_bfloat16>(lo[0], lo[1]); lo2.y = pack2<__nv_bfloat16>(lo[2], lo[3]);
+        *reinterpret_cast<uint2*>(dst) = hi2;
+        *reinterpret_cast<uint2*>(dst + 32) = lo2;
+    }
+}
+
+struct X3Params {
+    GemmParams g;                 // sizes, tile walk, A descriptor fields, epilogue
+    uint32_t idesc_tf32, idesc_bf16;
+    uint32_t l2_prefetch;         // k-blocks of A to prefetch into L2 ahead of the loads (0 = none)
+};
+
+__global__ void __launch_bounds__(kX3Threads, 1)
+gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_bh,
+                        const __grid_constant__ CUtensorMap tmap_bc,
+                        const __grid_constant__ CUtensorMap tmap_out,
+                        const __grid_constant__ X3Params xp)
+{
+    const GemmParams& p = xp.g;
+    constexpr uint32_t BN = 256;
+    constexpr uint32_t kTmemCols = 512;             // main accumulator [0, 256), corrections [256, 512)
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    __shared__ __align__(8) uint64_t full_a[kX3MaxStages];       // own A tile landed
+    __shared__ __align__(8) uint64_t full_b[kX3MaxStages];       // leader: both CTAs' Bh and Bc tiles landed
+    __shared__ __align__(8) uint64_t ready[kX3MaxStages];        // leader: both CTAs' correction tiles written
+    __shared__ __align__(8) uint64_t empty_bar[kX3MaxStages];    // both: the stage's MMAs have completed
+    __shared__ __align__(8) uint64_t tmem_full_bar;
+    __shared__ __align__(8) uint64_t tmem_empty_bar;             // leader, count 16
+    __shared__ uint32_t tmem_holder;
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t stages = p.stages;
+    const uint32_t cta_rank = cluster_ctarank();
+    const uint32_t pair_id = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_a[s]), 1);
+            mbar_init(smem_u32(&full_b[s]), 1);
+            mbar_init(smem_u32(&ready[s]), 2 * kX3TransformWarps);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&tmem_full_bar), 1);
+        mbar_init(smem_u32(&tmem_empty_bar), 16);
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_bh);
+        prefetch_tensormap(&tmap_bc);
+        if (p.out_tma) prefetch_tensormap(&tmap_out);
+    }
+    if (warp == 1) {
+        tmem_alloc_cta2(smem_u32(&tmem_holder), kTmemCols);
+        tmem_relinquish_cta2();
+    }
+    tc_fence_before_sync();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    // an abort is raised in both CTAs of the pair, so that the partner's waits end at once too
+    auto raise_abort = [&](uint32_t code) {
+        abort_flag = 1;
+        st_shared_remote_u32(smem_u32(const_cast<uint32_t*>(&abort_flag)), cta_rank ^ 1u, 1u);
+        atomicOr(&g_gemm_status, code);
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            grid_dependency_wait();                  // Bh / Bc come from the pack kernel launched just before
+            for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+                const TileCoord tc = decode_tile(p, tile, BN);
+                const uint32_t batch = tc.batch;
+                const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM;          // decode_tile counts 128-row units
+                const uint32_t n0 = tc.n0 + cta_rank * (BN / 2);
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * kX3StageBytes;
+                    const uint32_t sbh = sa + 2 * kX3TileBytes, sbc = sa + 3 * kX3TileBytes;
+                    const uint32_t bar_a = smem_u32(&full_a[stage]);
+                    const uint32_t bar_b = map_to_cta(smem_u32(&full_b[stage]), 0);
+                    mbar_arrive_expect_tx(bar_a, kX3TileBytes);
+                    if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_b[stage]), 4 * kX3TileBytes);
+                    tma_load_3d(sa, &tmap_a, bar_a, static_cast<int32_t>(kb * 32), m0, batch * p.a.batch_mul);
+                    tma_load_3d_pair(sbh, &tmap_bh, bar_b, static_cast<int32_t>(kb * 32), n0, batch * p.b.batch_mul);
+                    tma_load_3d_pair(sbc, &tmap_bc, bar_b, static_cast<int32_t>(kb * 64), n0, batch * p.b.batch_mul);
+                    if (xp.l2_prefetch && kb + xp.l2_prefetch < tc.kb1)
+                        tma_prefetch_l2_3d(&tmap_a, static_cast<int32_t>((kb + xp.l2_prefetch) * 32), m0, batch * p.a.batch_mul);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) raise_abort(kStatusProducerTimeout);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA)
+        if (cta_rank == 0 && elect_one()) {
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool ok = true;
+            const uint64_t hi64 = static_cast<uint64_t>(p.a.desc_hi) << 32;     // K-major, 128-byte swizzle: every tile alike
+            const uint32_t d_main = tmem_base, d_corr = tmem_base + BN;
+            for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
+                if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar), (local & 1) ^ 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const TileCoord tc = decode_tile(p, tile, BN);
+                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&full_b[stage]), phase, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_cluster(smem_u32(&ready[stage]), phase, &abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_base + stage * kX3StageBytes;
+                    const uint32_t a_raw = ((sa >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t a_cor = (((sa + kX3TileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t b_raw = (((sa + 2 * kX3TileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t b_cor = (((sa + 3 * kX3TileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t first = (kb != tc.kb0);
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k)          // 32 fp32 of K: four TF32 MMAs of K = 8 (32 bytes each)
+                        umma_tf32_cta2(d_main, hi64 | (a_raw + k * 2), hi64 | (b_raw + k * 2), xp.idesc_tf32, first | k);
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k)          // 64 bf16 of K: four BFloat16 MMAs of K = 16 (32 bytes each)
+                        umma_f16_cta2(d_corr, hi64 | (a_cor + k * 2), hi64 | (b_cor + k * 2), xp.idesc_bf16, first | k);
+                    umma_commit_cta2_mc(smem_u32(&empty_bar[stage]), 3);
+                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit_cta2_mc(smem_u32(&tmem_full_bar), 3);
+            }
+            if (!ok) raise_abort(kStatusMmaTimeout);
+        }
+    } else if (warp < 10) {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const uint32_t quarter = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
+            const TileCoord tc = decode_tile(p, tile, BN);
+            const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM;
+            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar), local & 1, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            drain_accumulator<float, BN, true, 2>(p, &tmap_out, smem_base + stages * kX3StageBytes + (warp - 2) * 4096, (warp - 2) >> 2,
+                                                  tmem_base, quarter, lane, tc.obatch, m0, tc.n0, tmem_base + BN);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar), 0);
+        }
+        drain_finish(lane);
+        if (!ok && lane == 0) raise_abort(kStatusEpilogueTimeout);
+    } else {
+        // ------------------------------------------------------------------ transform (both CTAs): row t of the A tile
+        const uint32_t row = threadIdx.x - 10 * 32;                 // 0 .. 127
+        const uint32_t sw = row & 7;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+            const TileCoord tc = decode_tile(p, tile, BN);
+            for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
+                if (!mbar_wait(smem_u32(&full_a[stage]), phase, &abort_flag)) { ok = false; break; }
+                const uint32_t src = smem_base + stage * kX3StageBytes + row * 128;
+                const uint32_t dst = src + kX3TileBytes;
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {              // 8 fp32 (two 16-byte chunks) -> one chunk of lo, one of b16
+                    uint32_t x[8];
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(src + (((2 * j) ^ sw) << 4)));
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]) : "r"(src + (((2 * j + 1) ^ sw) << 4)));
+                    uint32_t lo[4], hi[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        lo[e] = pack2<__nv_bfloat16>(tf32_low_part(x[2 * e]), tf32_low_part(x[2 * e + 1]));
+                        hi[e] = pack2<__nv_bfloat16>(__uint_as_float(x[2 * e]), __uint_as_float(x[2 * e + 1]));
+                    }
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst + ((j ^ sw) << 4)), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst + (((4 + j) ^ sw) << 4)), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
+                }
+                fence_proxy_async_smem();          // generic-proxy writes -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(smem_u32(&ready[stage]), 0);
+                if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (!ok && lane == 0) raise_abort(kStatusPairTimeout);
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        if (abort_flag != 0) __nanosleep(1000000);
+        tmem_dealloc_cta2(tmem_base, kTmemCols);
+    }
+    cluster_arrive_release();
+    cluster_wait_acquire();
+}
+
+}  // namespace srt

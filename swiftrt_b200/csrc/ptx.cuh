@@ -216,6 +216,23 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_
     return r;
 }
 
+// a 32-bit store into the shared memory of CTA `cta_rank` of the cluster, at this CTA's offset `smem_addr`
+__device__ __forceinline__ void st_shared_remote_u32(uint32_t smem_addr, uint32_t cta_rank, uint32_t value)
+{
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+        "st.shared::cluster.u32 [remote], %2;\n\t}"
+        ::"r"(smem_addr), "r"(cta_rank), "r"(value) : "memory");
+}
+
+// L2 prefetch of a tile a later tma_load_3d will fetch (no shared-memory destination, no barrier)
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
 // ----------------------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc_cta1(uint32_t holder_smem, uint32_t ncols)
 {

@@ -19,6 +19,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_splitk.cuh"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tf32x3.cuh"
 #include "lstm_cell.cuh"
 
 namespace {
@@ -49,7 +50,9 @@ cudaError_t fail(cudaError_t code, const char* fmt, ...)
 // resolves the stream's device, makes it current for the duration of the call when it differs and
 // restores the caller's device afterwards; per-device state (workspaces, kernel attributes, the
 // status word, the static scratch) is keyed by `device`.  The legacy and per-thread default
-// streams belong to whatever device is current.
+// streams belong to whatever device is current.  While a stream is being captured the runtime
+// refuses the device query (and a refused call would invalidate the capture), so a capturing
+// stream is taken to belong to the current device: capture with the stream's device current.
 struct DeviceScope {
     int device = -1;
     int previous = -1;
@@ -60,7 +63,9 @@ struct DeviceScope {
         status = cudaGetDevice(&cur);
         if (status != cudaSuccess) return;
         int dev = cur;
-        if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread &&
+            cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
             status = cudaStreamGetDevice(stream, &dev);
             if (status != cudaSuccess) {
                 fail(status, "cannot resolve the device of the stream: %s", cudaGetErrorString(status));
@@ -401,6 +406,41 @@ bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool sk
     // tiny problems are launch-bound either way; keep them on the exact kernel
     if (tc && force == 0 && Q.M * Q.N * Q.K * Q.batch < (1ull << 18)) tc = false;
 
+    // Float32 with a streamed, K-contiguous op(a) and a smaller op(b): the CTA-pair kernel that reads
+    // op(a) once, multiplies TF32 + BFloat16 corrections and takes op(b) pre-split from a pack pass
+    // (gemm_tf32x3.cuh).  K <= 2048 for the same accuracy reason as below; longer reductions go
+    // through split-K on the one-CTA kernel.
+    if (tc && split && !skinny_swap && (force == 0 || force == srtMatmulKernelTf32x3Pair) && !plan.ta.mn_major &&
+        Q.K <= 2048 && Q.K >= 32 && Q.M >= Q.N && Q.N > 128 && Q.M >= 512 && choice.split_k <= 1 &&
+        (force == srtMatmulKernelTf32x3Pair || Q.M * Q.N * Q.K * Q.batch >= (1ull << 28))) {
+        const uint64_t kp = (Q.K + 31) / 32 * 32;
+        const uint64_t b_items = (Q.batch == 1 || Q.b_b == 0) ? 1 : Q.batch;
+        const uint64_t pack_bytes = b_items * ((Q.N + 127) / 128 * 128) * kp * 8;
+        if (pack_bytes <= (256ull << 20)) {
+            plan.Q = Q;
+            uint32_t stages = (uint32_t)choice.stages;
+            if (stages < 2 || stages > kX3MaxStages) stages = kX3MaxStages;
+            const uint64_t tiles = ((Q.M + 255) / 256) * ((Q.N + 255) / 256) * Q.batch;
+            const uint64_t pairs = (uint64_t)dev.sms / 2;
+            uint32_t ctas = 2u * (uint32_t)(tiles < pairs ? tiles : pairs);
+            if (choice.max_ctas > 1 && ctas > (uint32_t)choice.max_ctas) ctas = (uint32_t)choice.max_ctas & ~1u;
+            plan.splits = 1;
+            plan.kb_per_split = (uint32_t)(kp / 32);
+            plan.pub.kernel = srtMatmulKernelTf32x3Pair;
+            plan.pub.tileM = 256; plan.pub.tileN = 256; plan.pub.tileK = 32;
+            plan.pub.stages = (int32_t)stages;
+            plan.pub.ctas = (int32_t)ctas;
+            plan.pub.tiles = (int32_t)tiles;
+            plan.pub.swapped = plan.swapped;
+            plan.pub.aMajor = 0; plan.pub.bMajor = 0;
+            plan.pub.fp32Split = 1;
+            plan.pub.splitK = 1;
+            plan.pub.workspaceBytes = (size_t)pack_bytes;
+            plan.pub.dynamicSmemBytes = (size_t)stages * kX3StageBytes + kEpilogueStagingBytes + 1024;
+            return true;
+        }
+    }
+
     if (!tc) {
         plan.Q = P;
         plan.swapped = false;
@@ -738,6 +778,10 @@ struct Prepared {
     void* ws_bound = nullptr;        // workspace the output tensor map and gp.out currently point at
     bool static_scratch = false;     // split-K partial sums go to the library's static array (srtMatmulNoAlloc)
     ReduceParams rp;
+    // TF32 + BFloat16-correction pair kernel only: the packed op(b) lives in the workspace
+    CUtensorMap mbc;
+    X3Params xp;
+    PackParams pk;
     uint32_t reduce_vec = 1, reduce_blocks = 0;
 };
 
@@ -857,6 +901,139 @@ cudaError_t bind_workspace(Prepared& pr, void* ws)
     }
     pr.ws_bound = ws;
     return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ TF32 + BFloat16-correction pair kernel
+cudaError_t prepare_x3(const Plan& plan, Prepared& pr)
+{
+    const Problem& Q = plan.Q;
+    X3Params& xp = pr.xp;
+    memset(&xp, 0, sizeof xp);
+    GemmParams& gp = xp.g;
+    cudaError_t e = encode_operand(&pr.ma, Q, Q.a, plan.ta, Q.M, Q.a_b, kTileM, gp.a);
+    if (e != cudaSuccess) return e;
+    gp.b = gp.a;                                          // the packed op(b) is K-contiguous too
+    gp.b.batch_mul = (Q.batch == 1 || Q.b_b == 0) ? 0 : 1;
+    gp.M = (uint32_t)Q.M; gp.N = (uint32_t)Q.N; gp.K = (uint32_t)Q.K; gp.batch = (uint32_t)Q.batch;
+    gp.tiles_m = (uint32_t)((Q.M + 255) / 256);
+    gp.tiles_n = (uint32_t)((Q.N + 255) / 256);
+    gp.tiles_per_batch = gp.tiles_m * gp.tiles_n;
+    gp.tiles_total = (uint32_t)plan.pub.tiles;
+    gp.k_splits = 1;
+    gp.num_tiles = gp.tiles_total;
+    gp.kb_elems = 32;
+    gp.k_blocks = (uint32_t)((Q.K + 31) / 32);
+    gp.kb_per_split = gp.k_blocks;
+    gp.group_m = 8;
+    gp.stages = (uint32_t)plan.pub.stages;
+    gp.stage_tx_bytes = 0;
+    // instruction descriptors: fp32 accumulator, both operands K-major, N = 256, M = 256
+    const uint32_t shape = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+    xp.idesc_tf32 = shape | (2u << 7) | (2u << 10);
+    xp.idesc_bf16 = shape | (1u << 7) | (1u << 10);
+    xp.l2_prefetch = 0;
+    if (const char* dbg = getenv("SRT_DEV_X3_PREFETCH")) xp.l2_prefetch = (uint32_t)atoi(dbg);   // DEV-ONLY, to be removed
+    gp.out = Q.out;
+    gp.ldo = Q.N == 1 ? (Q.M == 1 ? 1 : Q.o_m) : (Q.M == 1 ? (long long)Q.N : Q.o_m);
+    gp.out_batch_stride = Q.o_b;
+    gp.bias = Q.bias;
+    gp.bias_stride = Q.bias_stride;
+    gp.bias_mode = plan.bias_mode;
+    gp.act = Q.act;
+    gp.out_vec_ok = (reinterpret_cast<uintptr_t>(Q.out) % 16 == 0) && ((gp.ldo * (long long)Q.elem) % 16 == 0) &&
+                    ((Q.o_b * (long long)Q.elem) % 16 == 0) && (Q.N > 1 ? Q.o_n == 1 : true);
+    gp.out_tma = 0;
+    memset(&pr.mo, 0, sizeof pr.mo);
+    if (gp.out_vec_ok && Q.N > 1 && encode_out_map(&pr.mo, Q, gp.ldo, Q.out)) gp.out_tma = 1;
+    PackParams& pk = pr.pk;
+    memset(&pk, 0, sizeof pk);
+    pk.b = reinterpret_cast<const float*>(Q.b);
+    pk.b_b = gp.b.batch_mul ? Q.b_b : 0; pk.b_n = Q.b_n; pk.b_k = Q.b_k;
+    pk.N = (uint32_t)Q.N; pk.K = (uint32_t)Q.K; pk.Kp = gp.k_blocks * 32; pk.batch = gp.b.batch_mul ? (uint32_t)Q.batch : 1u;
+    pr.kernel = srtMatmulKernelTf32x3Pair;
+    pr.type = Q.type;
+    pr.bn = 256;
+    pr.smem = plan.pub.dynamicSmemBytes;
+    pr.ctas = (uint32_t)plan.pub.ctas;
+    pr.splits = 1;
+    pr.ws_bytes = plan.pub.workspaceBytes;
+    pr.ws_bound = nullptr;
+    pr.static_scratch = false;
+    return cudaSuccess;
+}
+
+// Points the pack pass and the tensor maps of the packed op(b) at the workspace: Bh = fp32 [items][N][Kp],
+// then Bc = bf16 [items][N][2 Kp].  Rows beyond N are never written: the maps end at N and TMA zero-fills.
+cudaError_t bind_pack(Prepared& pr, void* ws)
+{
+    PackParams& pk = pr.pk;
+    const uint64_t rows = (uint64_t)pk.batch * pk.N;
+    pk.bh = static_cast<float*>(ws);
+    pk.bc = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + rows * pk.Kp * 4);
+    {
+        cuuint64_t gdim[3] = {pk.Kp, pk.N, pk.batch};
+        cuuint64_t gstride[2] = {(cuuint64_t)pk.Kp * 4, (cuuint64_t)pk.Kp * 4 * pk.N};
+        cuuint32_t box[3] = {32, 128, 1}, estr[3] = {1, 1, 1};
+        if (g_encode(&pr.mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pk.bh, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed for the packed fp32 operand");
+    }
+    {
+        cuuint64_t gdim[3] = {2ull * pk.Kp, pk.N, pk.batch};
+        cuuint64_t gstride[2] = {(cuuint64_t)pk.Kp * 4, (cuuint64_t)pk.Kp * 4 * pk.N};
+        cuuint32_t box[3] = {64, 128, 1}, estr[3] = {1, 1, 1};
+        if (g_encode(&pr.mbc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, pk.bc, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed for the packed correction operand");
+    }
+    pr.ws_bound = ws;
+    return cudaSuccess;
+}
+
+cudaError_t launch_x3(const Prepared& pr, cudaStream_t stream)
+{
+    auto kernel = gemm_tf32x3_pair_kernel;
+    static std::atomic<uint64_t> attr_done{0};
+    static std::atomic<int> cluster_cache[64];
+    cudaError_t e = ensure_smem_attr(kernel, attr_done, pr.smem);
+    if (e != cudaSuccess) return e;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    const PackParams& pk = pr.pk;
+    const unsigned long long items = (unsigned long long)pk.batch * pk.N * (pk.Kp / 4);
+    unsigned long long blocks = (items + 255) / 256;
+    if (blocks > 148ull * 8) blocks = 148ull * 8;
+    tf32x3_pack_kernel<<<(unsigned)blocks, 256, 0, stream>>>(pk);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(pr.ctas, 1, 1);
+    cfg.blockDim = dim3(kX3Threads, 1, 1);
+    cfg.dynamicSmemBytes = pr.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    // scheduled while the pack pass still runs; the producer waits (griddepcontrol.wait) before its first load
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    int max_clusters = cluster_cache[dev & 63].load(std::memory_order_acquire);
+    if (max_clusters == 0) {
+        cudaLaunchConfig_t q = cfg;
+        q.numAttrs = 1;
+        q.dynamicSmemBytes = 227 * 1024 - 1024;
+        e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &q);
+        if (e != cudaSuccess) return e;
+        if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
+        cluster_cache[dev & 63].store(max_clusters, std::memory_order_release);
+    }
+    if (pr.ctas / 2 > (uint32_t)max_clusters) cfg.gridDim.x = 2u * (uint32_t)max_clusters;
+    return cudaLaunchKernelEx(&cfg, kernel, pr.ma, pr.mb, pr.mbc, pr.mo, pr.xp);
 }
 
 // Workspaces of split-K launches: one buffer per (device, stream), grown on demand.  Kernels of
@@ -1031,7 +1208,7 @@ cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
 {
     cudaError_t e;
     const uint32_t bn = pr.bn;
-    if (pr.splits > 1) {
+    if (pr.ws_bytes > 0) {
         int dev = 0;
         e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
@@ -1039,11 +1216,14 @@ cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
         e = pr.static_scratch ? no_alloc_scratch(dev, &ws) : workspace_for(dev, stream, pr.ws_bytes, &ws);
         if (e != cudaSuccess) return e;
         if (ws != pr.ws_bound) {
-            e = bind_workspace(pr, ws);
+            e = pr.kernel == srtMatmulKernelTf32x3Pair ? bind_pack(pr, ws) : bind_workspace(pr, ws);
             if (e != cudaSuccess) return e;
         }
     }
     switch (pr.kernel) {
+    case srtMatmulKernelTf32x3Pair:
+        e = launch_x3(pr, stream);
+        break;
     case srtMatmulKernelSimt:
         switch (pr.type) {
         case real32F:
@@ -1096,6 +1276,15 @@ cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
         if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
     }
     return e;
+}
+
+cudaError_t prepare_any(const Plan& plan, Prepared& pr)
+{
+    switch (plan.pub.kernel) {
+    case srtMatmulKernelSimt: return prepare_simt(plan, pr);
+    case srtMatmulKernelTf32x3Pair: return prepare_x3(plan, pr);
+    default: return prepare_tc(plan, pr);
+    }
 }
 
 // ------------------------------------------------------------------ call cache
@@ -1207,7 +1396,7 @@ int plan_table_load(const char* path)
         if (sscanf(line, "%d %u %llu %llu %llu %llu %d %d %d %d %d %f", &k.type, &k.flags, &M, &N, &K, &batch, &c.force, &c.tile_n,
                    &c.stages, &c.max_ctas, &c.split_k, &us) != 12)
             continue;
-        if (c.force < 0 || c.force > srtMatmulKernelTcgen05Split) continue;
+        if (c.force < 0 || c.force > srtMatmulKernelTf32x3Pair) continue;
         k.M = M; k.N = N; k.K = K; k.batch = batch;
         plan_store(k, c, us);
         ++loaded;
@@ -1334,17 +1523,23 @@ cudaError_t run_matmul(const void* a, const srtTensorDescriptor* aDesc, bool tra
     Plan plan;
     e = plan_for(P, plan);
     if (e != cudaSuccess) return e;
-    if (no_alloc && plan.splits > 1 && plan.pub.workspaceBytes > kNoAllocScratchBytes)
+    if (no_alloc && plan.pub.workspaceBytes > kNoAllocScratchBytes) {
+        if (plan.splits > 1)
+            return fail(cudaErrorInvalidValue,
+                        "srtMatmulNoAlloc: this product needs %zu bytes of scratch (%u partial results of %llu x %llu x %llu "
+                        "fp32 values) but the static scratch holds %zu; use srtMatmul, or srtMatmulSetSplitK(1)",
+                        (size_t)plan.pub.workspaceBytes, plan.splits, (unsigned long long)plan.Q.batch,
+                        (unsigned long long)plan.Q.M, (unsigned long long)plan.Q.N, kNoAllocScratchBytes);
         return fail(cudaErrorInvalidValue,
-                    "srtMatmulNoAlloc: this product needs %zu bytes of scratch (%u partial results of %llu x %llu x %llu "
-                    "fp32 values) but the static scratch holds %zu; use srtMatmul, or srtMatmulSetSplitK(1)",
-                    (size_t)plan.pub.workspaceBytes, plan.splits, (unsigned long long)plan.Q.batch,
-                    (unsigned long long)plan.Q.M, (unsigned long long)plan.Q.N, kNoAllocScratchBytes);
+                    "srtMatmulNoAlloc: this product needs %zu bytes of scratch (the pre-split copy of its %llu x %llu operand) but the "
+                    "static scratch holds %zu; use srtMatmul, or srtMatmulSetTuning(srtMatmulKernelTcgen05Split, 0, 0, 0)",
+                    (size_t)plan.pub.workspaceBytes, (unsigned long long)plan.Q.N, (unsigned long long)plan.Q.K, kNoAllocScratchBytes);
+    }
     Prepared& pr = t_cache->value[slot];
     t_cache->valid[slot] = false;
-    e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, pr) : prepare_tc(plan, pr);
+    e = prepare_any(plan, pr);
     if (e != cudaSuccess) return e;
-    pr.static_scratch = no_alloc && pr.splits > 1;
+    pr.static_scratch = no_alloc && pr.ws_bytes > 0;
     e = launch_prepared(pr, stream);
     if (e == cudaSuccess) {
         t_cache->key[slot] = key;
@@ -1392,7 +1587,7 @@ cudaError_t srtMatmulQueryPlan(const void* a, const srtTensorDescriptor* aDesc, 
 
 cudaError_t srtMatmulSetTuning(int32_t forceKernel, int32_t tileN, int32_t stages, int32_t maxCtas)
 {
-    if (forceKernel < 0 || forceKernel > srtMatmulKernelTcgen05Split) return fail(cudaErrorInvalidValue, "unknown kernel id");
+    if (forceKernel < 0 || forceKernel > srtMatmulKernelTf32x3Pair) return fail(cudaErrorInvalidValue, "unknown kernel id");
     if (tileN != 0 && tileN != 64 && tileN != 128 && tileN != 256) return fail(cudaErrorInvalidValue, "tileN must be 0, 64, 128 or 256");
     if (stages != 0 && (stages < 2 || stages > 8)) return fail(cudaErrorInvalidValue, "stages must be 0 or 2..8");
     if (maxCtas < 0) return fail(cudaErrorInvalidValue, "maxCtas must be >= 0");
@@ -1428,6 +1623,7 @@ cudaError_t srtMatmulTune(const void* a, const srtTensorDescriptor* aDesc, bool 
     if (P.type == real32F) {
         cands.push_back(Choice{srtMatmulKernelSimt, 0, 0, 0, 0});
         for (int32_t tn : {64, 128, 256}) cands.push_back(Choice{srtMatmulKernelTcgen05Split, tn, 0, 0, 0});
+        cands.push_back(Choice{srtMatmulKernelTf32x3Pair, 0, 0, 0, 0});
     } else {
         for (int32_t tn : {64, 128, 256}) {
             cands.push_back(Choice{srtMatmulKernelTcgen05, tn, 0, 0, 0});
@@ -1456,7 +1652,7 @@ cudaError_t srtMatmulTune(const void* a, const srtTensorDescriptor* aDesc, bool 
         for (const srtMatmulPlan& s : seen) dup = dup || memcmp(&s, &plan.pub, sizeof s) == 0;
         if (dup) continue;
         seen.push_back(plan.pub);
-        e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, *pr) : prepare_tc(plan, *pr);
+        e = prepare_any(plan, *pr);
         if (e != cudaSuccess) break;
         float us = 0.0f;
         e = time_prepared(*pr, stream, e0, e1, us);
@@ -2223,7 +2419,7 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
         Plan plan;
         e = plan_for(P, plan);
         if (e != cudaSuccess) return e;
-        e = plan.pub.kernel == srtMatmulKernelSimt ? prepare_simt(plan, ent.pr) : prepare_tc(plan, ent.pr);
+        e = prepare_any(plan, ent.pr);
         if (e != cudaSuccess) return e;
         ent.fused = (plan.pub.kernel == srtMatmulKernelTcgen05Pair || plan.pub.kernel == srtMatmulKernelTcgen05) &&
                     ent.pr.splits <= 1 && ent.pr.gp.out_tma;

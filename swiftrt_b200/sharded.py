@@ -145,3 +145,120 @@ def sharded_matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = 
         if r_hi > r_lo:
             full.narrow(dim, r_lo, r_hi - r_lo).copy_(staging[r].narrow(dim, 0, r_hi - r_lo))
     return full
+
+
+_HOST_STREAMS: dict = {}
+
+
+class _InlineStream:
+    """Stands in for a CUDA stream on CPU ranks (the gloo tests): everything runs in program order."""
+
+    def wait_stream(self, other):
+        pass
+
+    def wait_event(self, event):
+        pass
+
+    def record_event(self):
+        return None
+
+    def synchronize(self):
+        pass
+
+
+def _on(stream):
+    import contextlib
+    return contextlib.nullcontext() if isinstance(stream, _InlineStream) else torch.cuda.stream(stream)
+
+
+def _host_streams(dev: torch.device):
+    """(main, copy-in, all-gather, copy-out) streams of a device; the side streams are created once."""
+    if dev.type != "cuda":
+        return _InlineStream(), _InlineStream(), _InlineStream(), _InlineStream()
+    key = (dev.type, dev.index)
+    if key not in _HOST_STREAMS:
+        _HOST_STREAMS[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return (torch.cuda.current_stream(dev),) + _HOST_STREAMS[key]
+
+
+def sharded_matmul_host(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = False, transposed_rhs: bool = False,
+                        axis: str = "n", bias: Optional[torch.Tensor] = None, activation=None,
+                        out_host: Optional[torch.Tensor] = None, device=None, group=None, pieces: int = 4,
+                        rank: Optional[int] = None, world: Optional[int] = None,
+                        matmul_into_fn: Optional[Callable] = None, matmul_host_fn: Optional[Callable] = None) -> torch.Tensor:
+    """sharded_matmul for HOST tensors, one process per GPU: every rank passes only ITS OWN share of
+    the host data and receives its block of the result in host memory, so that each operand byte
+    crosses PCIe once whatever the number of GPUs (the reference migrates whole replicas on
+    deviceRead, Sources/SwiftRTCore/tensor/DiscreteStorage.swift:310-381).
+
+      axis "batch"  lhs, rhs: this rank's batch items          -> its batch items of the result
+      axis "m"      lhs: this rank's rows, rhs: all of it       -> its rows of the result
+      axis "n"      lhs: this rank's ROW block [M / world x K] of the operand every rank needs,
+                    rhs: this rank's column block [K x n_local] -> its column block [M x n_local]
+
+    For axis "n" the row blocks of lhs are all-gathered over NVLink (NCCL) into every rank's device
+    copy, piece by piece: the copy-in of piece p + 1, the all-gather of piece p, the product of the
+    rows already gathered and the copy-out of finished rows overlap.  The product kernel reads local
+    HBM only.  Row blocks must be equal on all ranks; lhs rank 2, not transposed."""
+    if axis not in AXES:
+        raise ValueError(f"axis must be one of {AXES}")
+    if world is None:
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if rank is None:
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if matmul_host_fn is None:
+        from .matmul import matmul_host as matmul_host_fn
+    dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    on_gpu = dev.type == "cuda"
+    if axis != "n" or world == 1:
+        return matmul_host_fn(lhs, rhs, transposed_lhs, transposed_rhs, bias=bias, activation=activation, device=dev,
+                              out_host=out_host)
+    if lhs.dim() != 2 or rhs.dim() != 2 or transposed_lhs:
+        raise ValueError("axis 'n' with host buffers takes a rank-2, untransposed lhs row block")
+    if matmul_into_fn is None:
+        from .matmul import matmul_into as matmul_into_fn
+    mb, k = lhs.shape
+    n_local = rhs.shape[0] if transposed_rhs else rhs.shape[1]
+    m = mb * world
+    if out_host is None:
+        out_host = torch.empty((m, n_local), dtype=lhs.dtype, pin_memory=on_gpu)
+    pieces = max(1, min(pieces, mb))
+    step = -(-mb // pieces)
+    step = min(mb, -(-step // 128) * 128)                     # whole tiles per piece
+    import contextlib
+    main, s_in, s_ag, s_out = _host_streams(dev)
+    for s in (s_in, s_ag, s_out):
+        s.wait_stream(main)
+    with (torch.cuda.device(dev) if on_gpu else contextlib.nullcontext()):
+        with _on(s_in):
+            b = rhs.to(dev, non_blocking=True)
+            bz = bias.to(dev, non_blocking=True) if bias is not None else None
+            b_ready = s_in.record_event()
+        c = torch.empty((world, mb, n_local), dtype=lhs.dtype, device=dev)
+        keep = [b, c] + ([bz] if bz is not None else [])
+        main.wait_event(b_ready)
+        for r0 in range(0, mb, step):
+            r1 = min(mb, r0 + step)
+            g = torch.empty((world, r1 - r0, k), dtype=lhs.dtype, device=dev)     # rows [r0, r1) of every rank's block
+            keep.append(g)
+            with _on(s_in):
+                g[rank].copy_(lhs[r0:r1], non_blocking=True)
+                arrived = s_in.record_event()
+            with _on(s_ag):
+                s_ag.wait_event(arrived)
+                dist.all_gather_into_tensor(g.view(world * (r1 - r0), k), g[rank], group=group)
+                gathered = s_ag.record_event()
+            main.wait_event(gathered)
+            # one batched product: item r = the rows of rank r's block, against this rank's columns
+            matmul_into_fn(c[:, r0:r1], g, False, b, transposed_rhs, bz, activation)
+            done = main.record_event()
+            with _on(s_out):
+                s_out.wait_event(done)
+                for r in range(world):
+                    out_host[r * mb + r0:r * mb + r1].copy_(c[r, r0:r1], non_blocking=True)
+        if on_gpu:
+            for t in keep:
+                for s in (main, s_in, s_ag, s_out):
+                    t.record_stream(s)
+    s_out.synchronize()
+    return out_host

@@ -215,12 +215,95 @@ def test_float32_3xtf32_epilogue_and_special_values(srt, oracle):
     assert oracle.rel_frobenius(got[fin], ref[fin]) <= TOL[F32]
 
 
+X3 = 5      # srtMatmulKernelTf32x3Pair
+
+
+@pytest.mark.parametrize("M,N,K,batch,tb,col_out", [
+    (512, 256, 1024, 0, False, False),        # whole tiles
+    (4096, 256, 256, 0, False, False),        # more tiles than CTA pairs: the persistent loop and its phases
+    (1000, 200, 100, 0, False, False),        # ragged M, N and K (K not a multiple of a k-block: zero filled)
+    (1536, 384, 2048, 0, True, False),        # two column tiles, K-contiguous op(b), the longest allowed reduction
+    (640, 136, 72, 3, False, False),          # batched
+    (640, 136, 72, 3, True, False),
+    (768, 264, 512, 0, False, True),          # column-order result: planned as the transposed problem
+])
+def test_float32_pair_kernel_with_bf16_corrections_within_tolerance(srt, oracle, M, N, K, batch, tb, col_out):
+    """Float32 as one TF32 pass plus BFloat16 correction terms, op(b) pre-split by the pack pass:
+    within 1e-5 of the reference loop."""
+    srt.set_tuning(X3, 0, 0, 0)
+    rng = np.random.default_rng(M + 3 * N + 7 * K + batch + tb)
+    if col_out:
+        # out^T = b^T . a^T: the library sees op(a') = b^T (K-contiguous when b is stored [N x K] ... use tb)
+        a, b = random_bits(oracle, rng, (N, K), F32), random_bits(oracle, rng, (M, K), F32)
+        da, db = to_dev(a, F32), to_dev(b, F32)
+        out = srt.empty((N, M), torch.float32, "cuda:0", srt.Order.col)
+        srt.matmul_into(out, da, False, db, True)
+        plan = srt.query_plan(da, db, out, False, True)
+        assert plan["kernel"] == X3 and plan["swapped"] == 1, plan
+        ref = oracle.matmul(a, b, F32, False, True)
+        torch.cuda.synchronize()
+        assert oracle.rel_frobenius(out.cpu().numpy(), ref) <= TOL[F32]
+        return
+    ash, bsh = _shapes(M, N, K, False, tb, batch)
+    a, b = random_bits(oracle, rng, ash, F32), random_bits(oracle, rng, bsh, F32)
+    got, ref = _run(srt, oracle, F32, a, b, False, tb, expect_kernel=X3)
+    err = oracle.rel_frobenius(got, ref)
+    assert err <= TOL[F32], err
+
+
+def test_float32_pair_kernel_epilogue_views_and_special_values(srt, oracle):
+    srt.set_tuning(X3, 0, 0, 0)
+    rng = np.random.default_rng(43)
+    a, b = random_bits(oracle, rng, (900, 256), F32), random_bits(oracle, rng, (256, 520), F32)
+    bias = random_bits(oracle, rng, (520,), F32)
+    got, ref = _run(srt, oracle, F32, a, b, False, False, bias=bias, act="relu", expect_kernel=X3)
+    assert oracle.rel_frobenius(got, ref) <= TOL[F32]
+    # a strided (but TMA-addressable) view of a wider operand, and a result view with guard columns
+    wide = random_bits(oracle, rng, (900, 512), F32)
+    av = wide[:, 128:384]
+    big = torch.full((900, 1024), -7.0, device="cuda:0")
+    out = big[:, 256:776]
+    dwide = to_dev(wide, F32)
+    srt.matmul_into(out, dwide[:, 128:384], False, to_dev(b, F32), False)
+    assert srt.query_plan(dwide[:, 128:384], to_dev(b, F32), out)["kernel"] == X3
+    torch.cuda.synchronize()
+    assert oracle.rel_frobenius(out.cpu().numpy(), oracle.matmul(av, b, F32)) <= TOL[F32]
+    assert bool((big[:, :256] == -7.0).all()) and bool((big[:, 776:] == -7.0).all())
+    # many binades, a NaN and infinities: the NaN poisons exactly its row; an infinity times a value whose
+    # low part is zero (1.0, 0.5, small integers) stays an infinity, as in the reference loop
+    a2 = a.copy()
+    a2[:, 0] *= 2.0 ** 60
+    a2[:, 1] *= 2.0 ** -60
+    a2[9, 5] = np.nan
+    a2[17, 3] = np.inf
+    a2[33, 7] = -np.inf
+    b2 = b.copy()
+    b2[3, :] = 1.0
+    b2[7, ::2] = 0.5
+    b2[7, 1::2] = -3.0
+    got, ref = _run(srt, oracle, F32, a2, b2, False, False, expect_kernel=X3)
+    fin = np.isfinite(ref)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert np.array_equal(got[~fin & ~np.isnan(ref)], ref[~fin & ~np.isnan(ref)])      # +inf / -inf in the same places
+    assert oracle.rel_frobenius(got[fin], ref[fin]) <= TOL[F32]
+    # the same special values through the 3 x TF32 kernel (one CTA per tile)
+    srt.set_tuning(SPLIT, 0, 0, 0)
+    got, ref = _run(srt, oracle, F32, a2, b2, False, False, expect_kernel=SPLIT)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert np.array_equal(got[~fin & ~np.isnan(ref)], ref[~fin & ~np.isnan(ref)])
+    assert oracle.rel_frobenius(got[fin], ref[fin]) <= TOL[F32]
+
+
 def test_float32_kernel_choice_follows_size_and_k(srt):
     dev = "cuda:0"
     small = torch.zeros((256, 256), device=dev)
     assert srt.query_plan(small, small, small)["kernel"] == SIMT
     a, b = torch.zeros((8192, 1024), device=dev), torch.zeros((1024, 256), device=dev)
-    assert srt.query_plan(a, b, torch.zeros((8192, 256), device=dev))["kernel"] == SPLIT
+    assert srt.query_plan(a, b, torch.zeros((8192, 256), device=dev))["kernel"] == X3          # streamed a, small b
+    a, b = torch.zeros((1024, 1024), device=dev), torch.zeros((1024, 4096), device=dev)
+    assert srt.query_plan(a, b, torch.zeros((1024, 4096), device=dev))["kernel"] == SPLIT      # b is the larger operand
+    a, b = torch.zeros((1024, 8192), device=dev).t(), torch.zeros((1024, 256), device=dev)
+    assert srt.query_plan(a, b, torch.zeros((8192, 256), device=dev), False, False)["kernel"] == SPLIT   # a not K-contiguous
     a, b = torch.zeros((1024, 4096), device=dev), torch.zeros((4096, 256), device=dev)
     plan = srt.query_plan(a, b, torch.zeros((1024, 256), device=dev))
     assert plan["kernel"] == SPLIT and plan["splitK"] >= 2                                 # K > 2048
@@ -420,7 +503,7 @@ def test_config4_tall_skinny_float32(srt, oracle):
     a, b = random_bits(oracle, rng, (65536, 1024), F32), random_bits(oracle, rng, (1024, 256), F32)
     da, db = to_dev(a, F32), to_dev(b, F32)
     c = srt.matmul(da, db)
-    assert srt.query_plan(da, db, c)["kernel"] == SPLIT
+    assert srt.query_plan(da, db, c)["kernel"] == X3
     got = from_dev(c, F32)
     rows = _sample_rows(65536, 2048)
     ref = oracle.matmul(np.ascontiguousarray(a[rows]), b, F32)

@@ -12,9 +12,11 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _oracle_matmul_into(out, lhs, tl, rhs, tr):
+def _oracle_matmul_into(out, lhs, tl, rhs, tr, bias=None, activation=None):
     from oracle import oracle
-    res = oracle.matmul(lhs.numpy(), rhs.numpy(), 0, tl, tr, threads=1)
+    if lhs.dim() == 3 and rhs.dim() == 2:
+        rhs = rhs.expand(lhs.shape[0], *rhs.shape)
+    res = oracle.matmul(lhs.contiguous().numpy(), rhs.contiguous().numpy(), 0, tl, tr, threads=1)
     out.copy_(torch.from_numpy(res))
     return out
 
@@ -48,6 +50,15 @@ def _worker(rank, world, port, results):
             lo, hi = srt.shard_range(total, world, rank, 4 if axis == "n" else 1)
             dim = {"batch": 0, "m": want.dim() - 2, "n": want.dim() - 1}[axis]
             ok &= bool(torch.equal(local, want.narrow(dim, lo, hi - lo)))
+        # host-buffer form, axis "n": every rank passes only its row block of lhs and its column block
+        # of rhs; the row blocks are all-gathered (gloo here) piece by piece
+        a = torch.rand((2 * 300, 24), generator=g) * 2 - 1
+        b = torch.rand((24, 40), generator=g) * 2 - 1
+        want = torch.from_numpy(oracle.matmul(a.numpy(), b.numpy(), 0, threads=1))
+        lo, hi = srt.shard_range(40, world, rank, 4)
+        mine = srt.sharded_matmul_host(a[rank * 300:(rank + 1) * 300].contiguous(), b[:, lo:hi].contiguous(), axis="n",
+                                       device="cpu", pieces=3, matmul_into_fn=_oracle_matmul_into)
+        ok &= bool(torch.equal(mine, want[:, lo:hi]))
         flag = torch.tensor([1 if ok else 0])
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
