@@ -72,6 +72,7 @@ struct GemmParams {
     uint32_t out_tma;            // the output view is TMA-addressable: bulk tensor stores from shared memory
     uint32_t n_peers;            // gathering kernels only: peer copies of the output view (<= kMaxPeers)
     uint32_t multicast;          // gathering kernels only: 1 = the result goes to a multicast mapping instead (no per-peer stores)
+    unsigned long long wait_cycles;   // limit of every pipeline wait, in SM clock cycles (set at launch)
 };
 
 enum : uint32_t { kActSigmoid = 0, kActRelu = 1, kActTanh = 2, kActIdentity = 5, kActGelu = 6, kActGeluTanh = 7 };
@@ -122,9 +123,9 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 __device__ __forceinline__ float tf32_low_part(uint32_t x)
 {
     const float v = __uint_as_float(x);
-    if ((x & 0x7f800000u) == 0x7f800000u) return v;
     const float lo = v - __uint_as_float(x & 0xffffe000u);
-    return lo != 0.0f ? lo : v * 9.31322574615478515625e-10f;          // 2^-30
+    const float small = lo != 0.0f ? lo : v * 9.31322574615478515625e-10f;   // 2^-30
+    return (x & 0x7f800000u) == 0x7f800000u ? v : small;
 }
 
 // work unit -> tile coordinates; m-tiles are visited in groups of group_m so that the CTAs running
@@ -356,6 +357,21 @@ __device__ __forceinline__ void drain_finish(uint32_t lane)
     __syncwarp();
 }
 
+// Orderly end of a kernel in which a wait gave up (abort_flag set).  Before TMEM is released and the CTA
+// leaves, nothing asynchronous may still target it: the producer waits for every stage it armed (its
+// TMA bytes land whether or not anybody consumes them) and the MMA issuer commits to a barrier of its own
+// and waits for it (all MMAs issued so far have then read shared memory and written TMEM).  These waits
+// ignore the abort flag and use a limit of their own; on a healthy GPU they last microseconds.
+constexpr uint64_t kDrainCycles = 4000000000ull;
+
+__device__ __forceinline__ void drain_armed_stages(uint64_t* full_bar, uint32_t stages, uint32_t issued, volatile uint32_t* never)
+{
+    for (uint32_t s = 0; s < stages && s < issued; ++s) {
+        const uint32_t last = issued - 1 - ((issued - 1 - s) % stages);      // last k-block iteration that used stage s
+        mbar_wait(smem_u32(&full_bar[s]), (last / stages) & 1, never, kDrainCycles);
+    }
+}
+
 // InT / OutT: element type of the inputs and of the output (float, __half, __nv_bfloat16).
 // BN: tile width (64, 128 or 256).  fp32 inputs are multiplied as TF32.
 // OutT differs from T only for split-K partial sums (16-bit inputs, fp32 workspace).
@@ -381,8 +397,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tmem_full_bar[2];
     __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+    __shared__ __align__(8) uint64_t drain_bar;
     __shared__ uint32_t tmem_holder;
     __shared__ volatile uint32_t abort_flag;
+    __shared__ volatile uint32_t never_set;          // the drain waits' stand-in for an abort flag
+    __shared__ uint32_t issued_loads;               // k-block iterations whose loads the producer issued
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -391,6 +410,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        never_set = 0;
+        issued_loads = 0;
+        mbar_init(smem_u32(&drain_bar), 1);
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -416,13 +438,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, issued = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 const TileCoord tc = decode_tile(p, tile, BN);
                 uint32_t batch = tc.batch, m0 = tc.m0, n0 = tc.n0;
                 for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     const uint32_t sa = smem_base + stage * kStageBytes;
                     const uint32_t sb = sa + kATileBytes;
@@ -442,9 +464,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             tma_load_3d(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0,
                                         batch * p.b.batch_mul);
                     }
+                    ++issued;
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
+            issued_loads = issued;
             if (!ok) {
                 abort_flag = 1;
                 atomicOr(&g_gemm_status, kStatusProducerTimeout);
@@ -458,12 +482,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
                 const uint32_t buf = local & 1;
                 const uint32_t acc_phase = (local >> 1) & 1;
-                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 const TileCoord tc = decode_tile(p, tile, BN);
                 for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + stage * kStageBytes;
                     const uint32_t sb = sa + kATileBytes;
@@ -496,7 +520,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             const uint32_t buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
             tc_fence_after_sync();
             if constexpr (GATHER)
                 drain_accumulator<OutT, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
@@ -519,9 +543,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    if (abort_flag != 0) {
+        if (warp == 0 && lane == 0) drain_armed_stages(full_bar, stages, issued_loads, &never_set);
+        if (warp == 1 && lane == 0) {
+            umma_commit_cta1(smem_u32(&drain_bar));
+            mbar_wait(smem_u32(&drain_bar), 0, &never_set, kDrainCycles);
+        }
+        __syncthreads();
+    }
     if (warp == 1) {
         tc_fence_after_sync();
-        if (abort_flag != 0) __nanosleep(1000000);   // let copies and MMAs in flight drain
         tmem_dealloc_cta1(tmem_base, kTmemCols);
     }
 }
@@ -565,8 +596,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tmem_full_bar[2];
     __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+    __shared__ __align__(8) uint64_t drain_bar;
     __shared__ uint32_t tmem_holder;
     __shared__ volatile uint32_t abort_flag;
+    __shared__ volatile uint32_t never_set;          // the drain waits' stand-in for an abort flag
+    __shared__ uint32_t issued_loads;               // k-block iterations whose loads this CTA's producer issued
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -577,6 +611,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        never_set = 0;
+        issued_loads = 0;
+        mbar_init(smem_u32(&drain_bar), 1);
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -599,11 +636,41 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     cluster_wait_acquire();
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_holder;
+    // a wait that gives up ends BOTH CTAs of the pair: the partner's waits see the flag at their next look
+    auto raise_abort = [&](uint32_t code) {
+        abort_flag = 1;
+        st_shared_remote_u32(smem_u32(const_cast<uint32_t*>(&abort_flag)), cta_rank ^ 1u, 1u);
+        atomicOr(&g_gemm_status, code);
+    };
+    // the loads of this CTA for k-block iteration j of the pair's work list (every tile has p.k_blocks of them:
+    // pair tiles are never split along K); CTA 0 arms the stage's barrier for both CTAs
+    auto issue_loads = [&](uint32_t j) {
+        const uint32_t t_local = j / p.k_blocks, kb = j - t_local * p.k_blocks, stage = j % stages;
+        const TileCoord tc = decode_tile(p, pair_id + t_local * num_pairs, BN);
+        const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM, n0 = tc.n0 + cta_rank * kBHalf, batch = tc.batch;
+        const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+        const uint32_t sa = smem_base + stage * kStageBytes;
+        const uint32_t sb = sa + kATileBytes;
+        const int32_t k0 = static_cast<int32_t>(kb * p.kb_elems);
+        if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * p.stage_tx_bytes);
+        if (!p.a.mn_major) {
+            tma_load_3d_pair(sa, &tmap_a, bar, k0, m0, batch * p.a.batch_mul);
+        } else {
+            for (uint32_t c = 0; c < p.a.chunks; ++c)
+                tma_load_3d_pair(sa + c * p.a.chunk_bytes, &tmap_a, bar, m0 + c * p.a.chunk_elems, k0, batch * p.a.batch_mul);
+        }
+        if (!p.b.mn_major) {
+            tma_load_3d_pair(sb, &tmap_b, bar, k0, n0, batch * p.b.batch_mul);
+        } else {
+            for (uint32_t c = 0; c < p.b.chunks; ++c)
+                tma_load_3d_pair(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0, batch * p.b.batch_mul);
+        }
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, issued = 0;
             bool ok = true;
             for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
                 const TileCoord tc = decode_tile(p, tile, BN);
@@ -611,7 +678,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 m0 = m0 * 2 + cta_rank * kTileM;            // decode_tile counts 128-row units; pair tiles are 256 rows
                 n0 += cta_rank * kBHalf;
                 for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     // every load of the pair reports to the leader's barrier
                     const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
                     const uint32_t sa = smem_base + stage * kStageBytes;
@@ -632,13 +699,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             tma_load_3d_pair(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0,
                                              batch * p.b.batch_mul);
                     }
+                    ++issued;
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
-            if (!ok) {
-                abort_flag = 1;
-                atomicOr(&g_gemm_status, kStatusProducerTimeout);
-            }
+            issued_loads = issued;
+            if (!ok) raise_abort(kStatusProducerTimeout);
         }
     } else if (warp == 1) {
         if (elect_one()) {
@@ -649,12 +715,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
                     const uint32_t buf = local & 1;
                     const uint32_t acc_phase = (local >> 1) & 1;
-                    if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * BN;
                     const TileCoord tc = decode_tile(p, tile, BN);
                     for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                        if (!mbar_wait_cluster(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                        if (!mbar_wait_cluster(smem_u32(&full_bar[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t sa = smem_base + stage * kStageBytes;
                         const uint32_t sb = sa + kATileBytes;
@@ -672,10 +738,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                     if (ok) umma_commit_cta2_mc(smem_u32(&tmem_full_bar[buf]), 3);
                 }
-                if (!ok) {
-                    abort_flag = 1;
-                    atomicOr(&g_gemm_status, kStatusMmaTimeout);
-                }
+                if (!ok) raise_abort(kStatusMmaTimeout);
             }
         }
     } else {
@@ -689,7 +752,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             m0 = m0 * 2 + cta_rank * kTileM;
             const uint32_t buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
-            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
             tc_fence_after_sync();
             if constexpr (GATHER)
                 drain_accumulator<T, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
@@ -703,10 +766,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
         }
         drain_finish(lane);
-        if (!ok) {
-            abort_flag = 1;
-            if (lane == 0) atomicOr(&g_gemm_status, kStatusEpilogueTimeout);
-        }
+        if (!ok && lane == 0) raise_abort(kStatusEpilogueTimeout);
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -715,9 +775,34 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
+    if (abort_flag != 0) {
+        // Both CTAs take this branch (the flag is raised in both before the barrier above).  In order: the
+        // leader waits for every MMA issued so far; the producer that issued fewer k-block iterations than its
+        // partner issues the missing loads, so that every armed stage receives the bytes of both CTAs; the
+        // leader waits for all armed stages.  After that nothing asynchronous targets either CTA.
+        if (cta_rank == 0 && warp == 1 && lane == 0) {
+            umma_commit_cta2_mc(smem_u32(&drain_bar), 1);
+            mbar_wait_cluster(smem_u32(&drain_bar), 0, &never_set, kDrainCycles);
+        }
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        uint32_t both = 0;
+        if (warp == 0 && lane == 0) {
+            const uint32_t mine = issued_loads, theirs = ld_shared_remote_u32(smem_u32(&issued_loads), cta_rank ^ 1u);
+            for (uint32_t j = mine; j < theirs; ++j) issue_loads(j);
+            both = mine > theirs ? mine : theirs;
+        }
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        if (cta_rank == 0 && warp == 0 && lane == 0) drain_armed_stages(full_bar, stages, both, &never_set);
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    }
     if (warp == 1) {
         tc_fence_after_sync();
-        if (abort_flag != 0) __nanosleep(1000000);
         tmem_dealloc_cta2(tmem_base, kTmemCols);
     }
     cluster_arrive_release();
@@ -766,8 +851,11 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ __align__(8) uint64_t tmem_full_bar[2];
     __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+    __shared__ __align__(8) uint64_t drain_bar;
     __shared__ uint32_t tmem_holder;
     __shared__ volatile uint32_t abort_flag;
+    __shared__ volatile uint32_t never_set;          // the drain waits' stand-in for an abort flag
+    __shared__ uint32_t issued_loads;               // k-block iterations whose loads the producer issued
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -776,6 +864,9 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        never_set = 0;
+        issued_loads = 0;
+        mbar_init(smem_u32(&drain_bar), 1);
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&ready_bar[s]), kSplitTransformWarps);
@@ -802,13 +893,13 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, issued = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 const TileCoord tc = decode_tile(p, tile, BN);
                 uint32_t batch = tc.batch, m0 = tc.m0, n0 = tc.n0;
                 for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     const uint32_t sa = smem_base + stage * kStageBytes;
                     const uint32_t sb = sa + kATileBytes;
@@ -828,9 +919,11 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             tma_load_3d(sb + c * p.b.chunk_bytes, &tmap_b, bar, n0 + c * p.b.chunk_elems, k0,
                                         batch * p.b.batch_mul);
                     }
+                    ++issued;
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
+            issued_loads = issued;
             if (!ok) {
                 abort_flag = 1;
                 atomicOr(&g_gemm_status, kStatusProducerTimeout);
@@ -844,13 +937,13 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
                 const uint32_t buf = local % kAccBufs;
                 const uint32_t acc_phase = (local / kAccBufs) & 1;
-                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_main = tmem_base + buf * 2 * BN;
                 const uint32_t d_small = d_main + BN;
                 const TileCoord tc = decode_tile(p, tile, BN);
                 for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&ready_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&ready_bar[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + stage * kStageBytes;
                     const uint32_t sb = sa + kATileBytes;
@@ -890,7 +983,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             const uint32_t buf = local % kAccBufs;
             const uint32_t acc_phase = (local / kAccBufs) & 1;
-            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
             tc_fence_after_sync();
             drain_accumulator<T, BN, true, 1>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096, 0,
                                               tmem_base + buf * 2 * BN, quarter, lane, batch, m0, n0,
@@ -912,7 +1005,7 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
             const TileCoord tc = decode_tile(p, tile, BN);
             for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                 const uint32_t hi_base = smem_base + stage * kStageBytes;
 #pragma unroll 4
                 for (uint32_t off = t * 16; off < kHalfBytes; off += kSplitTransformWarps * 32 * 16) {
@@ -941,9 +1034,16 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    if (abort_flag != 0) {
+        if (warp == 0 && lane == 0) drain_armed_stages(full_bar, stages, issued_loads, &never_set);
+        if (warp == 1 && lane == 0) {
+            umma_commit_cta1(smem_u32(&drain_bar));
+            mbar_wait(smem_u32(&drain_bar), 0, &never_set, kDrainCycles);
+        }
+        __syncthreads();
+    }
     if (warp == 1) {
         tc_fence_after_sync();
-        if (abort_flag != 0) __nanosleep(1000000);
         tmem_dealloc_cta1(tmem_base, kTmemCols);
     }
 }

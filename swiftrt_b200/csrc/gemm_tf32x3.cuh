@@ -9,7 +9,7 @@
 // passes instead of the three of gemm_tcgen05_split_kernel.  The dropped lo . lo term is 2^-22.
 //
 // Operands.  op(a) [M x K] must be K-contiguous; it is streamed by TMA as raw fp32 (the TF32 operand)
-// and four transform warps per CTA write the BFloat16 tile  [ lo(a) | b16(a) ]  (32 + 32 values = one
+// and the worker warps of each CTA write the BFloat16 tile  [ lo(a) | b16(a) ]  (32 + 32 values = one
 // 128-byte swizzled row per A row and k-block) beside it.  op(b) is the small, re-used operand: a
 // pre-pass (tf32x3_pack_kernel) writes it once per call as  Bh = fp32 [N x Kp]  (K-contiguous, zero
 // padded to whole k-blocks) and  Bc = bf16 [N x 2 Kp]  holding  [ b16(b) | lo(b) ]  per k-block, so
@@ -19,8 +19,8 @@
 //
 //   warp 0      TMA producer (both CTAs): A tile -> own fullA[s]; Bh and Bc half tiles -> the leader's fullB[s]
 //   warp 1      MMA issuer (leader CTA only) and TMEM owner
-//   warps 2-9   epilogue
-//   warps 10-13 transform: fullA[s] -> write [lo | b16] -> arrive on the leader's ready[s] (count 8)
+//   warps 2-9   workers: during the reduction fullA[s] -> write [lo | b16] -> arrive on the leader's ready[s]
+//               (count 16); after the tile's last MMA the same warps are the epilogue
 //   empty[s]    both CTAs, one multicast commit of the leader frees the stage in both
 //
 // Non-finite inputs: lo(x) = x for an infinity or NaN, and a zero low part of a non-zero value is
@@ -31,8 +31,8 @@
 
 namespace srt {
 
-constexpr uint32_t kX3TransformWarps = 4;
-constexpr uint32_t kX3Threads = (2 + 8 + kX3TransformWarps) * 32;      // 448
+constexpr uint32_t kX3WorkerWarps = 8;                                 // transform during the reduction, epilogue after it
+constexpr uint32_t kX3Threads = (2 + kX3WorkerWarps) * 32;             // 320
 constexpr uint32_t kX3TileBytes = 128 * kRowBytes;                     // one 128-row, 128-byte-wide tile: 16 KB
 constexpr uint32_t kX3StageBytes = 4 * kX3TileBytes;                   // A raw, A corrections, Bh half, Bc half
 constexpr uint32_t kX3MaxStages = 3;
@@ -80,7 +80,6 @@ tf32x3_pack_kernel(const PackParams p)
 struct X3Params {
     GemmParams g;                 // sizes, tile walk, A descriptor fields, epilogue
     uint32_t idesc_tf32, idesc_bf16;
-    uint32_t l2_prefetch;         // k-blocks of A to prefetch into L2 ahead of the loads (0 = none)
 };
 
 __global__ void __launch_bounds__(kX3Threads, 1)
@@ -103,8 +102,11 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __shared__ __align__(8) uint64_t empty_bar[kX3MaxStages];    // both: the stage's MMAs have completed
     __shared__ __align__(8) uint64_t tmem_full_bar;
     __shared__ __align__(8) uint64_t tmem_empty_bar;             // leader, count 16
+    __shared__ __align__(8) uint64_t drain_bar;
     __shared__ uint32_t tmem_holder;
     __shared__ volatile uint32_t abort_flag;
+    __shared__ volatile uint32_t never_set;          // the drain waits' stand-in for an abort flag
+    __shared__ uint32_t issued_loads;               // k-block iterations whose loads this CTA's producer issued
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -115,10 +117,13 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        never_set = 0;
+        issued_loads = 0;
+        mbar_init(smem_u32(&drain_bar), 1);
         for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_a[s]), 1);
             mbar_init(smem_u32(&full_b[s]), 1);
-            mbar_init(smem_u32(&ready[s]), 2 * kX3TransformWarps);
+            mbar_init(smem_u32(&ready[s]), 2 * kX3WorkerWarps);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         mbar_init(smem_u32(&tmem_full_bar), 1);
@@ -145,33 +150,37 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         atomicOr(&g_gemm_status, code);
     };
 
+    // the loads of this CTA for k-block iteration j of the pair's work list (every tile has p.k_blocks of them)
+    auto issue_loads = [&](uint32_t j) {
+        const uint32_t t_local = j / p.k_blocks, kb = j - t_local * p.k_blocks, stage = j % stages;
+        const TileCoord tc = decode_tile(p, pair_id + t_local * num_pairs, BN);
+        const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM, n0 = tc.n0 + cta_rank * (BN / 2);
+        const uint32_t sa = smem_base + stage * kX3StageBytes;
+        const uint32_t sbh = sa + 2 * kX3TileBytes, sbc = sa + 3 * kX3TileBytes;
+        const uint32_t bar_a = smem_u32(&full_a[stage]);
+        const uint32_t bar_b = map_to_cta(smem_u32(&full_b[stage]), 0);
+        mbar_arrive_expect_tx(bar_a, kX3TileBytes);
+        if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_b[stage]), 4 * kX3TileBytes);
+        tma_load_3d(sa, &tmap_a, bar_a, static_cast<int32_t>(kb * 32), m0, tc.batch * p.a.batch_mul);
+        tma_load_3d_pair(sbh, &tmap_bh, bar_b, static_cast<int32_t>(kb * 32), n0, tc.batch * p.b.batch_mul);
+        tma_load_3d_pair(sbc, &tmap_bc, bar_b, static_cast<int32_t>(kb * 64), n0, tc.batch * p.b.batch_mul);
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (elect_one()) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t stage = 0, phase = 0, issued = 0;
             bool ok = true;
             grid_dependency_wait();                  // Bh / Bc come from the pack kernel launched just before
             for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
-                const TileCoord tc = decode_tile(p, tile, BN);
-                const uint32_t batch = tc.batch;
-                const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM;          // decode_tile counts 128-row units
-                const uint32_t n0 = tc.n0 + cta_rank * (BN / 2);
-                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag)) { ok = false; break; }
-                    const uint32_t sa = smem_base + stage * kX3StageBytes;
-                    const uint32_t sbh = sa + 2 * kX3TileBytes, sbc = sa + 3 * kX3TileBytes;
-                    const uint32_t bar_a = smem_u32(&full_a[stage]);
-                    const uint32_t bar_b = map_to_cta(smem_u32(&full_b[stage]), 0);
-                    mbar_arrive_expect_tx(bar_a, kX3TileBytes);
-                    if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_b[stage]), 4 * kX3TileBytes);
-                    tma_load_3d(sa, &tmap_a, bar_a, static_cast<int32_t>(kb * 32), m0, batch * p.a.batch_mul);
-                    tma_load_3d_pair(sbh, &tmap_bh, bar_b, static_cast<int32_t>(kb * 32), n0, batch * p.b.batch_mul);
-                    tma_load_3d_pair(sbc, &tmap_bc, bar_b, static_cast<int32_t>(kb * 64), n0, batch * p.b.batch_mul);
-                    if (xp.l2_prefetch && kb + xp.l2_prefetch < tc.kb1)
-                        tma_prefetch_l2_3d(&tmap_a, static_cast<int32_t>((kb + xp.l2_prefetch) * 32), m0, batch * p.a.batch_mul);
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                    issue_loads(issued);
+                    ++issued;
                     if (++stage == stages) { stage = 0; phase ^= 1; }
                 }
             }
+            issued_loads = issued;
             if (!ok) raise_abort(kStatusProducerTimeout);
         }
     } else if (warp == 1) {
@@ -182,12 +191,12 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t hi64 = static_cast<uint64_t>(p.a.desc_hi) << 32;     // K-major, 128-byte swizzle: every tile alike
             const uint32_t d_main = tmem_base, d_corr = tmem_base + BN;
             for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
-                if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar), (local & 1) ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar), (local & 1) ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                 tc_fence_after_sync();
                 const TileCoord tc = decode_tile(p, tile, BN);
                 for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                    if (!mbar_wait_cluster(smem_u32(&full_b[stage]), phase, &abort_flag)) { ok = false; break; }
-                    if (!mbar_wait_cluster(smem_u32(&ready[stage]), phase, &abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_cluster(smem_u32(&full_b[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                    if (!mbar_wait_cluster(smem_u32(&ready[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_base + stage * kX3StageBytes;
                     const uint32_t a_raw = ((sa >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
@@ -208,15 +217,52 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             if (!ok) raise_abort(kStatusMmaTimeout);
         }
-    } else if (warp < 10) {
-        // ------------------------------------------------------------------ epilogue (both CTAs)
+    } else {
+        // ------------------------------------------------------------------ workers (both CTAs): transform, then epilogue
+        // During the reduction the eight warps write the correction tile of every stage: thread t owns half a row
+        // (row t mod 128, 16 of its 32 values).  The accumulators are not double-buffered (they fill TMEM), so the
+        // same warps drain them when the tile's last MMA has completed.
+        const uint32_t wt = threadIdx.x - 64;                       // 0 .. 255
+        const uint32_t row = wt & 127, half = wt >> 7;
+        const uint32_t sw = row & 7;
         const uint32_t quarter = warp & 3;
-        uint32_t local = 0;
+        uint32_t stage = 0, phase = 0, local = 0;
         bool ok = true;
         for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
             const TileCoord tc = decode_tile(p, tile, BN);
+            for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
+                if (!mbar_wait(smem_u32(&full_a[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                const uint32_t src = smem_base + stage * kX3StageBytes + row * 128;
+                const uint32_t dst = src + kX3TileBytes;
+                uint32_t x[16];
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c)                 // logical 16-byte chunks 4 half .. 4 half + 3 of the row
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(x[4 * c]), "=r"(x[4 * c + 1]), "=r"(x[4 * c + 2]), "=r"(x[4 * c + 3])
+                                 : "r"(src + (((4 * half + c) ^ sw) << 4)));
+                uint32_t lo[8], hi[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    lo[e] = pack2<__nv_bfloat16>(tf32_low_part(x[2 * e]), tf32_low_part(x[2 * e + 1]));
+                    hi[e] = pack2<__nv_bfloat16>(__uint_as_float(x[2 * e]), __uint_as_float(x[2 * e + 1]));
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 2; ++j) {               // 8 values each: chunk 2 half + j of lo, chunk 4 + 2 half + j of b16
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst + (((2 * half + j) ^ sw) << 4)), "r"(lo[4 * j]), "r"(lo[4 * j + 1]), "r"(lo[4 * j + 2]),
+                                   "r"(lo[4 * j + 3]) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst + (((4 + 2 * half + j) ^ sw) << 4)), "r"(hi[4 * j]), "r"(hi[4 * j + 1]), "r"(hi[4 * j + 2]),
+                                   "r"(hi[4 * j + 3]) : "memory");
+                }
+                fence_proxy_async_smem();          // generic-proxy writes -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(smem_u32(&ready[stage]), 0);
+                if (++stage == stages) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
             const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM;
-            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar), local & 1, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar), local & 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
             tc_fence_after_sync();
             drain_accumulator<float, BN, true, 2>(p, &tmap_out, smem_base + stages * kX3StageBytes + (warp - 2) * 4096, (warp - 2) >> 2,
                                                   tmem_base, quarter, lane, tc.obatch, m0, tc.n0, tmem_base + BN);
@@ -226,43 +272,6 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         drain_finish(lane);
         if (!ok && lane == 0) raise_abort(kStatusEpilogueTimeout);
-    } else {
-        // ------------------------------------------------------------------ transform (both CTAs): row t of the A tile
-        const uint32_t row = threadIdx.x - 10 * 32;                 // 0 .. 127
-        const uint32_t sw = row & 7;
-        uint32_t stage = 0, phase = 0;
-        bool ok = true;
-        for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
-            const TileCoord tc = decode_tile(p, tile, BN);
-            for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                if (!mbar_wait(smem_u32(&full_a[stage]), phase, &abort_flag)) { ok = false; break; }
-                const uint32_t src = smem_base + stage * kX3StageBytes + row * 128;
-                const uint32_t dst = src + kX3TileBytes;
-#pragma unroll
-                for (uint32_t j = 0; j < 4; ++j) {              // 8 fp32 (two 16-byte chunks) -> one chunk of lo, one of b16
-                    uint32_t x[8];
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(src + (((2 * j) ^ sw) << 4)));
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]) : "r"(src + (((2 * j + 1) ^ sw) << 4)));
-                    uint32_t lo[4], hi[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        lo[e] = pack2<__nv_bfloat16>(tf32_low_part(x[2 * e]), tf32_low_part(x[2 * e + 1]));
-                        hi[e] = pack2<__nv_bfloat16>(__uint_as_float(x[2 * e]), __uint_as_float(x[2 * e + 1]));
-                    }
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(dst + ((j ^ sw) << 4)), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(dst + (((4 + j) ^ sw) << 4)), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
-                }
-                fence_proxy_async_smem();          // generic-proxy writes -> visible to the MMA's reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(smem_u32(&ready[stage]), 0);
-                if (++stage == stages) { stage = 0; phase ^= 1; }
-            }
-        }
-        if (!ok && lane == 0) raise_abort(kStatusPairTimeout);
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -270,9 +279,36 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
+    if (abort_flag != 0) {
+        // As in gemm_tcgen05_pair_kernel: the leader waits for the MMAs issued so far, the producer that is
+        // behind issues the loads its partner already issued, then every producer waits for its own A stages
+        // and the leader for the stages of the packed operand.
+        if (cta_rank == 0 && warp == 1 && lane == 0) {
+            umma_commit_cta2_mc(smem_u32(&drain_bar), 1);
+            mbar_wait_cluster(smem_u32(&drain_bar), 0, &never_set, kDrainCycles);
+        }
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        uint32_t both = 0;
+        if (warp == 0 && lane == 0) {
+            const uint32_t mine = issued_loads, theirs = ld_shared_remote_u32(smem_u32(&issued_loads), cta_rank ^ 1u);
+            for (uint32_t j = mine; j < theirs; ++j) issue_loads(j);
+            both = mine > theirs ? mine : theirs;
+        }
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        if (warp == 0 && lane == 0) {
+            drain_armed_stages(full_a, stages, both, &never_set);
+            if (cta_rank == 0) drain_armed_stages(full_b, stages, both, &never_set);
+        }
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    }
     if (warp == 1) {
         tc_fence_after_sync();
-        if (abort_flag != 0) __nanosleep(1000000);
         tmem_dealloc_cta2(tmem_base, kTmemCols);
     }
     cluster_arrive_release();

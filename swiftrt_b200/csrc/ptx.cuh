@@ -62,6 +62,18 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_r
         ::"r"(bar), "r"(cta_rank) : "memory");
 }
 
+// The same with the default (CTA-scope release) semantics: the cluster-scope release above costs the
+// arriving thread on the order of a thousand cycles, which matters when the arrive is issued once per
+// pipeline stage.  For hand-offs whose data the async proxy reads (fence.proxy.async issued before).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_rank)
+{
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}"
+        ::"r"(bar), "r"(cta_rank) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
@@ -100,35 +112,42 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     return done != 0;
 }
 
-// Wall-clock limit of one pipeline wait, in nanoseconds.  A healthy wait lasts microseconds.  A
-// device variable rather than a constant so that a test can shorten it (srtMatmulSetWaitLimit) and
-// see a wait give up on a valid product; it is read only after a first try_wait has failed.
+// Limit of one pipeline wait.  A healthy wait lasts microseconds; the default limit is 2 s.  The
+// kernels receive the limit as a parameter in SM clock cycles (GemmParams::wait_cycles: nanoseconds
+// times 2, an upper bound of the cycles per nanosecond, so the limit is never shorter than asked) and
+// measure with the SM's own cycle counter: reading %globaltimer costs about a microsecond, which put
+// that microsecond on the critical path of every wait that did not succeed at its first try.
 constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
-__device__ unsigned long long g_wait_limit_ns = kDefaultWaitLimitNs;
 
-// Waits for the phase with the given parity.  Returns false when the limit ran out or
-// when another role of this CTA already gave up (*abort_flag != 0).  Each failed try_wait has
-// already slept for up to kSuspendHintNs, so the bookkeeping below runs a few thousand times a
-// second at most.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag)
+__device__ __forceinline__ uint64_t sm_clock()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+    return t;
+}
+
+// Waits for the phase with the given parity.  Returns false when the limit ran out or when another
+// role of this CTA already gave up (*abort_flag != 0).  Each failed try_wait has already slept for up
+// to kSuspendHintNs.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint64_t limit_cycles)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const uint64_t t0 = sm_clock();
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag != 0) return false;
-        if (global_timer_ns() - t0 > g_wait_limit_ns) return false;
+        if (sm_clock() - t0 > limit_cycles) return false;
+        if (mbar_try_wait(bar, parity)) return true;          // parks for up to kSuspendHintNs
     }
 }
 
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag)
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint64_t limit_cycles)
 {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const uint64_t t0 = sm_clock();
     for (;;) {
-        if (mbar_try_wait_cluster(bar, parity)) return true;
         if (*abort_flag != 0) return false;
-        if (global_timer_ns() - t0 > g_wait_limit_ns) return false;
+        if (sm_clock() - t0 > limit_cycles) return false;
+        if (mbar_try_wait_cluster(bar, parity)) return true;          // parks for up to kSuspendHintNs
     }
 }
 
@@ -226,11 +245,15 @@ __device__ __forceinline__ void st_shared_remote_u32(uint32_t smem_addr, uint32_
         ::"r"(smem_addr), "r"(cta_rank), "r"(value) : "memory");
 }
 
-// L2 prefetch of a tile a later tma_load_3d will fetch (no shared-memory destination, no barrier)
-__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int32_t c0, int32_t c1, int32_t c2)
+__device__ __forceinline__ uint32_t ld_shared_remote_u32(uint32_t smem_addr, uint32_t cta_rank)
 {
-    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+    uint32_t v;
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %1, %2;\n\t"
+        "ld.shared::cluster.u32 %0, [remote];\n\t}"
+        : "=r"(v) : "r"(smem_addr), "r"(cta_rank) : "memory");
+    return v;
 }
 
 // ----------------------------------------------------------------------------- tcgen05

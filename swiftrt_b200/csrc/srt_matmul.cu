@@ -28,6 +28,7 @@ using namespace srt;
 
 thread_local char g_error[512] = "";
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_wait_limit_ns{srt::kDefaultWaitLimitNs};     // srtMatmulSetWaitLimit
 
 struct Tuning {
     std::atomic<int32_t> force_kernel{0}, tile_n{0}, stages{0}, max_ctas{0}, split_k{0};
@@ -931,8 +932,6 @@ cudaError_t prepare_x3(const Plan& plan, Prepared& pr)
     const uint32_t shape = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
     xp.idesc_tf32 = shape | (2u << 7) | (2u << 10);
     xp.idesc_bf16 = shape | (1u << 7) | (1u << 10);
-    xp.l2_prefetch = 0;
-    if (const char* dbg = getenv("SRT_DEV_X3_PREFETCH")) xp.l2_prefetch = (uint32_t)atoi(dbg);   // DEV-ONLY, to be removed
     gp.out = Q.out;
     gp.ldo = Q.N == 1 ? (Q.M == 1 ? 1 : Q.o_m) : (Q.M == 1 ? (long long)Q.N : Q.o_m);
     gp.out_batch_stride = Q.o_b;
@@ -1208,6 +1207,8 @@ cudaError_t launch_prepared(Prepared& pr, cudaStream_t stream)
 {
     cudaError_t e;
     const uint32_t bn = pr.bn;
+    // nanoseconds -> SM cycles at an upper bound of 2 cycles per nanosecond
+    pr.gp.wait_cycles = pr.xp.g.wait_cycles = g_wait_limit_ns.load(std::memory_order_relaxed) * 2;
     if (pr.ws_bytes > 0) {
         int dev = 0;
         e = cudaGetDevice(&dev);
@@ -2315,9 +2316,8 @@ cudaError_t srtMatmulShardedDevices(srtShardAxis axis, int32_t nDevices, const c
 
 cudaError_t srtMatmulSetWaitLimit(uint64_t nanoseconds)
 {
-    const unsigned long long v = nanoseconds ? (unsigned long long)nanoseconds : (unsigned long long)srt::kDefaultWaitLimitNs;
-    const cudaError_t e = cudaMemcpyToSymbol(srt::g_wait_limit_ns, &v, sizeof v);
-    return e == cudaSuccess ? e : fail(e, "srtMatmulSetWaitLimit: %s", cudaGetErrorString(e));
+    g_wait_limit_ns.store(nanoseconds ? nanoseconds : (uint64_t)srt::kDefaultWaitLimitNs, std::memory_order_relaxed);
+    return cudaSuccess;
 }
 
 // ------------------------------------------------------------------ srtMatmulNoAlloc
@@ -2449,6 +2449,7 @@ static cudaError_t gather_impl(const void* a, const srtTensorDescriptor* aDesc, 
         if (e != cudaSuccess) return e;
         return copy_view_to_peers(P, oDesc, out, peerCount, peerOut, stream);
     }
+    ent.pr.gp.wait_cycles = g_wait_limit_ns.load(std::memory_order_relaxed) * 2;
     const Prepared& pr = ent.pr;
     if (pr.kernel == srtMatmulKernelTcgen05Pair) {
         switch (pr.type) {
