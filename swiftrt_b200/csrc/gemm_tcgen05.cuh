@@ -262,24 +262,30 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
         const uint32_t box_col = n0 + bx * kColsPerBox;
         if (box_col >= p.N) break;                              // uniform over the warp
         uint32_t packed[32];                                    // 128 bytes of this thread's output row
+        // all accumulator loads of the box are issued before the first wait: their latencies overlap
+        uint32_t raw[kLoadsPerBox][32];
+#pragma unroll
+        for (uint32_t h = 0; h < kLoadsPerBox; ++h) tmem_ld_32x32(acc + lane_addr + (bx * kLoadsPerBox + h) * 32, raw[h]);
 #pragma unroll
         for (uint32_t h = 0; h < kLoadsPerBox; ++h) {
             const uint32_t col0 = box_col + h * 32;
-            uint32_t raw[32];
-            tmem_ld_32x32(acc + lane_addr + (bx * kLoadsPerBox + h) * 32, raw);
             // one coalesced bias load per 32 columns, handed out by shuffle below
             float my_bias = 0.0f;
             if (p.bias_mode == 1 && col0 + lane < p.N)
                 my_bias = to_float<T>(__ldg(bias + static_cast<long long>(col0 + lane) * p.bias_stride));
-            tmem_ld_wait_regs(raw);
+            if (h == 0) {
+                if constexpr (kLoadsPerBox == 2) tmem_ld_wait_regs2(raw[0], raw[kLoadsPerBox - 1]);
+                else tmem_ld_wait_regs(raw[0]);
+            }
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[h][j]);
             if constexpr (DUAL) {
-                tmem_ld_32x32(acc2 + lane_addr + (bx * kLoadsPerBox + h) * 32, raw);
-                tmem_ld_wait_regs(raw);
+                uint32_t raw2[32];
+                tmem_ld_32x32(acc2 + lane_addr + (bx * kLoadsPerBox + h) * 32, raw2);
+                tmem_ld_wait_regs(raw2);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(raw[j]);
+                for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(raw2[j]);
             }
             if (p.bias_mode == 1) {
 #pragma unroll

@@ -31,11 +31,21 @@
 
 namespace srt {
 
-constexpr uint32_t kX3WorkerWarps = 8;                                 // transform during the reduction, epilogue after it
-constexpr uint32_t kX3Threads = (2 + kX3WorkerWarps) * 32;             // 320
+// Two shapes of the same kernel.
+//   BN = 256: 64 KB stages (three fit), both accumulators fill TMEM: eight "worker" warps write the correction
+//             tiles during the reduction and drain the accumulators afterwards (the epilogue is exposed).
+//             The default: measured faster (141 us against 161 us on 65536 x 1024 . 1024 x 256).
+//   BN = 128: 48 KB stages (four fit), accumulators double-buffered: eight transform warps and four epilogue
+//             warps, the epilogue of one tile runs under the reduction of the next; twice the MMA
+//             instructions and operand reads per flop.
+constexpr uint32_t kX3TransformWarps = 8;
 constexpr uint32_t kX3TileBytes = 128 * kRowBytes;                     // one 128-row, 128-byte-wide tile: 16 KB
-constexpr uint32_t kX3StageBytes = 4 * kX3TileBytes;                   // A raw, A corrections, Bh half, Bc half
-constexpr uint32_t kX3MaxStages = 3;
+__host__ __device__ constexpr uint32_t x3_stage_bytes(uint32_t bn) { return 2 * kX3TileBytes + bn * kRowBytes; }   // A raw, A corrections, Bh half, Bc half
+__host__ __device__ constexpr uint32_t x3_stages(uint32_t bn) { return bn == 128 ? 4u : 3u; }
+__host__ __device__ constexpr uint32_t x3_epilogue_warps(uint32_t bn) { return bn == 128 ? 4u : 8u; }
+__host__ __device__ constexpr uint32_t x3_threads(uint32_t bn) { return bn == 128 ? (2 + 4 + kX3TransformWarps) * 32 : (2 + 8) * 32; }
+__host__ __device__ constexpr uint32_t x3_smem_bytes(uint32_t bn) { return x3_stages(bn) * x3_stage_bytes(bn) + x3_epilogue_warps(bn) * 4096 + 1024; }
+constexpr uint32_t kX3MaxStages = 4;
 
 struct PackParams {
     const float* b;                 // op(b) element (n, k) at b + batch b_b + n b_n + k b_k
@@ -82,7 +92,8 @@ struct X3Params {
     uint32_t idesc_tf32, idesc_bf16;
 };
 
-__global__ void __launch_bounds__(kX3Threads, 1)
+template <uint32_t BN>
+__global__ void __launch_bounds__(x3_threads(BN), 1)
 gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ CUtensorMap tmap_bh,
                         const __grid_constant__ CUtensorMap tmap_bc,
@@ -90,8 +101,13 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ X3Params xp)
 {
     const GemmParams& p = xp.g;
-    constexpr uint32_t BN = 256;
-    constexpr uint32_t kTmemCols = 512;             // main accumulator [0, 256), corrections [256, 512)
+    constexpr uint32_t kStageBytes = x3_stage_bytes(BN);
+    constexpr uint32_t kStages = x3_stages(BN);
+    constexpr uint32_t kBTileBytes = (BN / 2) * kRowBytes;          // this CTA's half of the Bh (or Bc) tile
+    constexpr bool kOverlap = BN == 128;                            // separate epilogue warps, double-buffered accumulators
+    constexpr uint32_t kAccBufs = kOverlap ? 2 : 1;
+    constexpr uint32_t kEpiWarps = x3_epilogue_warps(BN);
+    constexpr uint32_t kTmemCols = 512;             // per buffer: main accumulator (BN columns), then corrections (BN columns)
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -100,8 +116,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __shared__ __align__(8) uint64_t full_b[kX3MaxStages];       // leader: both CTAs' Bh and Bc tiles landed
     __shared__ __align__(8) uint64_t ready[kX3MaxStages];        // leader: both CTAs' correction tiles written
     __shared__ __align__(8) uint64_t empty_bar[kX3MaxStages];    // both: the stage's MMAs have completed
-    __shared__ __align__(8) uint64_t tmem_full_bar;
-    __shared__ __align__(8) uint64_t tmem_empty_bar;             // leader, count 16
+    __shared__ __align__(8) uint64_t tmem_full_bar[2];
+    __shared__ __align__(8) uint64_t tmem_empty_bar[2];          // leader: one arrive per epilogue warp of both CTAs
     __shared__ __align__(8) uint64_t drain_bar;
     __shared__ uint32_t tmem_holder;
     __shared__ volatile uint32_t abort_flag;
@@ -110,7 +126,6 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t stages = p.stages;
     const uint32_t cta_rank = cluster_ctarank();
     const uint32_t pair_id = blockIdx.x >> 1;
     const uint32_t num_pairs = gridDim.x >> 1;
@@ -120,14 +135,16 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         never_set = 0;
         issued_loads = 0;
         mbar_init(smem_u32(&drain_bar), 1);
-        for (uint32_t s = 0; s < stages; ++s) {
+        for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&full_a[s]), 1);
             mbar_init(smem_u32(&full_b[s]), 1);
-            mbar_init(smem_u32(&ready[s]), 2 * kX3WorkerWarps);
+            mbar_init(smem_u32(&ready[s]), 2 * kX3TransformWarps);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(&tmem_full_bar), 1);
-        mbar_init(smem_u32(&tmem_empty_bar), 16);
+        for (uint32_t i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&tmem_full_bar[i]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[i]), 2 * kEpiWarps);
+        }
         fence_mbar_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_bh);
@@ -149,18 +166,17 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         st_shared_remote_u32(smem_u32(const_cast<uint32_t*>(&abort_flag)), cta_rank ^ 1u, 1u);
         atomicOr(&g_gemm_status, code);
     };
-
     // the loads of this CTA for k-block iteration j of the pair's work list (every tile has p.k_blocks of them)
     auto issue_loads = [&](uint32_t j) {
-        const uint32_t t_local = j / p.k_blocks, kb = j - t_local * p.k_blocks, stage = j % stages;
+        const uint32_t t_local = j / p.k_blocks, kb = j - t_local * p.k_blocks, stage = j % kStages;
         const TileCoord tc = decode_tile(p, pair_id + t_local * num_pairs, BN);
         const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM, n0 = tc.n0 + cta_rank * (BN / 2);
-        const uint32_t sa = smem_base + stage * kX3StageBytes;
-        const uint32_t sbh = sa + 2 * kX3TileBytes, sbc = sa + 3 * kX3TileBytes;
+        const uint32_t sa = smem_base + stage * kStageBytes;
+        const uint32_t sbh = sa + 2 * kX3TileBytes, sbc = sbh + kBTileBytes;
         const uint32_t bar_a = smem_u32(&full_a[stage]);
         const uint32_t bar_b = map_to_cta(smem_u32(&full_b[stage]), 0);
         mbar_arrive_expect_tx(bar_a, kX3TileBytes);
-        if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_b[stage]), 4 * kX3TileBytes);
+        if (cta_rank == 0) mbar_arrive_expect_tx(smem_u32(&full_b[stage]), 4 * kBTileBytes);
         tma_load_3d(sa, &tmap_a, bar_a, static_cast<int32_t>(kb * 32), m0, tc.batch * p.a.batch_mul);
         tma_load_3d_pair(sbh, &tmap_bh, bar_b, static_cast<int32_t>(kb * 32), n0, tc.batch * p.b.batch_mul);
         tma_load_3d_pair(sbc, &tmap_bc, bar_b, static_cast<int32_t>(kb * 64), n0, tc.batch * p.b.batch_mul);
@@ -177,7 +193,7 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     issue_loads(issued);
                     ++issued;
-                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
             issued_loads = issued;
@@ -189,21 +205,21 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t stage = 0, phase = 0, local = 0;
             bool ok = true;
             const uint64_t hi64 = static_cast<uint64_t>(p.a.desc_hi) << 32;     // K-major, 128-byte swizzle: every tile alike
-            const uint32_t d_main = tmem_base, d_corr = tmem_base + BN;
             for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
-                if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar), (local & 1) ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                const uint32_t buf = local % kAccBufs, acc_phase = (local / kAccBufs) & 1;
+                if (!mbar_wait_cluster(smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
                 tc_fence_after_sync();
-                const TileCoord tc = decode_tile(p, tile, BN);
-                for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
+                const uint32_t d_main = tmem_base + buf * 2 * BN, d_corr = d_main + BN;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
                     if (!mbar_wait_cluster(smem_u32(&full_b[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     if (!mbar_wait_cluster(smem_u32(&ready[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_base + stage * kX3StageBytes;
+                    const uint32_t sa = smem_base + stage * kStageBytes;
                     const uint32_t a_raw = ((sa >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
                     const uint32_t a_cor = (((sa + kX3TileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
                     const uint32_t b_raw = (((sa + 2 * kX3TileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
-                    const uint32_t b_cor = (((sa + 3 * kX3TileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
-                    const uint32_t first = (kb != tc.kb0);
+                    const uint32_t b_cor = (((sa + 2 * kX3TileBytes + kBTileBytes) >> 4) & 0x3fffu) | p.a.desc_lo_fixed;
+                    const uint32_t first = (kb != 0);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k)          // 32 fp32 of K: four TF32 MMAs of K = 8 (32 bytes each)
                         umma_tf32_cta2(d_main, hi64 | (a_raw + k * 2), hi64 | (b_raw + k * 2), xp.idesc_tf32, first | k);
@@ -211,67 +227,74 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (uint32_t k = 0; k < 4; ++k)          // 64 bf16 of K: four BFloat16 MMAs of K = 16 (32 bytes each)
                         umma_f16_cta2(d_corr, hi64 | (a_cor + k * 2), hi64 | (b_cor + k * 2), xp.idesc_bf16, first | k);
                     umma_commit_cta2_mc(smem_u32(&empty_bar[stage]), 3);
-                    if (++stage == stages) { stage = 0; phase ^= 1; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
-                if (ok) umma_commit_cta2_mc(smem_u32(&tmem_full_bar), 3);
+                if (ok) umma_commit_cta2_mc(smem_u32(&tmem_full_bar[buf]), 3);
             }
             if (!ok) raise_abort(kStatusMmaTimeout);
         }
     } else {
-        // ------------------------------------------------------------------ workers (both CTAs): transform, then epilogue
-        // During the reduction the eight warps write the correction tile of every stage: thread t owns half a row
-        // (row t mod 128, 16 of its 32 values).  The accumulators are not double-buffered (they fill TMEM), so the
-        // same warps drain them when the tile's last MMA has completed.
-        const uint32_t wt = threadIdx.x - 64;                       // 0 .. 255
-        const uint32_t row = wt & 127, half = wt >> 7;
+        // ------------------------------------------------------------------ transform and epilogue (both CTAs)
+        // BN = 256: warps 2-9 do both, one after the other (the accumulators fill TMEM, so there is nothing to
+        // overlap).  BN = 128: warps 2-5 are the epilogue, warps 6-13 the transform, each in its own loop.
+        const bool transforms = !kOverlap || warp >= 2 + kEpiWarps;
+        const bool drains = !kOverlap || warp < 2 + kEpiWarps;
+        const uint32_t wt = threadIdx.x - (kOverlap ? (2 + kEpiWarps) * 32 : 64);      // 0 .. 255 among the transform threads
+        const uint32_t row = wt & 127, half = wt >> 7;          // half a row of the A tile: 16 of its 32 values
         const uint32_t sw = row & 7;
         const uint32_t quarter = warp & 3;
         uint32_t stage = 0, phase = 0, local = 0;
         bool ok = true;
         for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
             const TileCoord tc = decode_tile(p, tile, BN);
-            for (uint32_t kb = tc.kb0; kb < tc.kb1; ++kb) {
-                if (!mbar_wait(smem_u32(&full_a[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
-                const uint32_t src = smem_base + stage * kX3StageBytes + row * 128;
-                const uint32_t dst = src + kX3TileBytes;
-                uint32_t x[16];
+            if (transforms) {
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&full_a[stage]), phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                    const uint32_t src = smem_base + stage * kStageBytes + row * 128;
+                    const uint32_t dst = src + kX3TileBytes;
+                    uint32_t x[16];
 #pragma unroll
-                for (uint32_t c = 0; c < 4; ++c)                 // logical 16-byte chunks 4 half .. 4 half + 3 of the row
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(x[4 * c]), "=r"(x[4 * c + 1]), "=r"(x[4 * c + 2]), "=r"(x[4 * c + 3])
-                                 : "r"(src + (((4 * half + c) ^ sw) << 4)));
-                uint32_t lo[8], hi[8];
+                    for (uint32_t c = 0; c < 4; ++c)                 // logical 16-byte chunks 4 half .. 4 half + 3 of the row
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(x[4 * c]), "=r"(x[4 * c + 1]), "=r"(x[4 * c + 2]), "=r"(x[4 * c + 3])
+                                     : "r"(src + (((4 * half + c) ^ sw) << 4)));
+                    uint32_t lo[8], hi[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    lo[e] = pack2<__nv_bfloat16>(tf32_low_part(x[2 * e]), tf32_low_part(x[2 * e + 1]));
-                    hi[e] = pack2<__nv_bfloat16>(__uint_as_float(x[2 * e]), __uint_as_float(x[2 * e + 1]));
+                    for (int e = 0; e < 8; ++e) {
+                        lo[e] = pack2<__nv_bfloat16>(tf32_low_part(x[2 * e]), tf32_low_part(x[2 * e + 1]));
+                        hi[e] = pack2<__nv_bfloat16>(__uint_as_float(x[2 * e]), __uint_as_float(x[2 * e + 1]));
+                    }
+#pragma unroll
+                    for (uint32_t c = 0; c < 2; ++c) {               // 8 values each: chunk 2 half + c of lo, chunk 4 + 2 half + c of b16
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dst + (((2 * half + c) ^ sw) << 4)), "r"(lo[4 * c]), "r"(lo[4 * c + 1]), "r"(lo[4 * c + 2]),
+                                       "r"(lo[4 * c + 3]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dst + (((4 + 2 * half + c) ^ sw) << 4)), "r"(hi[4 * c]), "r"(hi[4 * c + 1]), "r"(hi[4 * c + 2]),
+                                       "r"(hi[4 * c + 3]) : "memory");
+                    }
+                    fence_proxy_async_smem();          // generic-proxy writes -> visible to the MMA's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_remote(smem_u32(&ready[stage]), 0);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
-#pragma unroll
-                for (uint32_t j = 0; j < 2; ++j) {               // 8 values each: chunk 2 half + j of lo, chunk 4 + 2 half + j of b16
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(dst + (((2 * half + j) ^ sw) << 4)), "r"(lo[4 * j]), "r"(lo[4 * j + 1]), "r"(lo[4 * j + 2]),
-                                   "r"(lo[4 * j + 3]) : "memory");
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(dst + (((4 + 2 * half + j) ^ sw) << 4)), "r"(hi[4 * j]), "r"(hi[4 * j + 1]), "r"(hi[4 * j + 2]),
-                                   "r"(hi[4 * j + 3]) : "memory");
-                }
-                fence_proxy_async_smem();          // generic-proxy writes -> visible to the MMA's reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive_remote(smem_u32(&ready[stage]), 0);
-                if (++stage == stages) { stage = 0; phase ^= 1; }
+                if (!ok) break;
             }
-            if (!ok) break;
-            const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM;
-            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar), local & 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
-            tc_fence_after_sync();
-            drain_accumulator<float, BN, true, 2>(p, &tmap_out, smem_base + stages * kX3StageBytes + (warp - 2) * 4096, (warp - 2) >> 2,
-                                                  tmem_base, quarter, lane, tc.obatch, m0, tc.n0, tmem_base + BN);
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar), 0);
+            if (drains) {
+                const uint32_t buf = local % kAccBufs, acc_phase = (local / kAccBufs) & 1;
+                const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM;
+                if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t acc = tmem_base + buf * 2 * BN;
+                drain_accumulator<float, BN, true, kEpiWarps / 4>(p, &tmap_out, smem_base + kStages * kStageBytes + (warp - 2) * 4096,
+                                                                  (warp - 2) >> 2, acc, quarter, lane, tc.obatch, m0, tc.n0, acc + BN);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
+            }
         }
-        drain_finish(lane);
-        if (!ok && lane == 0) raise_abort(kStatusEpilogueTimeout);
+        if (drains) drain_finish(lane);
+        if (!ok && lane == 0) raise_abort(drains ? kStatusEpilogueTimeout : kStatusPairTimeout);
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -300,8 +323,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         cluster_arrive_release();
         cluster_wait_acquire();
         if (warp == 0 && lane == 0) {
-            drain_armed_stages(full_a, stages, both, &never_set);
-            if (cta_rank == 0) drain_armed_stages(full_b, stages, both, &never_set);
+            drain_armed_stages(full_a, kStages, both, &never_set);
+            if (cta_rank == 0) drain_armed_stages(full_b, kStages, both, &never_set);
         }
         __syncwarp();
         cluster_arrive_release();

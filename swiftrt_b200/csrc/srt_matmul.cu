@@ -419,17 +419,18 @@ bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool sk
         const uint64_t pack_bytes = b_items * ((Q.N + 127) / 128 * 128) * kp * 8;
         if (pack_bytes <= (256ull << 20)) {
             plan.Q = Q;
-            uint32_t stages = (uint32_t)choice.stages;
-            if (stages < 2 || stages > kX3MaxStages) stages = kX3MaxStages;
-            const uint64_t tiles = ((Q.M + 255) / 256) * ((Q.N + 255) / 256) * Q.batch;
+            // 256 x 256 tiles by default (three stages, exposed epilogue: 141 us on 65536 x 1024 x 256); 256 x 128 tiles
+            // (four stages, the epilogue under the next tile's reduction: 161 us there) on request
+            const uint32_t bn = choice.tile_n == 128 ? 128u : 256u;
+            const uint64_t tiles = ((Q.M + 255) / 256) * ((Q.N + bn - 1) / bn) * Q.batch;
             const uint64_t pairs = (uint64_t)dev.sms / 2;
             uint32_t ctas = 2u * (uint32_t)(tiles < pairs ? tiles : pairs);
             if (choice.max_ctas > 1 && ctas > (uint32_t)choice.max_ctas) ctas = (uint32_t)choice.max_ctas & ~1u;
             plan.splits = 1;
             plan.kb_per_split = (uint32_t)(kp / 32);
             plan.pub.kernel = srtMatmulKernelTf32x3Pair;
-            plan.pub.tileM = 256; plan.pub.tileN = 256; plan.pub.tileK = 32;
-            plan.pub.stages = (int32_t)stages;
+            plan.pub.tileM = 256; plan.pub.tileN = (int32_t)bn; plan.pub.tileK = 32;
+            plan.pub.stages = (int32_t)x3_stages(bn);
             plan.pub.ctas = (int32_t)ctas;
             plan.pub.tiles = (int32_t)tiles;
             plan.pub.swapped = plan.swapped;
@@ -437,7 +438,7 @@ bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool sk
             plan.pub.fp32Split = 1;
             plan.pub.splitK = 1;
             plan.pub.workspaceBytes = (size_t)pack_bytes;
-            plan.pub.dynamicSmemBytes = (size_t)stages * kX3StageBytes + kEpilogueStagingBytes + 1024;
+            plan.pub.dynamicSmemBytes = (size_t)x3_smem_bytes(bn);
             return true;
         }
     }
@@ -916,8 +917,9 @@ cudaError_t prepare_x3(const Plan& plan, Prepared& pr)
     gp.b = gp.a;                                          // the packed op(b) is K-contiguous too
     gp.b.batch_mul = (Q.batch == 1 || Q.b_b == 0) ? 0 : 1;
     gp.M = (uint32_t)Q.M; gp.N = (uint32_t)Q.N; gp.K = (uint32_t)Q.K; gp.batch = (uint32_t)Q.batch;
+    const uint32_t bn = (uint32_t)plan.pub.tileN;
     gp.tiles_m = (uint32_t)((Q.M + 255) / 256);
-    gp.tiles_n = (uint32_t)((Q.N + 255) / 256);
+    gp.tiles_n = (uint32_t)((Q.N + bn - 1) / bn);
     gp.tiles_per_batch = gp.tiles_m * gp.tiles_n;
     gp.tiles_total = (uint32_t)plan.pub.tiles;
     gp.k_splits = 1;
@@ -928,8 +930,8 @@ cudaError_t prepare_x3(const Plan& plan, Prepared& pr)
     gp.group_m = 8;
     gp.stages = (uint32_t)plan.pub.stages;
     gp.stage_tx_bytes = 0;
-    // instruction descriptors: fp32 accumulator, both operands K-major, N = 256, M = 256
-    const uint32_t shape = (1u << 4) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+    // instruction descriptors: fp32 accumulator, both operands K-major, N = tile width, M = 256
+    const uint32_t shape = (1u << 4) | ((bn >> 3) << 17) | ((256u >> 4) << 24);
     xp.idesc_tf32 = shape | (2u << 7) | (2u << 10);
     xp.idesc_bf16 = shape | (1u << 7) | (1u << 10);
     gp.out = Q.out;
@@ -951,7 +953,7 @@ cudaError_t prepare_x3(const Plan& plan, Prepared& pr)
     pk.N = (uint32_t)Q.N; pk.K = (uint32_t)Q.K; pk.Kp = gp.k_blocks * 32; pk.batch = gp.b.batch_mul ? (uint32_t)Q.batch : 1u;
     pr.kernel = srtMatmulKernelTf32x3Pair;
     pr.type = Q.type;
-    pr.bn = 256;
+    pr.bn = bn;
     pr.smem = plan.pub.dynamicSmemBytes;
     pr.ctas = (uint32_t)plan.pub.ctas;
     pr.splits = 1;
@@ -972,7 +974,7 @@ cudaError_t bind_pack(Prepared& pr, void* ws)
     {
         cuuint64_t gdim[3] = {pk.Kp, pk.N, pk.batch};
         cuuint64_t gstride[2] = {(cuuint64_t)pk.Kp * 4, (cuuint64_t)pk.Kp * 4 * pk.N};
-        cuuint32_t box[3] = {32, 128, 1}, estr[3] = {1, 1, 1};
+        cuuint32_t box[3] = {32, pr.bn / 2, 1}, estr[3] = {1, 1, 1};
         if (g_encode(&pr.mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pk.bh, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed for the packed fp32 operand");
@@ -980,7 +982,7 @@ cudaError_t bind_pack(Prepared& pr, void* ws)
     {
         cuuint64_t gdim[3] = {2ull * pk.Kp, pk.N, pk.batch};
         cuuint64_t gstride[2] = {(cuuint64_t)pk.Kp * 4, (cuuint64_t)pk.Kp * 4 * pk.N};
-        cuuint32_t box[3] = {64, 128, 1}, estr[3] = {1, 1, 1};
+        cuuint32_t box[3] = {64, pr.bn / 2, 1}, estr[3] = {1, 1, 1};
         if (g_encode(&pr.mbc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, pk.bc, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return fail(cudaErrorInvalidValue, "cuTensorMapEncodeTiled failed for the packed correction operand");
@@ -989,9 +991,10 @@ cudaError_t bind_pack(Prepared& pr, void* ws)
     return cudaSuccess;
 }
 
-cudaError_t launch_x3(const Prepared& pr, cudaStream_t stream)
+template <uint32_t BN>
+cudaError_t launch_x3_bn(const Prepared& pr, cudaStream_t stream)
 {
-    auto kernel = gemm_tf32x3_pair_kernel;
+    auto kernel = gemm_tf32x3_pair_kernel<BN>;
     static std::atomic<uint64_t> attr_done{0};
     static std::atomic<int> cluster_cache[64];
     cudaError_t e = ensure_smem_attr(kernel, attr_done, pr.smem);
@@ -1008,7 +1011,7 @@ cudaError_t launch_x3(const Prepared& pr, cudaStream_t stream)
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(pr.ctas, 1, 1);
-    cfg.blockDim = dim3(kX3Threads, 1, 1);
+    cfg.blockDim = dim3(x3_threads(BN), 1, 1);
     cfg.dynamicSmemBytes = pr.smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -1033,6 +1036,11 @@ cudaError_t launch_x3(const Prepared& pr, cudaStream_t stream)
     }
     if (pr.ctas / 2 > (uint32_t)max_clusters) cfg.gridDim.x = 2u * (uint32_t)max_clusters;
     return cudaLaunchKernelEx(&cfg, kernel, pr.ma, pr.mb, pr.mbc, pr.mo, pr.xp);
+}
+
+cudaError_t launch_x3(const Prepared& pr, cudaStream_t stream)
+{
+    return pr.bn == 256 ? launch_x3_bn<256>(pr, stream) : launch_x3_bn<128>(pr, stream);
 }
 
 // Workspaces of split-K launches: one buffer per (device, stream), grown on demand.  Kernels of

@@ -227,10 +227,12 @@ X3 = 5      # srtMatmulKernelTf32x3Pair
     (640, 136, 72, 3, True, False),
     (768, 264, 512, 0, False, True),          # column-order result: planned as the transposed problem
 ])
-def test_float32_pair_kernel_with_bf16_corrections_within_tolerance(srt, oracle, M, N, K, batch, tb, col_out):
+@pytest.mark.parametrize("tile_n", [0, 128])
+def test_float32_pair_kernel_with_bf16_corrections_within_tolerance(srt, oracle, M, N, K, batch, tb, col_out, tile_n):
     """Float32 as one TF32 pass plus BFloat16 correction terms, op(b) pre-split by the pack pass:
-    within 1e-5 of the reference loop."""
-    srt.set_tuning(X3, 0, 0, 0)
+    within 1e-5 of the reference loop.  Both tile widths: 256 (the default) and 128 (double-buffered
+    accumulators)."""
+    srt.set_tuning(X3, tile_n, 0, 0)
     rng = np.random.default_rng(M + 3 * N + 7 * K + batch + tb)
     if col_out:
         # out^T = b^T . a^T: the library sees op(a') = b^T (K-contiguous when b is stored [N x K] ... use tb)
@@ -239,7 +241,7 @@ def test_float32_pair_kernel_with_bf16_corrections_within_tolerance(srt, oracle,
         out = srt.empty((N, M), torch.float32, "cuda:0", srt.Order.col)
         srt.matmul_into(out, da, False, db, True)
         plan = srt.query_plan(da, db, out, False, True)
-        assert plan["kernel"] == X3 and plan["swapped"] == 1, plan
+        assert plan["kernel"] == X3 and plan["swapped"] == 1 and plan["tileN"] == (tile_n or 256), plan
         ref = oracle.matmul(a, b, F32, False, True)
         torch.cuda.synchronize()
         assert oracle.rel_frobenius(out.cpu().numpy(), ref) <= TOL[F32]
