@@ -158,11 +158,14 @@ def run_lstm(dev, iters: int, flush: torch.Tensor, peaks: dict, batch: int = 409
     state = srt.LSTMState(_uniform((batch, nh), bf16, dev, g, -1, 1), _uniform((batch, nh), bf16, dev, g, -1, 1))
     cell = srt.LSTMCell(_uniform((nx + nh, 4 * nh), bf16, dev, g, -0.03, 0.03), _uniform((4 * nh,), bf16, dev, g, -0.5, 0.5))
     med, best = _time_cold(lambda: cell(x, state), iters, flush)
+    fused_cell = srt.LSTMCell(cell.fused_weight, cell.fused_bias, fuse_gates=True)
+    fused_med, _ = _time_cold(lambda: fused_cell(x, state), iters, flush)
     flops = 2.0 * batch * (nx + nh) * 4 * nh
     # each tensor once: x, h, c, W, b in; c', h' out (the concatenated input and the fused product are intermediates)
     nbytes = 2 * (batch * nx + 2 * batch * nh + (nx + nh) * 4 * nh + 4 * nh + 2 * batch * nh)
     rec = {"config": "f4", "what": f"LSTM cell step bf16 batch {batch}, input {nx}, hidden {nh}",
            "kernel": "concat_kernel + gemm + lstm_gates_kernel", "ms_median": med, "ms_best": best,
+           "gates_in_epilogue_ms_median": fused_med,
            "algorithmic_flops": flops, "algorithmic_bytes": nbytes, "tflops": flops / med / 1e9, "gbs": nbytes / med / 1e6,
            "bound": "tensor", "frac_of_nominal": flops / med / 1e9 / NOMINAL["bf16_tflops"]}
     if "bf16_tflops" in peaks:

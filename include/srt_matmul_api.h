@@ -319,6 +319,34 @@ cudaError_t srtLstmCell(
     void* newHidden, const srtTensorDescriptor* newHiddenDesc,
     cudaStream_t stream);
 
+/* srtLstmCellFused: srtLstmCell with the gate pass inside the product's epilogue -- the fused product
+ * [batch x 4 hiddenSize] never reaches memory and the step is one launch (two with the concatenation).
+ * For that the four gate columns of a hidden unit must sit side by side: `interleavedWeight` and
+ * `interleavedBias` are fusedWeight / fusedBias with column 4 j + g = original column g hiddenSize + j,
+ * produced once per cell by srtLstmInterleaveGates.  Same tensors and aliasing rules as srtLstmCell otherwise
+ * (hidden may be NULL for a pre-concatenated gate input).  The gates see the fp32 pre-activations (srtLstmCell
+ * rounds the fused product to the element type first, as matmul(bias:) returns it), so results agree with
+ * srtLstmCell within the element type's rounding, not bit for bit.
+ * Float16 / BFloat16, hiddenSize a multiple of 8, row-contiguous 16-byte aligned state tensors, and a product
+ * that runs on a 16-bit tensor-core kernel in one pass; anything else returns cudaErrorNotSupported and the
+ * caller uses srtLstmCell (Recurrent.swift:255-266 is the definition of both). */
+cudaError_t srtLstmCellFused(
+    const void* input, const srtTensorDescriptor* inputDesc,
+    const void* hidden, const srtTensorDescriptor* hiddenDesc,
+    const void* cell, const srtTensorDescriptor* cellDesc,
+    const void* interleavedWeight, const srtTensorDescriptor* weightDesc,
+    const void* interleavedBias, const srtTensorDescriptor* biasDesc,
+    void* newCell, const srtTensorDescriptor* newCellDesc,
+    void* newHidden, const srtTensorDescriptor* newHiddenDesc,
+    cudaStream_t stream);
+
+/* out[.., 4 j + g] = in[.., g hiddenSize + j]: the column order srtLstmCellFused expects, for a rank-2 weight
+ * [rows x 4 hiddenSize] or a rank-1 bias [4 hiddenSize]; `out` has the shape of `in` and contiguous columns. */
+cudaError_t srtLstmInterleaveGates(
+    const void* in, const srtTensorDescriptor* inDesc,
+    void* out, const srtTensorDescriptor* outDesc,
+    cudaStream_t stream);
+
 /* srtRnnCell: one time step of BasicRNNCell (Sources/SwiftRTLayers/Recurrent.swift:110-161):
  *     newHidden = tanh(matmul(concatenate(input, hidden, axis: 1), weight) + bias)
  * weight [(inputSize + hiddenSize) x hiddenSize]; bias [hiddenSize] or, as the reference stores it,

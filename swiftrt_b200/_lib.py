@@ -43,7 +43,7 @@ EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMat
            "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell", "srtRnnCell",
            "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear",
            "srtActivationForward", "srtMatmulReleaseWorkspaces", "srtGruCell", "srtShardRange", "srtMatmulSharded",
-           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit"]
+           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit", "srtLstmCellFused", "srtLstmInterleaveGates"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -98,6 +98,10 @@ lib.srtPeerMemFree.argtypes = [_P]
 
 lib.srtLstmCell.restype = ctypes.c_int
 lib.srtLstmCell.argtypes = [_P, _D] * 7 + [_P]
+lib.srtLstmCellFused.restype = ctypes.c_int
+lib.srtLstmCellFused.argtypes = [_P, _D] * 7 + [_P]
+lib.srtLstmInterleaveGates.restype = ctypes.c_int
+lib.srtLstmInterleaveGates.argtypes = [_P, _D, _P, _D, _P]
 lib.srtRnnCell.restype = ctypes.c_int
 lib.srtRnnCell.argtypes = [_P, _D] * 5 + [_P]
 lib.srtMatmulTune.restype = ctypes.c_int

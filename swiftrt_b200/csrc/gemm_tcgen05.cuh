@@ -73,8 +73,14 @@ struct GemmParams {
     uint32_t n_peers;            // gathering kernels only: peer copies of the output view (<= kMaxPeers)
     uint32_t multicast;          // gathering kernels only: 1 = the result goes to a multicast mapping instead (no per-peer stores)
     unsigned long long wait_cycles;   // limit of every pipeline wait, in SM clock cycles (set at launch)
+    // LSTM epilogue (epilogue == kEpilogueLstm): the product's columns are the interleaved gate pre-activations
+    // (4 j + g for gate g of hidden unit j); nothing of the product is stored, the new cell and hidden states are
+    uint32_t epilogue;           // 0: bias / activation / store; 1: LSTM gates
+    const void* lstm_cell; void* lstm_new_cell; void* lstm_new_hidden;
+    long long lstm_c_m, lstm_nc_m, lstm_nh_m;   // row strides in elements (columns are contiguous)
 };
 
+enum : uint32_t { kEpilogueStore = 0, kEpilogueLstm = 1 };
 enum : uint32_t { kActSigmoid = 0, kActRelu = 1, kActTanh = 2, kActIdentity = 5, kActGelu = 6, kActGeluTanh = 7 };
 
 __device__ __forceinline__ float apply_activation(uint32_t act, float x)
@@ -355,6 +361,66 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
     }
 }
 
+// LSTM form of the epilogue.  The weight's columns were interleaved so that the four gate pre-activations of
+// hidden unit j -- input, update, forget, output (Part, Sources/SwiftRTLayers/Recurrent.swift:173) -- are columns
+// 4 j .. 4 j + 3 of the product: a thread's 32 accumulator columns are 8 whole hidden units.  Per unit
+//     cell' = cell * sigmoid(f) + sigmoid(i) * tanh(u),   hidden' = tanh(cell') * sigmoid(o)
+// (Recurrent.swift:255-266) in fp32 on the unrounded pre-activations, cell' rounded to the element type before
+// hidden' is computed from it.  The thread reads 8 cell values (16 bytes) and writes 8 + 8 (one full 32-byte
+// sector per pair of loads): no staging, the fused product itself never reaches memory.
+// 16-bit element types; hidden size a multiple of 8; state rows 16-byte aligned.
+template <typename T, uint32_t BN, uint32_t PARTS>
+__device__ __forceinline__ void drain_accumulator_lstm(const GemmParams& p, uint32_t part, uint32_t acc, uint32_t quarter,
+                                                       uint32_t lane, uint32_t m0, uint32_t n0)
+{
+    static_assert(sizeof(T) == 2, "16-bit element types");
+    constexpr uint32_t kBoxes = BN / 64;
+    const T* const bias = static_cast<const T*>(p.bias);
+    const uint32_t row = m0 + quarter * 32 + lane;
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    for (uint32_t bx = part; bx < kBoxes; bx += PARTS) {
+        const uint32_t box_col = n0 + bx * 64;
+        if (box_col >= p.N) break;                              // uniform over the warp
+        uint32_t raw[2][32];
+        tmem_ld_32x32(acc + lane_addr + bx * 64, raw[0]);
+        tmem_ld_32x32(acc + lane_addr + bx * 64 + 32, raw[1]);
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h) {
+            const uint32_t col0 = box_col + h * 32;
+            float my_bias = 0.0f;
+            if (p.bias_mode == 1 && col0 + lane < p.N)
+                my_bias = to_float<T>(__ldg(bias + static_cast<long long>(col0 + lane) * p.bias_stride));
+            const uint32_t unit0 = col0 >> 2;
+            const bool live = row < p.M && col0 < p.N;
+            __align__(16) T c[8];
+            if (live) *reinterpret_cast<uint4*>(c) = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.lstm_cell) + static_cast<long long>(row) * p.lstm_c_m + unit0);
+            if (h == 0) tmem_ld_wait_regs2(raw[0], raw[1]);
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[h][j]);
+            if (p.bias_mode == 1) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, my_bias, j);
+            }
+            __align__(16) T nc[8], nh[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float gi = __fdividef(1.0f, 1.0f + __expf(-v[4 * u]));
+                const float gu = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * v[4 * u + 1]));
+                const float gf = __fdividef(1.0f, 1.0f + __expf(-v[4 * u + 2]));
+                const float go = __fdividef(1.0f, 1.0f + __expf(-v[4 * u + 3]));
+                nc[u] = from_float<T>(__fadd_rn(__fmul_rn(to_float<T>(c[u]), gf), __fmul_rn(gi, gu)));
+                const float tc = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * to_float<T>(nc[u])));
+                nh[u] = from_float<T>(__fmul_rn(tc, go));
+            }
+            if (live) {
+                *reinterpret_cast<uint4*>(static_cast<T*>(p.lstm_new_cell) + static_cast<long long>(row) * p.lstm_nc_m + unit0) = *reinterpret_cast<const uint4*>(nc);
+                *reinterpret_cast<uint4*>(static_cast<T*>(p.lstm_new_hidden) + static_cast<long long>(row) * p.lstm_nh_m + unit0) = *reinterpret_cast<const uint4*>(nh);
+            }
+        }
+    }
+}
+
 // Before a warp leaves the kernel (or shared memory is reused for something else) its lane 0
 // waits for all its bulk stores.
 __device__ __forceinline__ void drain_finish(uint32_t lane)
@@ -532,7 +598,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 drain_accumulator<OutT, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                             (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
                                                             0, &peer_maps);
-            else
+            else if (sizeof(OutT) == 2 && p.epilogue == kEpilogueLstm) {
+                if constexpr (sizeof(OutT) == 2)
+                    drain_accumulator_lstm<OutT, BN, 2>(p, (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, m0, n0);
+            } else
                 drain_accumulator<OutT, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                       (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();
@@ -764,7 +833,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 drain_accumulator<T, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                          (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
                                                          0, &peer_maps);
-            else
+            else if (sizeof(T) == 2 && p.epilogue == kEpilogueLstm) {
+                if constexpr (sizeof(T) == 2)
+                    drain_accumulator_lstm<T, BN, 2>(p, (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, m0, n0);
+            } else
                 drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                    (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
             tc_fence_before_sync();

@@ -112,6 +112,29 @@ lstm_gates_kernel(const LstmGateParams p)
     }
 }
 
+// Column order for the fused LSTM epilogue: out[r][4 j + g] = in[r][g hidden + j], i.e. the four gate columns of
+// hidden unit j side by side (the reference keeps the gates as four column blocks, Recurrent.swift:173, 203-213).
+// Run once per weight (and bias, rows = 1) when a cell is built.
+struct InterleaveParams {
+    const void* in; void* out;
+    long long in_m, in_n, out_m;         // element strides (out columns are contiguous)
+    uint32_t rows, hidden;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+lstm_interleave_kernel(const InterleaveParams p)
+{
+    const unsigned long long cols = 4ull * p.hidden, total = cols * p.rows;
+    const T* in = static_cast<const T*>(p.in);
+    T* out = static_cast<T*>(p.out);
+    for (unsigned long long i = blockIdx.x * 256ull + threadIdx.x; i < total; i += gridDim.x * 256ull) {
+        const uint32_t r = static_cast<uint32_t>(i / cols), c = static_cast<uint32_t>(i % cols);
+        const uint32_t j = c >> 2, g = c & 3;
+        out[static_cast<long long>(r) * p.out_m + c] = in[static_cast<long long>(r) * p.in_m + static_cast<long long>(g * p.hidden + j) * p.in_n];
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // GRU cell (Sources/SwiftRTLayers/Recurrent.swift:328-337), around two fused products:
 //     [reset | update] = sigmoid([x | h] . [[resetW1 | updateW1], [resetW2 | updateW2]] + [resetB | updateB])

@@ -2003,6 +2003,125 @@ cudaError_t srtLstmCell(const void* input, const srtTensorDescriptor* inputDesc,
                              : launch_lstm_elementwise<__nv_bfloat16>(nullptr, &gp, stream);
 }
 
+// ------------------------------------------------------------------ srtLstmCellFused
+cudaError_t srtLstmInterleaveGates(const void* in, const srtTensorDescriptor* inDesc, void* out, const srtTensorDescriptor* outDesc,
+                                   cudaStream_t stream)
+{
+    if (!in || !out || !inDesc || !outDesc || !inDesc->shape || !inDesc->strides || !outDesc->shape || !outDesc->strides)
+        return fail(cudaErrorInvalidValue, "srtLstmInterleaveGates: null tensor or descriptor");
+    if (inDesc->rank != outDesc->rank || (inDesc->rank != 1 && inDesc->rank != 2) || inDesc->type != outDesc->type)
+        return fail(cudaErrorInvalidValue, "srtLstmInterleaveGates: in and out must be rank 1 or 2 tensors of one type and rank");
+    const uint32_t q = inDesc->rank - 1;
+    const uint64_t rows = inDesc->rank == 2 ? inDesc->shape[0] : 1, cols = inDesc->shape[q];
+    if (cols % 4 || outDesc->shape[q] != cols || (inDesc->rank == 2 && outDesc->shape[0] != rows) || outDesc->strides[q] != 1)
+        return fail(cudaErrorInvalidValue, "srtLstmInterleaveGates: 4 hiddenSize columns expected, out of the same shape with contiguous columns");
+    if (elem_size(inDesc->type) == 0) return fail(cudaErrorNotSupported, "element type %d is not computed by this library", (int)inDesc->type);
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    if (rows > 0xffffffffull || cols > 0xffffffffull) return fail(cudaErrorNotSupported, "srtLstmInterleaveGates: extents beyond 32 bits");
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    InterleaveParams ip;
+    ip.in = in; ip.out = out;
+    ip.in_m = inDesc->rank == 2 ? (long long)inDesc->strides[0] : 0; ip.in_n = (long long)inDesc->strides[q];
+    ip.out_m = outDesc->rank == 2 ? (long long)outDesc->strides[0] : 0;
+    ip.rows = (uint32_t)rows; ip.hidden = (uint32_t)(cols / 4);
+    unsigned long long blocks = (rows * cols + 255) / 256;
+    if (blocks > 148ull * 16) blocks = 148ull * 16;
+    switch (inDesc->type) {
+    case real32F: lstm_interleave_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(ip); break;
+    case real16F: lstm_interleave_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(ip); break;
+    default: lstm_interleave_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(ip); break;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
+cudaError_t srtLstmCellFused(const void* input, const srtTensorDescriptor* inputDesc, const void* hidden,
+                             const srtTensorDescriptor* hiddenDesc, const void* cell, const srtTensorDescriptor* cellDesc,
+                             const void* interleavedWeight, const srtTensorDescriptor* weightDesc, const void* interleavedBias,
+                             const srtTensorDescriptor* biasDesc, void* newCell, const srtTensorDescriptor* newCellDesc,
+                             void* newHidden, const srtTensorDescriptor* newHiddenDesc, cudaStream_t stream)
+{
+    if (!input || !cell || !interleavedWeight || !newCell || !newHidden || !inputDesc)
+        return fail(cudaErrorInvalidValue, "srtLstmCellFused: null tensor");
+    const srtDataType type = inputDesc->type;
+    if (type != real16F && type != real16BF)
+        return fail(cudaErrorNotSupported, "srtLstmCellFused: 16-bit element types only; use srtLstmCell");
+    uint64_t rows, nx, r2, nh, r3, c3, wk, wn, r4, c4, r5, c5;
+    long long x_m, x_n, h_m = 0, h_n = 0, c_m, c_n, w_m, w_n, nc_m, nc_n, nh_m, nh_n;
+    cudaError_t e;
+    if ((e = view2(inputDesc, "input", type, rows, nx, x_m, x_n)) != cudaSuccess) return e;
+    const bool preconcatenated = hidden == nullptr;
+    if ((e = view2(cellDesc, "cell", type, r3, c3, c_m, c_n)) != cudaSuccess) return e;
+    nh = c3;
+    if (preconcatenated) {
+        if (nx < nh) return fail(cudaErrorInvalidValue, "srtLstmCellFused: a gate input has at least hiddenSize columns");
+        nx -= nh;
+        r2 = rows;
+    } else {
+        uint64_t hcols;
+        if ((e = view2(hiddenDesc, "hidden", type, r2, hcols, h_m, h_n)) != cudaSuccess) return e;
+        if (hcols != nh) return fail(cudaErrorInvalidValue, "srtLstmCellFused: hidden and cell must have the same shape");
+    }
+    if ((e = view2(weightDesc, "interleavedWeight", type, wk, wn, w_m, w_n)) != cudaSuccess) return e;
+    if ((e = view2(newCellDesc, "newCell", type, r4, c4, nc_m, nc_n)) != cudaSuccess) return e;
+    if ((e = view2(newHiddenDesc, "newHidden", type, r5, c5, nh_m, nh_n)) != cudaSuccess) return e;
+    if (r2 != rows || r3 != rows || r4 != rows || r5 != rows || c4 != nh || c5 != nh)
+        return fail(cudaErrorInvalidValue, "srtLstmCellFused: state tensors must be [batch x hiddenSize]");
+    if (wk != nx + nh || wn != 4 * nh)
+        return fail(cudaErrorInvalidValue, "srtLstmCellFused: interleavedWeight must be [(inputSize + hiddenSize) x 4 hiddenSize]");
+    if (interleavedBias && (!biasDesc || biasDesc->rank != 1 || biasDesc->shape[0] != 4 * nh || biasDesc->type != type))
+        return fail(cudaErrorInvalidValue, "srtLstmCellFused: interleavedBias must be rank 1 with 4 hiddenSize elements");
+    if (rows == 0 || nh == 0) return cudaSuccess;
+    // the epilogue moves 8 hidden units (16 bytes) per access
+    const bool state_ok = nh % 8 == 0 && c_n == 1 && nc_n == 1 && nh_n == 1 && aligned16(cell, c_m, 2) && aligned16(newCell, nc_m, 2) &&
+                          aligned16(newHidden, nh_m, 2);
+    if (!state_ok || rows > 0x7fffffffull || nx + nh > 0x7fffffffull)
+        return fail(cudaErrorNotSupported, "srtLstmCellFused: hiddenSize must be a multiple of 8 and the state tensors row-contiguous and "
+                                           "16-byte aligned; use srtLstmCell");
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+
+    // the gate input: the caller's, or the concatenation staged in the workspace
+    const void* gate_in = input;
+    long long g_m = x_m, g_n = x_n;
+    if (!preconcatenated) {
+        void* ws = nullptr;
+        if ((e = workspace_for(scope.device, stream, (size_t)rows * (nx + nh) * 2, &ws, 1)) != cudaSuccess) return e;
+        ConcatParams cp;
+        cp.x = input; cp.h = hidden; cp.out = ws;
+        cp.x_m = x_m; cp.x_n = x_n; cp.h_m = h_m; cp.h_n = h_n;
+        cp.rows = (uint32_t)rows; cp.nx = (uint32_t)nx; cp.nh = (uint32_t)nh;
+        e = type == real16F ? launch_lstm_elementwise<__half>(&cp, nullptr, stream) : launch_lstm_elementwise<__nv_bfloat16>(&cp, nullptr, stream);
+        if (e != cudaSuccess) return e;
+        gate_in = ws; g_m = (long long)(nx + nh); g_n = 1;
+    }
+    // the product [batch x (inputSize + hiddenSize)] . [.. x 4 hiddenSize] as the planner sees it; its "result" is never stored
+    Problem P;
+    memset(&P, 0, sizeof P);
+    P.type = type; P.elem = 2;
+    P.batch = 1; P.M = rows; P.N = 4 * nh; P.K = nx + nh;
+    P.a = static_cast<const char*>(gate_in); P.a_m = g_m; P.a_k = g_n;
+    P.b = static_cast<const char*>(interleavedWeight); P.b_k = w_m; P.b_n = w_n;
+    P.out = static_cast<char*>(newCell);               // an aligned stand-in: the LSTM epilogue writes no product
+    P.o_m = (long long)(4 * nh); P.o_n = 1;
+    P.bias = static_cast<const char*>(interleavedBias); P.bias_stride = interleavedBias ? (long long)biasDesc->strides[0] : 0;
+    P.act = kActIdentity;
+    Plan plan;
+    if ((e = plan_for(P, plan)) != cudaSuccess) return e;
+    if ((plan.pub.kernel != srtMatmulKernelTcgen05 && plan.pub.kernel != srtMatmulKernelTcgen05Pair) || plan.splits > 1 || plan.swapped)
+        return fail(cudaErrorNotSupported, "srtLstmCellFused: this product does not run on a 16-bit tensor-core kernel in one pass; use srtLstmCell");
+    std::unique_ptr<Prepared> pr(new Prepared());
+    if ((e = prepare_tc(plan, *pr)) != cudaSuccess) return e;
+    GemmParams& gp = pr->gp;
+    gp.epilogue = kEpilogueLstm;
+    gp.out = nullptr; gp.out_tma = 0;
+    gp.lstm_cell = cell; gp.lstm_new_cell = newCell; gp.lstm_new_hidden = newHidden;
+    gp.lstm_c_m = c_m; gp.lstm_nc_m = nc_m; gp.lstm_nh_m = nh_m;
+    return launch_prepared(*pr, stream);
+}
+
 // ------------------------------------------------------------------ srtRnnCell
 cudaError_t srtRnnCell(const void* input, const srtTensorDescriptor* inputDesc, const void* hidden,
                        const srtTensorDescriptor* hiddenDesc, const void* weight, const srtTensorDescriptor* weightDesc,

@@ -25,7 +25,13 @@ class LSTMCell:
     """fusedWeight [(inputSize + hiddenSize) x 4 hiddenSize], fusedBias [4 hiddenSize]; the four
     column blocks are the input, update, forget and output gates (Part, Recurrent.swift:173)."""
 
-    def __init__(self, fused_weight: torch.Tensor, fused_bias: torch.Tensor | None, hidden_size: int | None = None):
+    def __init__(self, fused_weight: torch.Tensor, fused_bias: torch.Tensor | None, hidden_size: int | None = None,
+                 fuse_gates: bool = False):
+        """`fuse_gates`: run the gate pass inside the product's epilogue (srtLstmCellFused) when the step is
+        eligible -- 16-bit elements, hiddenSize a multiple of 8, a one-pass tensor-core product -- and fall
+        back to the three-launch step otherwise.  The interleaved copies of weight and bias are made once, here."""
+        self.fuse_gates = bool(fuse_gates)
+        self._interleaved = None
         if fused_weight.dim() != 2 or fused_weight.shape[1] % 4:
             raise ValueError("fusedWeight must be [(inputSize + hiddenSize) x 4 hiddenSize]")
         self.fused_weight = fused_weight
@@ -35,6 +41,23 @@ class LSTMCell:
             raise ValueError("fusedWeight has 4 hiddenSize columns")
         if fused_bias is not None and tuple(fused_bias.shape) != (4 * self.hidden_size,):
             raise ValueError("fusedBias has 4 hiddenSize elements")
+
+    def interleaved(self):
+        """(weight, bias) with the four gate columns of every hidden unit side by side (srtLstmInterleaveGates)."""
+        if self._interleaved is None:
+            w = torch.empty_like(self.fused_weight, memory_format=torch.contiguous_format)
+            b = torch.empty_like(self.fused_bias, memory_format=torch.contiguous_format) if self.fused_bias is not None else None
+            with torch.cuda.device(w.device):
+                stream = torch.cuda.current_stream(w.device).cuda_stream
+                for src, dst in ((self.fused_weight, w), (self.fused_bias, b)):
+                    if src is None:
+                        continue
+                    ds, dd = _descriptor(src), _descriptor(dst)
+                    rc = lib.srtLstmInterleaveGates(src.data_ptr(), ds.ref(), dst.data_ptr(), dd.ref(), stream)
+                    if rc != _lib.cudaSuccess:
+                        raise MatmulError(rc, _lib.last_error())
+            self._interleaved = (w, b)
+        return self._interleaved
 
     def zero_state(self, input: torch.Tensor) -> LSTMState:
         """zeroState(for:) (Recurrent.swift:245-248)."""
@@ -49,19 +72,24 @@ class LSTMCell:
             raise ValueError("device tensors expected")
         new_cell = torch.empty_like(state.cell, memory_format=torch.contiguous_format)
         new_hidden = torch.empty_like(state.hidden, memory_format=torch.contiguous_format)
-        tensors = (input, state.hidden, state.cell, self.fused_weight, self.fused_bias, new_cell, new_hidden)
+        _lstm_call(self, input, state.hidden, state.cell, new_cell, new_hidden)
+        return LSTMState(new_cell, new_hidden)
+
+
+def _lstm_call(cell: "LSTMCell", input, hidden, cell_state, new_cell, new_hidden) -> None:
+    if cell.fuse_gates and input.dtype in (torch.float16, torch.bfloat16):
+        w, b = cell.interleaved()
+        tensors = (input, hidden, cell_state, w, b, new_cell, new_hidden)
         descs = [_descriptor(t) if t is not None else None for t in tensors]
         args = []
         for t, d in zip(tensors, descs):
             args += [t.data_ptr() if t is not None else None, d.ref() if d is not None else None]
         with torch.cuda.device(input.device):
-            rc = lib.srtLstmCell(*args, torch.cuda.current_stream(input.device).cuda_stream)
-        if rc != _lib.cudaSuccess:
+            rc = lib.srtLstmCellFused(*args, torch.cuda.current_stream(input.device).cuda_stream)
+        if rc == _lib.cudaSuccess:
+            return
+        if rc != _lib.cudaErrorNotSupported:
             raise MatmulError(rc, _lib.last_error())
-        return LSTMState(new_cell, new_hidden)
-
-
-def _lstm_call(cell: "LSTMCell", input, hidden, cell_state, new_cell, new_hidden) -> None:
     tensors = (input, hidden, cell_state, cell.fused_weight, cell.fused_bias, new_cell, new_hidden)
     descs = [_descriptor(t) if t is not None else None for t in tensors]
     args = []

@@ -252,3 +252,59 @@ def test_gru_cell_matches_operator_by_operator_composition(srt, oracle, dtype, b
     want2 = oracle.gru_cell(x, want, w, dtype)
     got2 = cell(to_dev(x, dtype), got)
     assert oracle.rel_frobenius(oracle.decode(from_dev(got2, dtype), dtype), oracle.decode(want2, dtype)) <= 2 * tol
+
+
+@pytest.mark.parametrize("dtype,batch,nx,nh", [(BF16, 512, 256, 256), (F16, 300, 136, 72), (BF16, 4096, 1024, 1024)])
+def test_lstm_step_with_gates_in_the_product_epilogue(srt, oracle, dtype, batch, nx, nh):
+    """srtLstmCellFused: the gate pass runs on the accumulators of the product over an interleaved
+    weight; new cell and hidden states against the oracle (which rounds the fused product to the element
+    type first, as the reference's matmul(bias:) does: tolerance, not bit equality) and against the
+    three-launch step."""
+    rng = np.random.default_rng(batch + nx + nh)
+    w = to_dev(random_bits(oracle, rng, (nx + nh, 4 * nh), dtype, scale=1.0 / np.sqrt(nx + nh)), dtype)
+    b = to_dev(random_bits(oracle, rng, (4 * nh,), dtype, scale=0.5), dtype)
+    x_bits, h_bits, c_bits = (random_bits(oracle, rng, (batch, n), dtype) for n in (nx, nh, nh))
+    plain = srt.LSTMCell(w, b)
+    fused = srt.LSTMCell(w, b, fuse_gates=True)
+    wi, bi = fused.interleaved()
+    torch.cuda.synchronize()
+    assert torch.equal(wi, w.reshape(nx + nh, 4, nh).transpose(1, 2).reshape(nx + nh, 4 * nh))
+    assert torch.equal(bi, b.reshape(4, nh).t().reshape(4 * nh))
+    x, state = to_dev(x_bits, dtype), srt.LSTMState(to_dev(c_bits, dtype), to_dev(h_bits, dtype))
+    ref = plain(x, state)
+    before = srt.launch_count()
+    got = fused(x, state)
+    torch.cuda.synchronize()
+    assert srt.launch_count() - before == 2              # concatenation + the product with its gate epilogue
+    assert srt.check_status() == 0
+    if batch <= 512:
+        want_c, want_h = oracle.lstm_cell(x_bits, h_bits, c_bits, from_dev(w, dtype), from_dev(b, dtype), dtype)
+        for g, wnt in ((got.cell, want_c), (got.hidden, want_h)):
+            assert oracle.rel_frobenius(oracle.decode(from_dev(g, dtype), dtype), oracle.decode(wnt, dtype)) <= TOL[dtype]
+    for g, r in ((got.cell, ref.cell), (got.hidden, ref.hidden)):
+        assert oracle.rel_frobenius(oracle.decode(from_dev(g, dtype), dtype), oracle.decode(from_dev(r, dtype), dtype)) <= TOL[dtype]
+    # a sequence with the hidden state kept inside the next step's gate input: one launch per step
+    xs = [to_dev(random_bits(oracle, rng, (batch, nx), dtype), dtype) for _ in range(3)]
+    before = srt.launch_count()
+    seq = srt.run_sequence_preconcatenated(fused, xs)
+    torch.cuda.synchronize()
+    assert srt.launch_count() - before == 3
+    seq_ref = srt.run_sequence(plain, xs)
+    for a, r in zip(seq, seq_ref):
+        assert oracle.rel_frobenius(oracle.decode(from_dev(a.hidden, dtype), dtype), oracle.decode(from_dev(r.hidden, dtype), dtype)) <= 2 * TOL[dtype]
+    assert srt.check_status() == 0
+
+
+def test_fused_lstm_step_falls_back_when_not_eligible(srt, oracle):
+    rng = np.random.default_rng(9)
+    batch, nx, nh = 64, 40, 12                       # hiddenSize not a multiple of 8
+    w = to_dev(random_bits(oracle, rng, (nx + nh, 4 * nh), BF16, scale=0.1), BF16)
+    b = to_dev(random_bits(oracle, rng, (4 * nh,), BF16, scale=0.5), BF16)
+    x = to_dev(random_bits(oracle, rng, (batch, nx), BF16), BF16)
+    state = srt.LSTMState(to_dev(random_bits(oracle, rng, (batch, nh), BF16), BF16), to_dev(random_bits(oracle, rng, (batch, nh), BF16), BF16))
+    ref = srt.LSTMCell(w, b)(x, state)
+    before = srt.launch_count()
+    got = srt.LSTMCell(w, b, fuse_gates=True)(x, state)
+    torch.cuda.synchronize()
+    assert srt.launch_count() - before >= 3 + 2      # the two interleave passes, then the ordinary three-launch step
+    assert torch.equal(got.cell, ref.cell) and torch.equal(got.hidden, ref.hidden)
