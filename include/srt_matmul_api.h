@@ -397,6 +397,16 @@ cudaError_t srtPeerMemAlloc(size_t bytes, void** ptr, srtPeerMemHandle* handle);
 /* Maps another rank's buffer into this process (peer access is enabled on demand).  A process
  * cannot open its own handle. */
 cudaError_t srtPeerMemOpen(const srtPeerMemHandle* handle, void** ptr);
+/* Ordering the ranks without a collective.  Each rank keeps an array of (at most 8) 64-bit flags in a buffer
+ * from srtPeerMemAlloc, zeroed once, slot r belonging to rank r.
+ * srtPeerSignal enqueues on `stream`: after everything enqueued before it, store `epoch` into slot `slot` (this
+ * rank's) of every array in peerFlags (the other ranks' arrays, mapped with srtPeerMemOpen).
+ * srtPeerWait enqueues on `stream`: wait until every slot of this rank's own array except `skipSlot` holds a
+ * value >= epoch; what follows on the stream then sees what those ranks stored before their signal.  The wait
+ * is bounded (timeoutNs, 0 = 2 s): when it runs out, bit 4 of the status word (srtMatmulCheckStatus) is set and
+ * the stream continues.  Use increasing epochs (1, 2, ...).  Every GPU runs only its own two small kernels. */
+cudaError_t srtPeerSignal(void* const* peerFlags, int32_t peerCount, int32_t slot, uint64_t epoch, cudaStream_t stream);
+cudaError_t srtPeerWait(const void* localFlags, int32_t slots, int32_t skipSlot, uint64_t epoch, uint64_t timeoutNs, cudaStream_t stream);
 /* Unmaps a pointer obtained from srtPeerMemOpen. */
 cudaError_t srtPeerMemClose(void* ptr);
 /* Frees a buffer obtained from srtPeerMemAlloc (after every peer has closed its mapping). */
@@ -482,6 +492,8 @@ cudaError_t srtMatmulSharded(
  * and out[i] are that device's copies of the full tensors.  Block i is enqueued on streams[i]; with
  * `gather` every block is also stored into the other devices' result buffers (peer access is
  * enabled on demand), so that after all streams have drained every out[i] holds the whole result.
+ * `multicastOut` (may be NULL; used with `gather`): the multicast mapping of the out[] buffers when they come from
+ * srtMulticastAlloc -- eligible products then store every tile once and the NVSwitch replicates it.
  * At most 8 devices.  Returns after enqueuing; synchronise every stream before reading. */
 cudaError_t srtMatmulShardedDevices(
     srtShardAxis axis, int32_t nDevices, const cudaStream_t* streams,
@@ -490,7 +502,23 @@ cudaError_t srtMatmulShardedDevices(
     const void* const* bias, const srtTensorDescriptor* biasDesc,
     srtActivationType activation,
     void* const* out, const srtTensorDescriptor* oDesc,
-    bool gather);
+    bool gather, void* multicastOut);
+
+/* NVLink multicast buffers for ONE process that drives several GPUs: one physical allocation of `bytes`
+ * (rounded up to the multicast granularity) on each device, all bound to one multicast object.
+ * localPtrs[i] is device i's buffer (addressable from every listed device), *multicastPtr the multicast
+ * mapping: a multimem store to it lands in every device's buffer at the same offset -- what
+ * srtMatmulAllGatherMulticast / srtMatmulShardedDevices(…, multicastOut) write through.  Built on the driver's
+ * virtual-memory and multicast entry points (cuMulticastCreate / cuMulticastBindMem / cuMemMap), obtained at
+ * run time; cudaErrorNotSupported when a device or the driver has no multicast.  The reference has no counterpart
+ * (its device memory is one cub-cached cudaMalloc per tensor, Modules/SwiftRTCuda/memory.cu:31-41).
+ * Processes that each own one GPU exchange such allocations through file descriptors instead; that plumbing
+ * is not part of this library (torch.distributed._symmetric_memory provides it for the Python mirror). */
+typedef void* srtMulticastBuffer;
+cudaError_t srtMulticastAlloc(int32_t nDevices, const int32_t* devices, size_t bytes, void** localPtrs, void** multicastPtr,
+                              srtMulticastBuffer* handle);
+/* Synchronises the devices, unmaps and frees everything srtMulticastAlloc made. */
+cudaError_t srtMulticastFree(srtMulticastBuffer handle);
 
 /* Wall-clock limit of every pipeline wait inside the tensor-core kernels of the current device, in
  * nanoseconds (0 restores the default of 2 s).  A wait that runs out ends its kernel in an orderly

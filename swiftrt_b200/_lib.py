@@ -43,7 +43,7 @@ EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMat
            "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell", "srtRnnCell",
            "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear",
            "srtActivationForward", "srtMatmulReleaseWorkspaces", "srtGruCell", "srtShardRange", "srtMatmulSharded",
-           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit", "srtLstmCellFused", "srtLstmInterleaveGates"]
+           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit", "srtLstmCellFused", "srtLstmInterleaveGates", "srtPeerSignal", "srtPeerWait", "srtMulticastAlloc", "srtMulticastFree"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -91,6 +91,10 @@ lib.srtPeerMemAlloc.restype = ctypes.c_int
 lib.srtPeerMemAlloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(PeerMemHandle)]
 lib.srtPeerMemOpen.restype = ctypes.c_int
 lib.srtPeerMemOpen.argtypes = [ctypes.POINTER(PeerMemHandle), ctypes.POINTER(ctypes.c_void_p)]
+lib.srtPeerSignal.restype = ctypes.c_int
+lib.srtPeerSignal.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, _P]
+lib.srtPeerWait.restype = ctypes.c_int
+lib.srtPeerWait.argtypes = [_P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, _P]
 lib.srtPeerMemClose.restype = ctypes.c_int
 lib.srtPeerMemClose.argtypes = [_P]
 lib.srtPeerMemFree.restype = ctypes.c_int
@@ -132,7 +136,12 @@ lib.srtMatmulShardedDevices.argtypes = [ctypes.c_int, ctypes.c_int32, ctypes.POI
                                         ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool,
                                         ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool,
                                         ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_int,
-                                        ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool]
+                                        ctypes.POINTER(ctypes.c_void_p), _D, ctypes.c_bool, _P]
+lib.srtMulticastAlloc.restype = ctypes.c_int
+lib.srtMulticastAlloc.argtypes = [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p),
+                                  ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]
+lib.srtMulticastFree.restype = ctypes.c_int
+lib.srtMulticastFree.argtypes = [_P]
 lib.srtMatmulSetWaitLimit.restype = ctypes.c_int
 lib.srtMatmulSetWaitLimit.argtypes = [ctypes.c_uint64]
 

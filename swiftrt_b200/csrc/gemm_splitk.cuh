@@ -134,4 +134,48 @@ splitk_reduce_transposed_kernel(const ReduceParams p)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Ordering the ranks of one machine without a collective.  Every rank owns an array of 64-bit flags in
+// peer-mapped memory, one slot per rank.  After its product a rank writes the step's number into ITS slot
+// of every peer's array (peer_signal_kernel: system-scope fence, then the stores); before it reads what
+// the others wrote it waits until every other slot of its own array has reached that number
+// (peer_wait_kernel).  Each GPU runs only its own two kernels, so nothing here waits for another launch
+// on the same GPU.  The wait is bounded: when the limit runs out it sets kStatusPeerTimeout in the status
+// word and returns, and the stream goes on.
+constexpr uint32_t kStatusPeerTimeout = 16u;
+constexpr int kMaxFlagSlots = 8;
+
+struct PeerSignalParams {
+    unsigned long long* peer_flags[kMaxFlagSlots];     // the other ranks' flag arrays, mapped into this process
+    int count;
+    int slot;                                          // this rank's slot
+    unsigned long long epoch;
+};
+
+__global__ void peer_signal_kernel(const PeerSignalParams p)
+{
+    if (threadIdx.x < static_cast<unsigned>(p.count)) {
+        __threadfence_system();                        // everything this GPU stored before is visible before the flag
+        *reinterpret_cast<volatile unsigned long long*>(p.peer_flags[threadIdx.x] + p.slot) = p.epoch;
+    }
+}
+
+__global__ void peer_wait_kernel(const volatile unsigned long long* flags, int slots, int skip, unsigned long long epoch,
+                                 unsigned long long limit_cycles)
+{
+    if (threadIdx.x != 0) return;
+    const long long t0 = clock64();
+    for (int s = 0; s < slots; ++s) {
+        if (s == skip) continue;
+        while (flags[s] < epoch) {
+            if (static_cast<unsigned long long>(clock64() - t0) > limit_cycles) {
+                atomicOr(&g_gemm_status, kStatusPeerTimeout);
+                return;
+            }
+            __nanosleep(200);
+        }
+    }
+    __threadfence_system();                            // what follows on this stream sees the peers' stores
+}
+
 }  // namespace srt

@@ -1499,6 +1499,79 @@ cudaError_t launch_lstm_elementwise(const ConcatParams* cp, const LstmGateParams
     return e;
 }
 
+// ------------------------------------------------------------------ driver entry points for multicast buffers
+struct DriverApi {
+    CUresult (*MulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags) = nullptr;
+    CUresult (*MulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*) = nullptr;
+    CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice) = nullptr;
+    CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t, unsigned long long) = nullptr;
+    CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
+    CUresult (*MemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+    CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
+    CUresult (*MemAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+    CUresult (*MemAddressFree)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*MemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+    CUresult (*MemUnmap)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+    CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice) = nullptr;
+    bool ok = false;
+};
+
+template <typename F>
+bool driver_symbol(const char* name, F& fn)
+{
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) return false;
+    fn = reinterpret_cast<F>(p);
+    return true;
+}
+
+const DriverApi& driver_api()
+{
+    static DriverApi api = [] {
+        DriverApi d;
+        d.ok = driver_symbol("cuMulticastGetGranularity", d.MulticastGetGranularity) && driver_symbol("cuMulticastCreate", d.MulticastCreate) &&
+               driver_symbol("cuMulticastAddDevice", d.MulticastAddDevice) && driver_symbol("cuMulticastBindMem", d.MulticastBindMem) &&
+               driver_symbol("cuMulticastUnbind", d.MulticastUnbind) && driver_symbol("cuMemCreate", d.MemCreate) &&
+               driver_symbol("cuMemRelease", d.MemRelease) && driver_symbol("cuMemAddressReserve", d.MemAddressReserve) &&
+               driver_symbol("cuMemAddressFree", d.MemAddressFree) && driver_symbol("cuMemMap", d.MemMap) &&
+               driver_symbol("cuMemUnmap", d.MemUnmap) && driver_symbol("cuMemSetAccess", d.MemSetAccess) &&
+               driver_symbol("cuDeviceGetAttribute", d.DeviceGetAttribute);
+        return d;
+    }();
+    return api;
+}
+
+struct MulticastBuffer {
+    int n = 0;
+    int devices[kMaxPeers + 1] = {};
+    size_t size = 0;
+    CUmemGenericAllocationHandle mc = 0;
+    CUmemGenericAllocationHandle mem[kMaxPeers + 1] = {};
+    CUdeviceptr va[kMaxPeers + 1] = {};
+    CUdeviceptr mc_va = 0;
+    bool bound[kMaxPeers + 1] = {};
+};
+
+void multicast_destroy(MulticastBuffer* b)
+{
+    const DriverApi& d = driver_api();
+    for (int i = 0; i < b->n; ++i) {
+        cudaSetDevice(b->devices[i]);
+        cudaDeviceSynchronize();
+    }
+    if (b->mc_va) { d.MemUnmap(b->mc_va, b->size); d.MemAddressFree(b->mc_va, b->size); }
+    for (int i = 0; i < b->n; ++i) {
+        if (b->va[i]) { d.MemUnmap(b->va[i], b->size); d.MemAddressFree(b->va[i], b->size); }
+        if (b->bound[i]) d.MulticastUnbind(b->mc, b->devices[i], 0, b->size);
+        if (b->mem[i]) d.MemRelease(b->mem[i]);
+    }
+    if (b->mc) d.MemRelease(b->mc);
+    delete b;
+}
+
+
 // ------------------------------------------------------------------ one product
 // Parses, plans (or finds the prepared launch of an identical earlier call) and enqueues.
 // `no_alloc`: split-K partial sums go to the static scratch array; products whose partial sums do
@@ -2402,7 +2475,7 @@ cudaError_t srtMatmulShardedDevices(srtShardAxis axis, int32_t nDevices, const c
                                     const srtTensorDescriptor* aDesc, bool transA, const void* const* b,
                                     const srtTensorDescriptor* bDesc, bool transB, const void* const* bias,
                                     const srtTensorDescriptor* biasDesc, srtActivationType activation, void* const* out,
-                                    const srtTensorDescriptor* oDesc, bool gather)
+                                    const srtTensorDescriptor* oDesc, bool gather, void* multicastOut)
 {
     if (nDevices < 1 || nDevices > (int32_t)kMaxPeers + 1 || !streams || !a || !b || !out)
         return fail(cudaErrorInvalidValue, "srtMatmulShardedDevices: 1..%u devices with their streams and buffers expected", kMaxPeers + 1);
@@ -2435,9 +2508,91 @@ cudaError_t srtMatmulShardedDevices(srtShardAxis axis, int32_t nDevices, const c
             for (int32_t j = 0; j < nDevices; ++j)
                 if (j != i) peers[count++] = out[j];
         cudaError_t e = srtMatmulSharded(axis, nDevices, i, a[i], aDesc, transA, b[i], bDesc, transB, bias ? bias[i] : nullptr, biasDesc,
-                                         activation, out[i], oDesc, count, peers, nullptr, streams[i]);
+                                         activation, out[i], oDesc, count, peers, gather ? multicastOut : nullptr, streams[i]);
         if (e != cudaSuccess) return e;
     }
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ NVLink multicast buffers (one process, several devices)
+cudaError_t srtMulticastAlloc(int32_t nDevices, const int32_t* devices, size_t bytes, void** localPtrs, void** multicastPtr,
+                              srtMulticastBuffer* handle)
+{
+    if (nDevices < 2 || nDevices > (int32_t)kMaxPeers + 1 || !devices || !localPtrs || !multicastPtr || !handle || bytes == 0)
+        return fail(cudaErrorInvalidValue, "srtMulticastAlloc: 2..%u devices, a size and result pointers expected", kMaxPeers + 1);
+    const DriverApi& d = driver_api();
+    if (!d.ok) return fail(cudaErrorNotSupported, "srtMulticastAlloc: the driver does not export the multicast entry points");
+    int cur = 0;
+    cudaError_t ce = cudaGetDevice(&cur);
+    if (ce != cudaSuccess) return ce;
+    for (int32_t i = 0; i < nDevices; ++i) {
+        if ((ce = cudaSetDevice(devices[i])) != cudaSuccess || (ce = cudaFree(nullptr)) != cudaSuccess) {      // primary context up
+            cudaSetDevice(cur);
+            return fail(ce, "srtMulticastAlloc: device %d: %s", devices[i], cudaGetErrorString(ce));
+        }
+        int supported = 0;
+        if (d.DeviceGetAttribute(&supported, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, devices[i]) != CUDA_SUCCESS || !supported) {
+            cudaSetDevice(cur);
+            return fail(cudaErrorNotSupported, "srtMulticastAlloc: device %d has no NVLink multicast", devices[i]);
+        }
+    }
+    MulticastBuffer* b = new MulticastBuffer();
+    b->n = nDevices;
+    for (int32_t i = 0; i < nDevices; ++i) b->devices[i] = devices[i];
+    CUmulticastObjectProp prop;
+    memset(&prop, 0, sizeof prop);
+    prop.numDevices = (unsigned)nDevices;
+    prop.size = bytes;
+    size_t gran = 0;
+    CUresult r = d.MulticastGetGranularity(&gran, &prop, CU_MULTICAST_GRANULARITY_RECOMMENDED);
+    auto bail = [&](const char* what, CUresult code) {
+        multicast_destroy(b);
+        cudaSetDevice(cur);
+        return fail(code == CUDA_ERROR_NOT_SUPPORTED || code == CUDA_ERROR_NOT_PERMITTED ? cudaErrorNotSupported : cudaErrorUnknown,
+                    "srtMulticastAlloc: %s failed with driver code %d", what, (int)code);
+    };
+    if (r != CUDA_SUCCESS || gran == 0) return bail("cuMulticastGetGranularity", r);
+    b->size = (bytes + gran - 1) / gran * gran;
+    prop.size = b->size;
+    if ((r = d.MulticastCreate(&b->mc, &prop)) != CUDA_SUCCESS) { b->mc = 0; return bail("cuMulticastCreate", r); }
+    for (int32_t i = 0; i < nDevices; ++i)
+        if ((r = d.MulticastAddDevice(b->mc, devices[i])) != CUDA_SUCCESS) return bail("cuMulticastAddDevice", r);
+    CUmemAccessDesc access[kMaxPeers + 1];
+    for (int32_t i = 0; i < nDevices; ++i) {
+        access[i].location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        access[i].location.id = devices[i];
+        access[i].flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    }
+    for (int32_t i = 0; i < nDevices; ++i) {
+        CUmemAllocationProp ap;
+        memset(&ap, 0, sizeof ap);
+        ap.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        ap.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        ap.location.id = devices[i];
+        if ((r = d.MemCreate(&b->mem[i], b->size, &ap, 0)) != CUDA_SUCCESS) { b->mem[i] = 0; return bail("cuMemCreate", r); }
+        if ((r = d.MulticastBindMem(b->mc, 0, b->mem[i], 0, b->size, 0)) != CUDA_SUCCESS) return bail("cuMulticastBindMem", r);
+        b->bound[i] = true;
+        if ((r = d.MemAddressReserve(&b->va[i], b->size, gran, 0, 0)) != CUDA_SUCCESS) { b->va[i] = 0; return bail("cuMemAddressReserve", r); }
+        if ((r = d.MemMap(b->va[i], b->size, 0, b->mem[i], 0)) != CUDA_SUCCESS) return bail("cuMemMap", r);
+        if ((r = d.MemSetAccess(b->va[i], b->size, access, (size_t)nDevices)) != CUDA_SUCCESS) return bail("cuMemSetAccess", r);
+    }
+    if ((r = d.MemAddressReserve(&b->mc_va, b->size, gran, 0, 0)) != CUDA_SUCCESS) { b->mc_va = 0; return bail("cuMemAddressReserve (multicast)", r); }
+    if ((r = d.MemMap(b->mc_va, b->size, 0, b->mc, 0)) != CUDA_SUCCESS) return bail("cuMemMap (multicast)", r);
+    if ((r = d.MemSetAccess(b->mc_va, b->size, access, (size_t)nDevices)) != CUDA_SUCCESS) return bail("cuMemSetAccess (multicast)", r);
+    for (int32_t i = 0; i < nDevices; ++i) localPtrs[i] = reinterpret_cast<void*>(b->va[i]);
+    *multicastPtr = reinterpret_cast<void*>(b->mc_va);
+    *handle = b;
+    cudaSetDevice(cur);
+    return cudaSuccess;
+}
+
+cudaError_t srtMulticastFree(srtMulticastBuffer handle)
+{
+    if (!handle) return cudaSuccess;
+    int cur = 0;
+    cudaGetDevice(&cur);
+    multicast_destroy(static_cast<MulticastBuffer*>(handle));
+    cudaSetDevice(cur);
     return cudaSuccess;
 }
 
@@ -2648,6 +2803,39 @@ cudaError_t srtPeerMemOpen(const srtPeerMemHandle* handle, void** ptr)
     if (e != cudaSuccess) return fail(e, "srtPeerMemOpen: cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
     *ptr = p;
     return cudaSuccess;
+}
+
+cudaError_t srtPeerSignal(void* const* peerFlags, int32_t peerCount, int32_t slot, uint64_t epoch, cudaStream_t stream)
+{
+    if (peerCount < 0 || peerCount >= kMaxFlagSlots || (peerCount > 0 && !peerFlags) || slot < 0 || slot >= kMaxFlagSlots)
+        return fail(cudaErrorInvalidValue, "srtPeerSignal: at most %d peers, slot 0..%d", kMaxFlagSlots - 1, kMaxFlagSlots - 1);
+    if (peerCount == 0) return cudaSuccess;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    PeerSignalParams p;
+    memset(&p, 0, sizeof p);
+    for (int32_t i = 0; i < peerCount; ++i) {
+        if (!peerFlags[i]) return fail(cudaErrorInvalidValue, "srtPeerSignal: peerFlags[%d] is null", i);
+        p.peer_flags[i] = static_cast<unsigned long long*>(peerFlags[i]);
+    }
+    p.count = peerCount; p.slot = slot; p.epoch = epoch;
+    peer_signal_kernel<<<1, 32, 0, stream>>>(p);
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
+cudaError_t srtPeerWait(const void* localFlags, int32_t slots, int32_t skipSlot, uint64_t epoch, uint64_t timeoutNs, cudaStream_t stream)
+{
+    if (!localFlags || slots < 1 || slots > kMaxFlagSlots)
+        return fail(cudaErrorInvalidValue, "srtPeerWait: a flag array of 1..%d slots expected", kMaxFlagSlots);
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    const uint64_t ns = timeoutNs ? timeoutNs : (uint64_t)srt::kDefaultWaitLimitNs;
+    peer_wait_kernel<<<1, 32, 0, stream>>>(static_cast<const volatile unsigned long long*>(localFlags), slots, skipSlot, epoch, ns * 2);
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
 }
 
 cudaError_t srtPeerMemClose(void* ptr)

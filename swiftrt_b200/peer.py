@@ -33,6 +33,29 @@ class _RawDeviceMemory:
                                          "version": 2, "strides": None}
 
 
+def _alloc_and_exchange(nbytes: int, device, rank: int, world: int, group):
+    """(own device pointer, {rank: mapped pointer of that rank's buffer}) for a srtPeerMemAlloc'ed buffer of
+    `nbytes` on every rank; the 64-byte handles travel through torch.distributed."""
+    ptr = ctypes.c_void_p()
+    handle = _lib.PeerMemHandle()
+    with torch.cuda.device(device):
+        _check(lib.srtPeerMemAlloc(nbytes, ctypes.byref(ptr), ctypes.byref(handle)))
+    peers: dict[int, int] = {}
+    if world > 1:
+        handles: list = [None] * world
+        dist.all_gather_object(handles, bytes(handle.bytes), group=group)
+        with torch.cuda.device(device):
+            for r, blob in enumerate(handles):
+                if r == rank:
+                    continue
+                h = _lib.PeerMemHandle()
+                ctypes.memmove(h.bytes, blob, 64)
+                p = ctypes.c_void_p()
+                _check(lib.srtPeerMemOpen(ctypes.byref(h), ctypes.byref(p)))
+                peers[r] = p.value
+    return ptr, peers
+
+
 class PeerBuffer:
     """A dense tensor of `shape` on this rank's GPU plus the addresses of the same tensor on the
     other ranks' GPUs.
@@ -62,6 +85,13 @@ class PeerBuffer:
         self.nbytes = max(count * torch.empty((), dtype=dtype).element_size(), 16)
         self._ptr = ctypes.c_void_p()
         self.peer_base: dict[int, int] = {}
+        # flags for ranks_done(): one 64-bit slot per rank in every rank's array, zeroed before anybody signals
+        self._epoch = 0
+        self._flags_ptr, self._peer_flags = _alloc_and_exchange(256, self.device, self.rank, self.world, group)
+        torch.as_tensor(_RawDeviceMemory(self._flags_ptr.value, 256), device=self.device).zero_()
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=group)
         if multicast and self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
             with torch.cuda.device(self.device):
@@ -112,11 +142,15 @@ class PeerBuffer:
         """Orders everything the ranks enqueued so far before what follows on this rank's current
         stream: after it, blocks written by other ranks may be read."""
         if self.world > 1:
-            # a one-element all-reduce on the current stream: every rank's kernel precedes its
-            # contribution, so what follows on this stream sees all blocks; the host is not blocked
-            if self._token is None:
-                self._token = torch.zeros(1, device=self.device)
-            dist.all_reduce(self._token, group=self.group)
+            # no collective: this rank's step number goes into its slot of every peer's flag array (behind the
+            # kernels enqueued so far), then the stream waits -- bounded -- until all peers' numbers have arrived
+            self._epoch += 1
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            ptrs = [p for _, p in sorted(self._peer_flags.items())]
+            arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+            with torch.cuda.device(self.device):
+                _check(lib.srtPeerSignal(arr, len(ptrs), self.rank, self._epoch, stream))
+                _check(lib.srtPeerWait(self._flags_ptr, self.world, self.rank, self._epoch, 0, stream))
 
     def close(self) -> None:
         """Collective: unmaps the peers' buffers, then frees this rank's."""
@@ -126,6 +160,14 @@ class PeerBuffer:
         torch.cuda.synchronize(self.device)
         if self.world > 1:
             dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for p in self._peer_flags.values():
+                _check(lib.srtPeerMemClose(p))
+        self._peer_flags = {}
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            _check(lib.srtPeerMemFree(self._flags_ptr))
         if self._symm is not None:
             # symmetric memory is owned by torch: dropping the references releases the mappings
             self.peer_base = {}

@@ -101,7 +101,8 @@ def sharded_matmul(lhs: torch.Tensor, rhs: torch.Tensor, transposed_lhs: bool = 
             view = peer_buffer.tensor.narrow(dim, lo, hi - lo)
             if gather_fn is None:
                 from .matmul import MatmulError, matmul_all_gather_into, matmul_all_gather_multicast_into
-                mc = peer_buffer.multicast_pointer(view) if getattr(peer_buffer, "multicast_base", 0) else 0
+                # between two GPUs there is nothing for the switch to replicate: the per-peer form is faster there
+                mc = peer_buffer.multicast_pointer(view) if (getattr(peer_buffer, "multicast_base", 0) and world > 2) else 0
                 if mc:
                     try:        # one multimem store per tile; products it does not take (code 801) go peer by peer
                         matmul_all_gather_multicast_into(view, mc, a, transposed_lhs, b, transposed_rhs)

@@ -201,7 +201,7 @@ def test_sharded_devices_entry_point_from_one_process(srt, oracle):
     vp = ctypes.c_void_p * n_dev
     rc = _lib.lib.srtMatmulShardedDevices(2, n_dev, vp(*[s.cuda_stream for s in streams]), vp(*[t.data_ptr() for t in a]), da.ref(), False,
                                           vp(*[t.data_ptr() for t in b]), db.ref(), False, None, None, 5,
-                                          vp(*[t.data_ptr() for t in out]), do.ref(), True)
+                                          vp(*[t.data_ptr() for t in out]), do.ref(), True, None)
     assert rc == 0, _lib.last_error()
     for s in streams:
         s.synchronize()
@@ -209,3 +209,56 @@ def test_sharded_devices_entry_point_from_one_process(srt, oracle):
         err = oracle.rel_frobenius(oracle.decode(from_dev(t, BF16), BF16), oracle.decode(want, BF16))
         assert err <= 2e-3, err
     assert torch.equal(out[0].cpu(), out[1].cpu())
+
+
+def test_multicast_buffers_from_one_process(srt, oracle):
+    """srtMulticastAlloc: one process binds a buffer of every GPU to one NVLink multicast object; the
+    sharded product then stores each tile once (multimem.st) and every GPU's buffer holds all of C."""
+    from swiftrt_b200 import _lib
+    from swiftrt_b200.peer import _RawDeviceMemory
+    from swiftrt_b200.tensor import Descriptor
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    n_dev, M, N, K = 2, 512, 1024, 1024
+    nbytes = M * N * 2
+    devs = (ctypes.c_int32 * n_dev)(0, 1)
+    local = (ctypes.c_void_p * n_dev)()
+    mc, handle = ctypes.c_void_p(), ctypes.c_void_p()
+    rc = _lib.lib.srtMulticastAlloc(n_dev, devs, nbytes, local, ctypes.byref(mc), ctypes.byref(handle))
+    if rc == 801:
+        pytest.skip("no NVLink multicast on this machine: " + _lib.last_error())
+    assert rc == 0, _lib.last_error()
+    try:
+        rng = np.random.default_rng(5)
+        a_bits, b_bits = random_bits(oracle, rng, (M, K), BF16), random_bits(oracle, rng, (K, N), BF16)
+        want = oracle.matmul(a_bits, b_bits, BF16)
+        out = []
+        for i in range(n_dev):
+            raw = torch.as_tensor(_RawDeviceMemory(local[i], nbytes), device=f"cuda:{i}")
+            out.append(raw.view(torch.bfloat16).reshape(M, N))
+            out[-1].fill_(-2.0)
+        a = [to_dev(a_bits, BF16, f"cuda:{i}") for i in range(n_dev)]
+        b = [to_dev(b_bits, BF16, f"cuda:{i}") for i in range(n_dev)]
+        streams = [torch.cuda.Stream(device=i) for i in range(n_dev)]
+        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(1)
+        da, db, do = Descriptor(a[0]), Descriptor(b[0]), Descriptor(out[0])
+        vp = ctypes.c_void_p * n_dev
+        before = srt.launch_count()
+        rc = _lib.lib.srtMatmulShardedDevices(2, n_dev, vp(*[s.cuda_stream for s in streams]), vp(*[t.data_ptr() for t in a]), da.ref(), False,
+                                              vp(*[t.data_ptr() for t in b]), db.ref(), False, None, None, 5,
+                                              vp(*[t.data_ptr() for t in out]), do.ref(), True, mc)
+        assert rc == 0, _lib.last_error()
+        for s in streams:
+            s.synchronize()
+        assert srt.launch_count() - before == n_dev       # one fused kernel per device, no copies
+        for i, t in enumerate(out):
+            err = oracle.rel_frobenius(oracle.decode(from_dev(t, BF16), BF16), oracle.decode(want, BF16))
+            assert err <= 2e-3, (i, err)
+        assert torch.equal(out[0].cpu(), out[1].cpu())
+        for i in range(n_dev):
+            st = ctypes.c_uint32(9)
+            assert _lib.lib.srtMatmulCheckStatus(streams[i].cuda_stream, ctypes.byref(st)) == 0 and st.value == 0
+        del out
+    finally:
+        assert _lib.lib.srtMulticastFree(handle) == 0
