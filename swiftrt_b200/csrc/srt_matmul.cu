@@ -511,7 +511,12 @@ bool make_plan_impl(const Problem& P, const DeviceInfo& dev, Plan& plan, bool sk
     if (split3 && max_stages > 4) max_stages = 4;
     // Four 32 KB stages keep the pair kernel's MMAs fed; deeper rings measured slower on a
     // power-capped B200 (higher pipe utilisation, lower clock, lower L2 hit rate).
-    if (stages < 2 || stages > 8) stages = pair ? 4 : 8;
+    if (stages < 2 || stages > 8) {
+        // a single wave of pair tiles starts cold on every SM at once and is bound by load latency: six stages
+        // (36.9 us against 39.7 us on the Dense configuration); in a long run of waves four are faster (above)
+        const uint64_t pair_tiles = ((Q.M + 2 * kTileM - 1) / (2 * kTileM)) * ((Q.N + bn - 1) / bn) * Q.batch;
+        stages = pair ? (pair_tiles <= sms / 2 ? 6 : 4) : 8;
+    }
     if (stages > max_stages) stages = max_stages;
     const uint32_t kb_elems = kRowBytes / Q.elem;
     const uint64_t tiles_m = (Q.M + tile_m - 1) / tile_m, tiles_n = (Q.N + bn - 1) / bn;
