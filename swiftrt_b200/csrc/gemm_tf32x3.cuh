@@ -87,6 +87,80 @@ tf32x3_pack_kernel(const PackParams p)
     }
 }
 
+// Epilogue of this kernel: main + correction accumulators -> bias, activation -> memory, 32 columns (one 128-byte
+// segment of 32 rows) at a time.  tcgen05.wait::ld waits for every load of the thread, so the loads of the next
+// segment are issued right after the wait for the current one: their latency passes while the current segment is
+// staged and stored.  The store paths are those of drain_accumulator.
+template <uint32_t BN, uint32_t PARTS>
+__device__ __forceinline__ void drain_two_accumulators(const GemmParams& p, const CUtensorMap* tmap_out, uint32_t staging,
+                                                       uint32_t part, uint32_t acc, uint32_t acc2, uint32_t quarter,
+                                                       uint32_t lane, uint32_t batch, uint32_t m0, uint32_t n0)
+{
+    constexpr uint32_t kPer = BN / 32 / PARTS;                  // segments per warp
+    static_assert(kPer % 2 == 0, "segments are handled in pairs");
+    float* const out = static_cast<float*>(p.out);
+    const float* const bias = static_cast<const float*>(p.bias);
+    const uint32_t row = m0 + quarter * 32 + lane;
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    float row_bias = 0.0f;
+    if (p.bias_mode == 2 && row < p.M) row_bias = bias[static_cast<long long>(row) * p.bias_stride];
+    float* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
+
+    auto load = [&](uint32_t i, uint32_t (&x)[32], uint32_t (&y)[32]) {
+        const uint32_t col = (part + i * PARTS) * 32;
+        tmem_ld_32x32(acc + lane_addr + col, x);
+        tmem_ld_32x32(acc2 + lane_addr + col, y);
+    };
+    auto finish = [&](uint32_t i, uint32_t (&x)[32], uint32_t (&y)[32]) {
+        const uint32_t col0 = n0 + (part + i * PARTS) * 32;
+        if (col0 >= p.N) return;                                // uniform over the warp
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(x[j]) + __uint_as_float(y[j]);
+        if (p.bias_mode == 1) {
+            float my_bias = 0.0f;                               // one coalesced load, handed out by shuffle
+            if (col0 + lane < p.N) my_bias = __ldg(bias + static_cast<long long>(col0 + lane) * p.bias_stride);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, my_bias, j);
+        } else if (p.bias_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += row_bias;
+        }
+        activate_chunk(p.act, v);
+        if (!p.out_tma) {
+            if (row < p.M) store_row_chunk<float>(p, row_ptr, col0, v);
+            return;
+        }
+        if (lane == 0) bulk_wait_group_read<0>();               // the previous store has read the staging buffer
+        __syncwarp();
+#pragma unroll
+        for (uint32_t q = 0; q < 8; ++q) {
+            const uint32_t addr = staging + lane * 128 + ((q ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                         ::"r"(addr), "r"(__float_as_uint(v[4 * q])), "r"(__float_as_uint(v[4 * q + 1])),
+                           "r"(__float_as_uint(v[4 * q + 2])), "r"(__float_as_uint(v[4 * q + 3])) : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_3d(tmap_out, staging, static_cast<int32_t>(col0), static_cast<int32_t>(m0 + quarter * 32),
+                         static_cast<int32_t>(batch));
+            bulk_commit_group();
+        }
+    };
+    uint32_t x0[32], y0[32], x1[32], y1[32];
+    load(0, x0, y0);
+#pragma unroll
+    for (uint32_t i = 0; i < kPer; i += 2) {
+        tmem_ld_wait_regs2(x0, y0);
+        load(i + 1, x1, y1);
+        finish(i, x0, y0);
+        tmem_ld_wait_regs2(x1, y1);
+        if (i + 2 < kPer) load(i + 2, x0, y0);
+        finish(i + 1, x1, y1);
+    }
+}
+
 struct X3Params {
     GemmParams g;                 // sizes, tile walk, A descriptor fields, epilogue
     uint32_t idesc_tf32, idesc_bf16;
@@ -286,11 +360,13 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t acc = tmem_base + buf * 2 * BN;
-                drain_accumulator<float, BN, true, kEpiWarps / 4>(p, &tmap_out, smem_base + kStages * kStageBytes + (warp - 2) * 4096,
-                                                                  (warp - 2) >> 2, acc, quarter, lane, tc.obatch, m0, tc.n0, acc + BN);
+                drain_two_accumulators<BN, kEpiWarps / 4>(p, &tmap_out, smem_base + kStages * kStageBytes + (warp - 2) * 4096,
+                                                          (warp - 2) >> 2, acc, acc + BN, quarter, lane, tc.obatch, m0, tc.n0);
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
+                // the accumulator reads have completed (tcgen05.wait::ld) and nothing in memory is handed over: the
+                // plain arrive is enough, and unlike the cluster-scope release it does not wait for this warp's stores
+                if (lane == 0) mbar_arrive_remote(smem_u32(&tmem_empty_bar[buf]), 0);
             }
         }
         if (drains) drain_finish(lane);
