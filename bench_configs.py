@@ -199,6 +199,35 @@ def run_small_batch(dev, iters: int, flush: torch.Tensor, peaks: dict) -> list:
     return out
 
 
+def run_transform(dev, iters: int, flush: torch.Tensor, peaks: dict) -> list:
+    """t1: srtMatrixTransform re-layouts (one read and one write per element): HBM-bound byte shuffles."""
+    out = []
+    D, O = srt.DataType, srt.Order
+    cases = [("int8 16384x16384 row -> colTiledTC32x32", D.real8I, 16384, 16384, O.row, O.colTiledTC32x32),
+             ("int8 16384x16384 colTiledTC32x32 -> row", D.real8I, 16384, 16384, O.colTiledTC32x32, O.row),
+             ("bf16 16384x8192 row -> colTiled32", D.real16BF, 16384, 8192, O.row, O.colTiled32),
+             ("fp32 8192x8192 row -> col (transpose)", D.real32F, 8192, 8192, O.row, O.col),
+             ("fp32 8192x8192 row -> row (copy)", D.real32F, 8192, 8192, O.row, O.row)]
+    for what, dtype, rows, cols, src, dst in cases + [("fp32 row -> int8 colTiledTC32x32 16384x8192, alpha = 0.5 (quantise)", D.real32F, 16384, 8192, O.row, O.colTiledTC32x32)]:
+        quantise = "quantise" in what
+        la, lc = srt.MatrixLayout(dtype, src, rows, cols), srt.MatrixLayout(D.real8I if quantise else dtype, dst, rows, cols)
+        a = la.empty(dev)
+        if dtype == D.real8I:
+            a.random_(-128, 128)
+        else:
+            a.normal_()
+        c = lc.empty(dev)
+        med, best = _time_cold(lambda: srt.matrix_transform(a, la, lc, alpha=0.5 if quantise else 1.0, out=c), iters, flush)
+        nbytes = rows * cols * (a.element_size() + c.element_size())
+        rec = {"config": "t1", "what": what, "kernel": "matrix_transform_kernel", "ms_median": med, "ms_best": best,
+               "algorithmic_bytes": nbytes, "gbs": nbytes / med / 1e6, "bound": "hbm", "frac_of_nominal": nbytes / med / 1e6 / NOMINAL["hbm_gbs"]}
+        if "hbm_gbs" in peaks:
+            rec["frac_of_measured"] = rec["gbs"] / peaks["hbm_gbs"]
+        out.append(rec)
+        del a, c
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
@@ -213,13 +242,16 @@ def main():
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
     peaks = measured_peaks()
     only = args.only.split(",") if args.only else []
-    # the callers either side of the product and the small-batch Dense shapes are measured on request only (--only f1,f4,s1)
+    # the callers either side of the product and the small-batch Dense shapes are measured on request only (--only f1,f4,s1,t1)
     if "f1" in only:
         print(json.dumps(run_backward(dev, args.iters, flush, peaks)), flush=True)
     if "f4" in only:
         print(json.dumps(run_lstm(dev, args.iters, flush, peaks)), flush=True)
     if "s1" in only:
         for rec in run_small_batch(dev, args.iters, flush, peaks):
+            print(json.dumps(rec), flush=True)
+    if "t1" in only:
+        for rec in run_transform(dev, args.iters, flush, peaks):
             print(json.dumps(rec), flush=True)
     for make in configs(dev):
         if only and make.__name__ not in only:

@@ -54,11 +54,15 @@ typedef enum {
 } srtDataType;
 
 /* Storage order.  Values equal cublasLtOrder_t, which the reference's descriptor uses
- * (tensor_api.h:76): CUBLASLT_ORDER_COL = 0, CUBLASLT_ORDER_ROW = 1.  Tiled orders
- * (values >= 2) return cudaErrorNotSupported. */
+ * (tensor_api.h:76; Order.cublas, cublaslt/MatrixLayout.swift:221-231).  The matmul entry points
+ * compute row and col only and return cudaErrorNotSupported for the tiled orders; srtMatrixTransform
+ * moves matrices into and out of them. */
 typedef enum {
     srtOrderCol = 0,
-    srtOrderRow = 1
+    srtOrderRow = 1,
+    srtOrderColTiled32 = 2,         /* CUBLASLT_ORDER_COL32 */
+    srtOrderColTiledTC32x8 = 3,     /* CUBLASLT_ORDER_COL4_4R2_8C */
+    srtOrderColTiledTC32x32 = 4     /* CUBLASLT_ORDER_COL32_2R_4R4 */
 } srtOrder;
 
 /* Replaces srtTensorDescriptor of Modules/SwiftRTCuda/tensor_api.h:70-87 field for field
@@ -175,6 +179,52 @@ cudaError_t srtActivationForward(
     srtActivationType activation,
     void* y, const srtTensorDescriptor* yDesc,
     cudaStream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * srtMatrixTransform: C = alpha . op(A) + beta . op(B), every matrix in its own storage order and
+ * element type -- the re-layout operation between row / col and the tiled tensor-core orders.
+ *
+ * Replaces cublasLtMatrixTransform for the descriptors the reference wraps but never runs:
+ * MatrixTransform (Sources/SwiftRTCore/platform/cuda/cublaslt/MatrixTransform.swift:21-129: scale type,
+ * pointer mode, transA, transB) and MatrixLayout (cublaslt/MatrixLayout.swift:21-204: type, order, rows,
+ * cols, leadingDimension, batchCount, batchStride -- srtMatrixLayout has the same fields).
+ *
+ * rows / cols / ld describe the matrix as STORED; op(X) is the stored matrix or its transpose, and op(A),
+ * op(B) and C must agree in rows, cols and batchCount.  Element (r, c) of a stored matrix lives at
+ *   srtOrderRow              r ld + c
+ *   srtOrderCol              c ld + r
+ *   srtOrderColTiled32       (c / 32) ld + r 32 + c % 32                                   ld >= 32 rows
+ *   srtOrderColTiledTC32x32  (c / 32) ld + (r / 32) 1024 + t(r % 32) 32 + c % 32,
+ *                            t(q) = ((q % 8) / 2 * 4 + q / 8) * 2 + q % 2                  ld >= 32 roundUp(rows, 32)
+ * (the formulas of Order, tensor/Tensor.swift:188-192 and :219-231).  srtOrderColTiledTC32x8 returns
+ * cudaErrorNotSupported: the reference states no element formula for it and names it an operand layout of
+ * SM 7.2 / 7.5 only (Tensor.swift:204-217).  srtMatrixLayoutLeadingDimension gives the smallest valid ld.
+ *
+ * Types: real32F, real16F, real16BF, real8I in any combination; alpha and beta are host floats (the
+ * default pointer mode and the fp32 scale type of the wrapper), the sum is formed in fp32 and rounded once
+ * (Int8: to nearest even, saturated to [-128, 127]).  B may be NULL when *beta is 0.  C must not overlap
+ * A or B.  One launch on `stream`, no workspace; a C without elements succeeds without a launch.
+ */
+typedef struct {
+    srtDataType type;
+    srtOrder order;
+    uint64_t rows;
+    uint64_t cols;
+    int64_t leadingDimension;       /* elements */
+    int32_t batchCount;             /* >= 1 */
+    int64_t batchStride;            /* elements between consecutive matrices */
+} srtMatrixLayout;
+
+cudaError_t srtMatrixTransform(
+    const float* alpha, const void* A, const srtMatrixLayout* aLayout, bool transA,
+    const float* beta, const void* B, const srtMatrixLayout* bLayout, bool transB,
+    void* C, const srtMatrixLayout* cLayout, cudaStream_t stream);
+
+/* Smallest leading dimension of a rows x cols matrix in `order` (the rule of Tensor.leadingDimension,
+ * cuda/device/CudaPlatform.swift:298-311, written in terms of the stored rows as cublasLt defines it),
+ * and the number of elements a buffer for it must hold.  0 for an order that is not computed. */
+uint64_t srtMatrixLayoutLeadingDimension(srtOrder order, uint64_t rows, uint64_t cols);
+uint64_t srtMatrixLayoutElementCount(srtOrder order, uint64_t rows, uint64_t cols, uint64_t leadingDimension);
 
 /* ---------------------------------------------------------------------------------------
  * Plan query and tuning knobs.  Stand in for MatmulAlgorithm.query / .search

@@ -14,3 +14,4 @@ KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TCGEN05_PAIR = 1, 2, 3
 from .sharded import shard_range, sharded_matmul, sharded_matmul_host  # noqa: F401,E402
 from .peer import PeerBuffer  # noqa: F401,E402
 from .recurrent import BasicRNNCell, GRUCell, GraphedSequence, LSTMCell, LSTMState, run_sequence, run_sequence_preconcatenated  # noqa: F401,E402
+from .transform import MatrixLayout, leading_dimension, matrix_transform  # noqa: F401,E402

@@ -43,7 +43,8 @@ EXPORTS = ["srtMatmul", "srtMatmulBiasActivation", "srtMatmulQueryPlan", "srtMat
            "srtMatmulAllGather", "srtPeerMemAlloc", "srtPeerMemOpen", "srtPeerMemClose", "srtPeerMemFree", "srtLstmCell", "srtRnnCell",
            "srtMatmulAllGatherMulticast", "srtMatmulTune", "srtMatmulPlanCacheSave", "srtMatmulPlanCacheLoad", "srtMatmulPlanCacheClear",
            "srtActivationForward", "srtMatmulReleaseWorkspaces", "srtGruCell", "srtShardRange", "srtMatmulSharded",
-           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit", "srtLstmCellFused", "srtLstmInterleaveGates", "srtPeerSignal", "srtPeerWait", "srtMulticastAlloc", "srtMulticastFree"]
+           "srtMatmulShardedDevices", "srtMatmulSetWaitLimit", "srtLstmCellFused", "srtLstmInterleaveGates", "srtPeerSignal", "srtPeerWait", "srtMulticastAlloc", "srtMulticastFree",
+           "srtMatrixTransform", "srtMatrixLayoutLeadingDimension", "srtMatrixLayoutElementCount"]
 
 if not os.path.exists(SO):
     raise ImportError(
@@ -119,6 +120,20 @@ lib.srtMatmulPlanCacheClear.restype = ctypes.c_int
 lib.srtMatmulPlanCacheClear.argtypes = []
 
 
+class MatrixLayoutStruct(ctypes.Structure):
+    """srtMatrixLayout of include/srt_matmul_api.h."""
+    _fields_ = [("type", ctypes.c_int), ("order", ctypes.c_int), ("rows", ctypes.c_uint64), ("cols", ctypes.c_uint64),
+                ("leadingDimension", ctypes.c_int64), ("batchCount", ctypes.c_int32), ("batchStride", ctypes.c_int64)]
+
+
+lib.srtMatrixTransform.restype = ctypes.c_int
+lib.srtMatrixTransform.argtypes = [ctypes.POINTER(ctypes.c_float), _P, ctypes.POINTER(MatrixLayoutStruct), ctypes.c_bool,
+                                   ctypes.POINTER(ctypes.c_float), _P, ctypes.POINTER(MatrixLayoutStruct), ctypes.c_bool,
+                                   _P, ctypes.POINTER(MatrixLayoutStruct), _P]
+lib.srtMatrixLayoutLeadingDimension.restype = ctypes.c_uint64
+lib.srtMatrixLayoutLeadingDimension.argtypes = [ctypes.c_int, ctypes.c_uint64, ctypes.c_uint64]
+lib.srtMatrixLayoutElementCount.restype = ctypes.c_uint64
+lib.srtMatrixLayoutElementCount.argtypes = [ctypes.c_int, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64]
 lib.srtActivationForward.restype = ctypes.c_int
 lib.srtActivationForward.argtypes = [_P, _D, ctypes.c_int, _P, _D, _P]
 lib.srtMatmulReleaseWorkspaces.restype = ctypes.c_int

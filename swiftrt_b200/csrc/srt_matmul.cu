@@ -21,6 +21,7 @@
 #include "gemm_tcgen05.cuh"
 #include "gemm_tf32x3.cuh"
 #include "lstm_cell.cuh"
+#include "matrix_transform.cuh"
 
 namespace {
 
@@ -1901,6 +1902,151 @@ cudaError_t srtBiasActivationBackward(const void* dy, const srtTensorDescriptor*
 }
 
 // ------------------------------------------------------------------ srtActivationForward
+// ---------------------------------------------------------------------------------------------
+// srtMatrixTransform and its layout helpers (cublaslt/MatrixTransform.swift:21-129, MatrixLayout.swift:21-204)
+uint64_t srtMatrixLayoutLeadingDimension(srtOrder order, uint64_t rows, uint64_t cols)
+{
+    switch ((int)order) {
+    case srtOrderRow: return cols;
+    case srtOrderCol: return rows;
+    case srtOrderColTiled32: return 32 * rows;
+    case srtOrderColTiledTC32x32: return 32 * ((rows + 31) / 32 * 32);
+    default: return 0;
+    }
+}
+
+uint64_t srtMatrixLayoutElementCount(srtOrder order, uint64_t rows, uint64_t cols, uint64_t ld)
+{
+    if (rows == 0 || cols == 0) return 0;
+    switch ((int)order) {
+    case srtOrderRow: return (rows - 1) * ld + cols;
+    case srtOrderCol: return (cols - 1) * ld + rows;
+    case srtOrderColTiled32: return ((cols - 1) / 32) * ld + 32 * rows;
+    case srtOrderColTiledTC32x32: return ((cols - 1) / 32) * ld + 32 * ((rows + 31) / 32 * 32);
+    default: return 0;
+    }
+}
+
+namespace {
+cudaError_t check_layout(const srtMatrixLayout* l, const char* name)
+{
+    switch ((int)l->type) {
+    case real32F: case real16F: case real16BF: case real8I: break;
+    default: return fail(cudaErrorNotSupported, "srtMatrixTransform: element type %d of %s is not computed", (int)l->type, name);
+    }
+    switch ((int)l->order) {
+    case srtOrderRow: case srtOrderCol: case srtOrderColTiled32: case srtOrderColTiledTC32x32: break;
+    case srtOrderColTiledTC32x8:
+        return fail(cudaErrorNotSupported, "srtMatrixTransform: order colTiledTC32x8 of %s is not computed (an operand layout of SM 7.2 / 7.5)", name);
+    default: return fail(cudaErrorInvalidValue, "srtMatrixTransform: unknown order %d of %s", (int)l->order, name);
+    }
+    if (l->rows > 0x7fffffffull || l->cols > 0x7fffffffull)          // "only values that can be expressed as Int32" (MatrixLayout.swift:115-143)
+        return fail(cudaErrorInvalidValue, "srtMatrixTransform: rows / cols of %s outside the Int32 range", name);
+    if (l->batchCount < 1) return fail(cudaErrorInvalidValue, "srtMatrixTransform: batchCount of %s must be at least 1", name);
+    if (l->leadingDimension < 0 || l->batchStride < 0)
+        return fail(cudaErrorInvalidValue, "srtMatrixTransform: negative leading dimension or batch stride of %s", name);
+    if (l->rows != 0 && l->cols != 0 &&
+        (uint64_t)l->leadingDimension < srtMatrixLayoutLeadingDimension(l->order, l->rows, l->cols))
+        return fail(cudaErrorInvalidValue, "srtMatrixTransform: leading dimension %lld of %s is below the %llu its order needs",
+                    (long long)l->leadingDimension, name, (unsigned long long)srtMatrixLayoutLeadingDimension(l->order, l->rows, l->cols));
+    return cudaSuccess;
+}
+}  // namespace
+
+cudaError_t srtMatrixTransform(const float* alpha, const void* A, const srtMatrixLayout* aLayout, bool transA,
+                               const float* beta, const void* B, const srtMatrixLayout* bLayout, bool transB,
+                               void* C, const srtMatrixLayout* cLayout, cudaStream_t stream)
+{
+    if (!alpha || !A || !aLayout || !C || !cLayout) return fail(cudaErrorInvalidValue, "srtMatrixTransform: null alpha, A, C or layout");
+    const float bt = beta ? *beta : 0.0f;
+    const bool use_b = bt != 0.0f;
+    if (use_b && (!B || !bLayout)) return fail(cudaErrorInvalidValue, "srtMatrixTransform: beta is not 0 but B or its layout is null");
+    cudaError_t e = check_layout(aLayout, "A");
+    if (e != cudaSuccess) return e;
+    if ((e = check_layout(cLayout, "C")) != cudaSuccess) return e;
+    if (use_b && (e = check_layout(bLayout, "B")) != cudaSuccess) return e;
+    auto same_shape = [&](const srtMatrixLayout* l, bool t) {
+        return (t ? l->cols : l->rows) == cLayout->rows && (t ? l->rows : l->cols) == cLayout->cols && l->batchCount == cLayout->batchCount;
+    };
+    if (!same_shape(aLayout, transA)) return fail(cudaErrorInvalidValue, "srtMatrixTransform: op(A) and C differ in rows, cols or batchCount");
+    if (use_b && !same_shape(bLayout, transB)) return fail(cudaErrorInvalidValue, "srtMatrixTransform: op(B) and C differ in rows, cols or batchCount");
+    if (cLayout->rows == 0 || cLayout->cols == 0) return cudaSuccess;
+    g_error[0] = 0;
+    DeviceScope scope(stream);
+    if (scope.status != cudaSuccess) return scope.status;
+    TransformParams tp;
+    memset(&tp, 0, sizeof tp);
+    auto fill = [](StoredMatrix& m, const void* ptr, const srtMatrixLayout* l, bool t) {
+        m.ptr = const_cast<void*>(ptr);
+        m.ld = l->leadingDimension;
+        m.batch_stride = l->batchStride;
+        m.order = (int32_t)l->order;
+        m.type = (int32_t)l->type;
+        m.transposed = t ? 1u : 0u;
+    };
+    fill(tp.a, A, aLayout, transA);
+    fill(tp.c, C, cLayout, false);
+    if (use_b) fill(tp.b, B, bLayout, transB); else tp.b = tp.a;
+    tp.alpha = *alpha;
+    tp.beta = bt;
+    tp.use_b = use_b ? 1u : 0u;
+    tp.rows = (uint32_t)cLayout->rows;
+    tp.cols = (uint32_t)cLayout->cols;
+    tp.batch = (uint32_t)cLayout->batchCount;
+    tp.tiles_r = (tp.rows + kTransformTile - 1) / kTransformTile;
+    tp.tiles_c = (tp.cols + kTransformTile - 1) / kTransformTile;
+    // V elements per access: 16 bytes of the widest element type, if every operand's addresses allow it
+    auto size_of = [](int32_t t) { return t == kTypeF32 ? 4u : t == kTypeI8 ? 1u : 2u; };
+    uint32_t widest = size_of(tp.a.type) > size_of(tp.c.type) ? size_of(tp.a.type) : size_of(tp.c.type);
+    if (use_b && size_of(tp.b.type) > widest) widest = size_of(tp.b.type);
+    uint32_t vec = 16 / widest;
+    auto aligned = [&](const StoredMatrix& m) {
+        return reinterpret_cast<uintptr_t>(m.ptr) % (vec * size_of(m.type)) == 0 && m.ld % vec == 0 && m.batch_stride % vec == 0;
+    };
+    if (!aligned(tp.a) || !aligned(tp.c) || (use_b && !aligned(tp.b))) vec = 1;
+    const bool stream_form = runs_along_columns(tp.a) == runs_along_columns(tp.c) &&
+                             (!use_b || runs_along_columns(tp.b) == runs_along_columns(tp.c));
+    if (stream_form) {
+        const bool along_columns = runs_along_columns(tp.c);
+        const unsigned long long fast = along_columns ? tp.cols : tp.rows, slow = along_columns ? tp.rows : tp.cols;
+        const unsigned long long work = (unsigned long long)tp.batch * slow * ((fast + vec - 1) / vec);
+        unsigned long long blocks = (work + kTransformThreads - 1) / kTransformThreads;
+        if (blocks > 148ull * 16) blocks = 148ull * 16;
+        const unsigned grid = (unsigned)blocks;
+        const bool raw = !use_b && tp.alpha == 1.0f && tp.a.type == tp.c.type;
+        switch (vec) {
+        case 16:
+            if (raw) matrix_transform_stream_kernel<16, true><<<grid, kTransformThreads, 0, stream>>>(tp);
+            else     matrix_transform_stream_kernel<16, false><<<grid, kTransformThreads, 0, stream>>>(tp);
+            break;
+        case 8:
+            if (raw) matrix_transform_stream_kernel<8, true><<<grid, kTransformThreads, 0, stream>>>(tp);
+            else     matrix_transform_stream_kernel<8, false><<<grid, kTransformThreads, 0, stream>>>(tp);
+            break;
+        case 4:
+            if (raw) matrix_transform_stream_kernel<4, true><<<grid, kTransformThreads, 0, stream>>>(tp);
+            else     matrix_transform_stream_kernel<4, false><<<grid, kTransformThreads, 0, stream>>>(tp);
+            break;
+        default:
+            if (raw) matrix_transform_stream_kernel<1, true><<<grid, kTransformThreads, 0, stream>>>(tp);
+            else     matrix_transform_stream_kernel<1, false><<<grid, kTransformThreads, 0, stream>>>(tp);
+            break;
+        }
+    } else {
+        const unsigned long long tiles = (unsigned long long)tp.tiles_r * tp.tiles_c * tp.batch;
+        const unsigned grid = (unsigned)(tiles < 148ull * 8 ? tiles : 148ull * 8);
+        switch (vec) {
+        case 16: matrix_transform_tile_kernel<16><<<grid, kTransformThreads, 0, stream>>>(tp); break;
+        case 8: matrix_transform_tile_kernel<8><<<grid, kTransformThreads, 0, stream>>>(tp); break;
+        case 4: matrix_transform_tile_kernel<4><<<grid, kTransformThreads, 0, stream>>>(tp); break;
+        default: matrix_transform_tile_kernel<1><<<grid, kTransformThreads, 0, stream>>>(tp); break;
+        }
+    }
+    e = cudaGetLastError();
+    if (e == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return e;
+}
+
 cudaError_t srtActivationForward(const void* z, const srtTensorDescriptor* zDesc, srtActivationType activation, void* y,
                                  const srtTensorDescriptor* yDesc, cudaStream_t stream)
 {

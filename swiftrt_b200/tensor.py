@@ -18,6 +18,7 @@ class DataType(enum.IntEnum):
     """srtDataType values (Modules/SwiftRTCuda/tensor_api.h:31-38)."""
     real32F = 0
     real16F = 2
+    real8I = 3
     real16BF = 14
 
 
@@ -25,6 +26,9 @@ class Order(enum.IntEnum):
     """Storage order with cublasLtOrder_t values (Sources/SwiftRTCore/tensor/Tensor.swift:177-236)."""
     col = 0
     row = 1
+    colTiled32 = 2          # tiled orders: storage of MatrixLayout buffers only (transform.py), not of torch tensors
+    colTiledTC32x8 = 3
+    colTiledTC32x32 = 4
 
 
 class ActivationType(enum.IntEnum):
