@@ -27,7 +27,7 @@
 
 namespace srt_host {
 
-enum class Order { col = 0, row = 1 };
+enum class Order { col = 0, row = 1, colTiled32 = 2, colTiledTC32x8 = 3, colTiledTC32x32 = 4 };   // Tensor.swift:177-231
 enum class ActivationType { sigmoid = 0, relu, tanh, clippedRelu, elu, identity, gelu, geluTanh };
 
 template <typename E> struct ElementTraits;
@@ -320,5 +320,56 @@ std::vector<typename LSTMCell<E>::State> runSequence(const LSTMCell<E>& cell, co
     }
     return outputs;
 }
+
+// MatrixLayout (cublaslt/MatrixLayout.swift:21-204): the same properties, a plain value instead of a cublasLt handle.
+struct MatrixLayout {
+    srtDataType type = real32F;
+    Order order = Order::row;
+    size_t rows = 0, cols = 0;
+    long long leadingDimension = 0;
+    int batchCount = 1;
+    long long batchStride = 0;
+
+    MatrixLayout() = default;
+    MatrixLayout(srtDataType type_, Order order_, size_t rows_, size_t cols_, int batchCount_ = 1)
+        : type(type_), order(order_), rows(rows_), cols(cols_), batchCount(batchCount_)
+    {
+        leadingDimension = static_cast<long long>(srtMatrixLayoutLeadingDimension(static_cast<srtOrder>(order), rows, cols));
+        batchStride = static_cast<long long>(elementCount());
+    }
+    // MatrixLayout.init(_ tensor:) (MatrixLayout.swift:27-47) for a row- or col-ordered rank-2 tensor
+    template <typename E>
+    explicit MatrixLayout(const Tensor<E>& t)
+        : type(ElementTraits<E>::type), order(t.strides[t.rank() - 1] == 1 ? Order::row : Order::col), rows(t.shape[t.rank() - 2]),
+          cols(t.shape[t.rank() - 1])
+    {
+        leadingDimension = static_cast<long long>(order == Order::row ? t.strides[t.rank() - 2] : t.strides[t.rank() - 1]);
+        batchStride = static_cast<long long>(elementCount());
+    }
+    size_t elementCount() const
+    {
+        return srtMatrixLayoutElementCount(static_cast<srtOrder>(order), rows, cols, static_cast<uint64_t>(leadingDimension));
+    }
+    size_t bufferElements() const { return rows && cols ? (batchCount - 1) * static_cast<size_t>(batchStride) + elementCount() : 0; }
+    srtMatrixLayout raw() const
+    {
+        return srtMatrixLayout{type, static_cast<srtOrder>(order), rows, cols, leadingDimension, batchCount, batchStride};
+    }
+};
+
+// MatrixTransform (cublaslt/MatrixTransform.swift:21-129): transA / transB and host scalars; callAsFunction runs
+// C = alpha . op(A) + beta . op(B), which the reference's wrapper only describes.
+struct MatrixTransform {
+    bool transA = false, transB = false;
+    void operator()(float alpha, const void* a, const MatrixLayout& aLayout, float beta, const void* b, const MatrixLayout* bLayout,
+                    void* c, const MatrixLayout& cLayout, cudaStream_t stream = nullptr) const
+    {
+        const srtMatrixLayout la = aLayout.raw(), lc = cLayout.raw();
+        srtMatrixLayout lb{};
+        if (bLayout) lb = bLayout->raw();
+        check(srtMatrixTransform(&alpha, a, &la, transA, &beta, b, bLayout ? &lb : nullptr, transB, c, &lc, stream),
+              "srtMatrixTransform");
+    }
+};
 
 }  // namespace srt_host

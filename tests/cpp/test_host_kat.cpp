@@ -94,6 +94,36 @@ static void test_dense_and_errors()
     EXPECT(threw);
 }
 
+// Row order -> colTiledTC32x32 -> row order: the round trip returns the values, and an element sits where the
+// order's formula (Tensor.swift:222) puts it.
+static void test_matrix_transform()
+{
+    const size_t rows = 70, cols = 45;
+    std::vector<float> v(rows * cols);
+    for (size_t i = 0; i < v.size(); ++i) v[i] = static_cast<float>(i % 251) - 125.0f;
+    auto x = array(v, {rows, cols});
+    MatrixLayout rowLayout(x), tiled(real32F, Order::colTiledTC32x32, rows, cols);
+    EXPECT(tiled.leadingDimension == 32 * 96 && rowLayout.leadingDimension == (long long)cols);
+    float* buf = nullptr;
+    EXPECT(cudaMalloc(&buf, tiled.bufferElements() * sizeof(float)) == cudaSuccess);
+    Tensor<float> y({rows, cols});
+    MatrixTransform transform;
+    transform(1.0f, x.data(), rowLayout, 0.0f, nullptr, nullptr, buf, tiled);
+    transform(2.0f, buf, tiled, 0.0f, nullptr, nullptr, y.data(), MatrixLayout(y));
+    std::vector<float> twice(v);
+    for (float& f : twice) f *= 2.0f;
+    EXPECT(y.values() == twice);
+    const size_t r = 37, c = 40, q = r % 32;
+    const size_t off = (c / 32) * tiled.leadingDimension + (r / 32) * 1024 + (((q % 8) / 2 * 4 + q / 8) * 2 + q % 2) * 32 + c % 32;
+    float one = 0;
+    EXPECT(cudaMemcpy(&one, buf + off, sizeof one, cudaMemcpyDeviceToHost) == cudaSuccess && one == v[r * cols + c]);
+    bool threw = false;
+    try { transform(1.0f, x.data(), rowLayout, 0.0f, nullptr, nullptr, buf, MatrixLayout(real32F, Order::colTiledTC32x32, rows, cols + 1)); }
+    catch (const Error& e) { threw = e.code == cudaErrorInvalidValue; }
+    EXPECT(threw);
+    cudaFree(buf);
+}
+
 // All numbers of the (possibly nested) array stored under `key` in a JSON text, flattened.
 static std::vector<float> json_numbers(const std::string& text, const std::string& key)
 {
@@ -158,6 +188,7 @@ int main(int argc, char** argv)
     test_leftAndRightBatchMatmul();
     test_transposes_orders_and_types();
     test_dense_and_errors();
+    test_matrix_transform();
     test_lstm_golden_sequence(argc > 1 ? argv[1] : "tests/golden/lstm_kat.json");
     uint32_t status = 1;
     EXPECT(srtMatmulCheckStatus(nullptr, &status) == cudaSuccess && status == 0);
