@@ -206,6 +206,7 @@ def run_transform(dev, iters: int, flush: torch.Tensor, peaks: dict) -> list:
     cases = [("int8 16384x16384 row -> colTiledTC32x32", D.real8I, 16384, 16384, O.row, O.colTiledTC32x32),
              ("int8 16384x16384 colTiledTC32x32 -> row", D.real8I, 16384, 16384, O.colTiledTC32x32, O.row),
              ("bf16 16384x8192 row -> colTiled32", D.real16BF, 16384, 8192, O.row, O.colTiled32),
+             ("int8 16384x16384 col -> colTiledTC32x32 (transposition)", D.real8I, 16384, 16384, O.col, O.colTiledTC32x32),
              ("fp32 8192x8192 row -> col (transpose)", D.real32F, 8192, 8192, O.row, O.col),
              ("fp32 8192x8192 row -> row (copy)", D.real32F, 8192, 8192, O.row, O.row)]
     for what, dtype, rows, cols, src, dst in cases + [("fp32 row -> int8 colTiledTC32x32 16384x8192, alpha = 0.5 (quantise)", D.real32F, 16384, 8192, O.row, O.colTiledTC32x32)]:

@@ -24,6 +24,7 @@
 //   matrix_transform_tile_kernel     the contiguous axes differ (a transposition): a CTA takes 64 x 64
 //       logical elements of C, reads the operands along their own contiguous axis into a padded fp32 tile in
 //       shared memory, and writes C along its contiguous axis.
+//   matrix_transform_transpose_kernel  the same case for a pure re-layout of 1- or 2-byte elements (see below).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -266,6 +267,67 @@ matrix_transform_tile_kernel(const TransformParams p)
 #pragma unroll
             for (int k = 0; k < V; ++k) v[k] = c_cols ? tile[lr][lc + k] : tile[lr + k][lc];
             store_run<V>(p.c, logical_offset(p.c, bt, r, c), c_cols ? p.cols - c : p.rows - r, v);
+        }
+        __syncthreads();
+    }
+}
+
+// Pure transposing re-layout of 1- or 2-byte elements (alpha = 1, beta = 0, one element type, contiguous axes of
+// source and destination differ, extents multiples of the tile): the fp32 tile above would spend its time on one
+// shared-memory access per element, so here elements stay packed in 32-bit words.  X is the axis along which the
+// source is contiguous, Y the destination's.  A thread reads E = 4 / S source runs of 16 bytes (consecutive in Y),
+// transposes their E x E blocks in registers (byte permutes) into words of E consecutive Y elements, and writes
+// them to T[x][y / E]; then 16 bytes along Y are read back per thread and stored.  The word index is XOR-ed with
+// the run index of x so that the eight runs a warp writes at once fall into different banks.
+template <int S>
+__global__ void __launch_bounds__(kTransformThreads)
+matrix_transform_transpose_kernel(const TransformParams p)
+{
+    constexpr uint32_t E = 4 / S;                  // elements per word
+    constexpr uint32_t XE = 16 / S;                // elements per 16-byte run
+    constexpr uint32_t TX = 8 * XE, TY = 32 * E;   // tile: 128 x 128 (S = 1) or 64 x 64 (S = 2) elements
+    __shared__ __align__(16) uint32_t T[TX][32];
+    const bool x_is_col = runs_along_columns(p.a);
+    const uint32_t tiles_x = (x_is_col ? p.cols : p.rows) / TX, tiles_y = (x_is_col ? p.rows : p.cols) / TY;
+    const unsigned long long per_batch = static_cast<unsigned long long>(tiles_x) * tiles_y, total = per_batch * p.batch;
+    const uint32_t tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+    const char* const src = static_cast<const char*>(p.a.ptr);
+    char* const dst = static_cast<char*>(p.c.ptr);
+    for (unsigned long long t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint32_t bt = static_cast<uint32_t>(t / per_batch);
+        const uint32_t in_batch = static_cast<uint32_t>(t - bt * per_batch);
+        const uint32_t x0 = (in_batch / tiles_y) * TX, y0 = (in_batch % tiles_y) * TY;     // consecutive CTAs walk along Y
+        uint4 run[E];
+#pragma unroll
+        for (uint32_t i = 0; i < E; ++i) {
+            const uint32_t x = x0 + tx * XE, y = y0 + ty * E + i;
+            const long long off = x_is_col ? logical_offset(p.a, bt, y, x) : logical_offset(p.a, bt, x, y);
+            run[i] = *reinterpret_cast<const uint4*>(src + off * S);
+        }
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {          // word b of every run: an E x E block
+            uint32_t in[E], out[E];
+#pragma unroll
+            for (uint32_t i = 0; i < E; ++i) in[i] = b == 0 ? run[i].x : b == 1 ? run[i].y : b == 2 ? run[i].z : run[i].w;
+            if constexpr (S == 1) {
+                const uint32_t t0 = __byte_perm(in[0], in[1], 0x5140), t1 = __byte_perm(in[2], in[3], 0x5140);
+                const uint32_t t2 = __byte_perm(in[0], in[1], 0x7362), t3 = __byte_perm(in[2], in[3], 0x7362);
+                out[0] = __byte_perm(t0, t1, 0x5410); out[1] = __byte_perm(t0, t1, 0x7632);
+                out[2] = __byte_perm(t2, t3, 0x5410); out[3] = __byte_perm(t2, t3, 0x7632);
+            } else {
+                out[0] = __byte_perm(in[0], in[1], 0x5410); out[1] = __byte_perm(in[0], in[1], 0x7632);
+            }
+#pragma unroll
+            for (uint32_t k = 0; k < E; ++k) T[tx * XE + b * E + k][ty ^ (tx << 2)] = out[k];
+        }
+        __syncthreads();
+#pragma unroll
+        for (uint32_t e = threadIdx.x; e < TX * 8; e += kTransformThreads) {
+            const uint32_t q = e & 7, xi = e >> 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(&T[xi][(4 * q) ^ (((xi / XE) & 7) << 2)]);
+            const uint32_t x = x0 + xi, y = y0 + q * 4 * E;
+            const long long off = x_is_col ? logical_offset(p.c, bt, y, x) : logical_offset(p.c, bt, x, y);
+            *reinterpret_cast<uint4*>(dst + off * S) = v;
         }
         __syncthreads();
     }

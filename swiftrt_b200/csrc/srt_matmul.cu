@@ -1999,11 +1999,17 @@ cudaError_t srtMatrixTransform(const float* alpha, const void* A, const srtMatri
     auto size_of = [](int32_t t) { return t == kTypeF32 ? 4u : t == kTypeI8 ? 1u : 2u; };
     uint32_t widest = size_of(tp.a.type) > size_of(tp.c.type) ? size_of(tp.a.type) : size_of(tp.c.type);
     if (use_b && size_of(tp.b.type) > widest) widest = size_of(tp.b.type);
-    uint32_t vec = 16 / widest;
-    auto aligned = [&](const StoredMatrix& m) {
-        return reinterpret_cast<uintptr_t>(m.ptr) % (vec * size_of(m.type)) == 0 && m.ld % vec == 0 && m.batch_stride % vec == 0;
+    uint32_t narrowest = size_of(tp.a.type) < size_of(tp.c.type) ? size_of(tp.a.type) : size_of(tp.c.type);
+    if (use_b && size_of(tp.b.type) < narrowest) narrowest = size_of(tp.b.type);
+    auto aligned = [&](const StoredMatrix& m, uint32_t v) {
+        return reinterpret_cast<uintptr_t>(m.ptr) % (v * size_of(m.type)) == 0 && m.ld % v == 0 && m.batch_stride % v == 0;
     };
-    if (!aligned(tp.a) || !aligned(tp.c) || (use_b && !aligned(tp.b))) vec = 1;
+    auto all_aligned = [&](uint32_t v) { return aligned(tp.a, v) && aligned(tp.c, v) && (!use_b || aligned(tp.b, v)); };
+    // 16 bytes of the narrowest type per thread (wider operands then move as several 16-byte accesses), else 16 bytes
+    // of the widest, else element by element
+    uint32_t vec = 16 / narrowest;
+    if (!all_aligned(vec)) vec = 16 / widest;
+    if (!all_aligned(vec)) vec = 1;
     const bool stream_form = runs_along_columns(tp.a) == runs_along_columns(tp.c) &&
                              (!use_b || runs_along_columns(tp.b) == runs_along_columns(tp.c));
     if (stream_form) {
@@ -2032,6 +2038,14 @@ cudaError_t srtMatrixTransform(const float* alpha, const void* A, const srtMatri
             else     matrix_transform_stream_kernel<1, false><<<grid, kTransformThreads, 0, stream>>>(tp);
             break;
         }
+    } else if (!use_b && tp.alpha == 1.0f && tp.a.type == tp.c.type && widest <= 2 && vec == 16 / widest &&
+               tp.rows % (widest == 1 ? 128u : 64u) == 0 && tp.cols % (widest == 1 ? 128u : 64u) == 0) {
+        // a pure transposition of whole tiles of 1- or 2-byte elements: packed words, byte permutes
+        const unsigned long long edge = widest == 1 ? 128 : 64;
+        const unsigned long long tiles = (tp.rows / edge) * (tp.cols / edge) * tp.batch;
+        const unsigned grid = (unsigned)(tiles < 148ull * 8 ? tiles : 148ull * 8);
+        if (widest == 1) matrix_transform_transpose_kernel<1><<<grid, kTransformThreads, 0, stream>>>(tp);
+        else             matrix_transform_transpose_kernel<2><<<grid, kTransformThreads, 0, stream>>>(tp);
     } else {
         const unsigned long long tiles = (unsigned long long)tp.tiles_r * tp.tiles_c * tp.batch;
         const unsigned grid = (unsigned)(tiles < 148ull * 8 ? tiles : 148ull * 8);

@@ -78,6 +78,20 @@ def test_relayout_every_order_pair_is_bit_exact(srt, src, dst, trans, dtype, vec
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("src,dst", list(itertools.product(ORDERS, ORDERS)))
+@pytest.mark.parametrize("trans", [False, True])
+@pytest.mark.parametrize("dtype", [I8, BF16, F16])
+def test_whole_tile_relayouts_of_small_elements_are_bit_exact(srt, src, dst, trans, dtype):
+    """Extents that are multiples of 128: transpositions of 1- and 2-byte elements take the packed-word kernel."""
+    rng = np.random.default_rng(src * 16 + dst * 2 + trans + 1000)
+    rows, cols, batch = 256, 384, 2
+    la = _padded(dtype, src, cols if trans else rows, rows if trans else cols, batch, True)
+    lc = _padded(dtype, dst, rows, cols, batch, True)
+    a = L.to_storage(rng.integers(-100, 100, (batch, la.rows, la.cols)), la, fill=7)
+    got, ref = _run(srt, 1.0, a, la, trans, 0.0, None, None, False, lc)
+    assert np.array_equal(got, ref)
+
+
 @pytest.mark.parametrize("ta,tc", [(F32, I8), (I8, F32), (I8, I8), (BF16, F16), (F16, BF16), (F32, BF16), (I8, BF16)])
 @pytest.mark.parametrize("src,dst", [(L.ROW, L.COL_TILED_TC32X32), (L.COL_TILED_TC32X32, L.COL), (L.COL, L.COL_TILED32), (L.COL_TILED32, L.ROW)])
 def test_element_types_convert_with_one_rounding(srt, ta, tc, src, dst):
