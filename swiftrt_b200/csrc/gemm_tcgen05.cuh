@@ -247,21 +247,55 @@ struct NoPeers { uint32_t unused; };
 template <bool GATHER> struct PeerArgOf { using type = NoPeers; };
 template <> struct PeerArgOf<true> { using type = PeerMaps; };
 
+// `rehearsal` (drain_accumulator): run the whole epilogue once on whatever an idle accumulator buffer holds, with
+// every store left out.  The epilogue warps have nothing to do while the first tile is reduced, and the first
+// execution of the epilogue on an SM otherwise waits for its instructions to arrive (about 4000 cycles on the first
+// 32-row segment after another kernel has run there, against 1600-1900 for the following ones): rehearsed under the
+// reduction, the real epilogue runs from a warm instruction cache.  Only worth it where the epilogue is exposed.
+//
+// The bias values one epilogue warp needs for one tile: per 32-column chunk it drains, the value of this lane's
+// column (handed out to the other lanes by shuffle), or the value of this thread's row.  They are loaded BEFORE the
+// warp waits for the tile's accumulator, so that their latency (a trip to HBM when the cache is cold) passes under
+// the reduction instead of inside the epilogue: on a single-wave Dense product the epilogue is exposed in full.
+template <typename T, uint32_t BN, uint32_t PARTS>
+struct TileBias {
+    static constexpr uint32_t kColsPerBox = 128 / sizeof(T), kLoadsPerBox = kColsPerBox / 32, kBoxes = BN / kColsPerBox;
+    static constexpr uint32_t kChunks = ((kBoxes + PARTS - 1) / PARTS) * kLoadsPerBox;
+    float col[kChunks];
+    float row;
+};
+
+template <typename T, uint32_t BN, uint32_t PARTS>
+__device__ __forceinline__ void load_tile_bias(const GemmParams& p, uint32_t part, uint32_t quarter, uint32_t lane, uint32_t m0,
+                                               uint32_t n0, TileBias<T, BN, PARTS>& tb)
+{
+    using TB = TileBias<T, BN, PARTS>;
+    const T* const bias = static_cast<const T*>(p.bias);
+    const uint32_t row = m0 + quarter * 32 + lane;
+    tb.row = 0.0f;
+    if (p.bias_mode == 2 && row < p.M) tb.row = to_float<T>(__ldg(bias + static_cast<long long>(row) * p.bias_stride));
+#pragma unroll
+    for (uint32_t c = 0; c < TB::kChunks; ++c) {
+        const uint32_t bx = part + (c / TB::kLoadsPerBox) * PARTS;
+        const uint32_t col = n0 + bx * TB::kColsPerBox + (c % TB::kLoadsPerBox) * 32 + lane;
+        tb.col[c] = 0.0f;
+        if (p.bias_mode == 1 && bx < TB::kBoxes && col < p.N) tb.col[c] = to_float<T>(__ldg(bias + static_cast<long long>(col) * p.bias_stride));
+    }
+}
+
 template <typename T, uint32_t BN, bool DUAL = false, uint32_t PARTS = 1, bool GATHER = false>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tmap_out, uint32_t staging,
                                                   uint32_t part, uint32_t acc, uint32_t quarter, uint32_t lane,
-                                                  uint32_t batch, uint32_t m0, uint32_t n0, uint32_t acc2 = 0,
-                                                  const PeerMaps* peers = nullptr)
+                                                  uint32_t batch, uint32_t m0, uint32_t n0, TileBias<T, BN, PARTS> tb,
+                                                  uint32_t acc2 = 0, const PeerMaps* peers = nullptr, uint32_t rehearsal = 0)
 {
     constexpr uint32_t kColsPerBox = 128 / sizeof(T);            // 64 (16-bit) or 32 (fp32)
     constexpr uint32_t kLoadsPerBox = kColsPerBox / 32;
     constexpr uint32_t kBoxes = BN / kColsPerBox;
     T* const out = static_cast<T*>(p.out);
-    const T* const bias = static_cast<const T*>(p.bias);
     const uint32_t row = m0 + quarter * 32 + lane;
     const uint32_t lane_addr = (quarter * 32u) << 16;
-    float row_bias = 0.0f;
-    if (p.bias_mode == 2 && row < p.M) row_bias = to_float<T>(bias[static_cast<long long>(row) * p.bias_stride]);
+    const float row_bias = tb.row;
     T* row_ptr = out + static_cast<long long>(batch) * p.out_batch_stride + static_cast<long long>(row) * p.ldo;
 
     for (uint32_t bx = part; bx < kBoxes; bx += PARTS) {
@@ -275,10 +309,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
 #pragma unroll
         for (uint32_t h = 0; h < kLoadsPerBox; ++h) {
             const uint32_t col0 = box_col + h * 32;
-            // one coalesced bias load per 32 columns, handed out by shuffle below
-            float my_bias = 0.0f;
-            if (p.bias_mode == 1 && col0 + lane < p.N)
-                my_bias = to_float<T>(__ldg(bias + static_cast<long long>(col0 + lane) * p.bias_stride));
+            const float my_bias = tb.col[h];      // this lane's column of the chunk, handed out by shuffle below
             if (h == 0) {
                 if constexpr (kLoadsPerBox == 2) tmem_ld_wait_regs2(raw[0], raw[kLoadsPerBox - 1]);
                 else tmem_ld_wait_regs(raw[0]);
@@ -302,7 +333,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
             }
             activate_chunk(p.act, v);
             if (!p.out_tma) {
-                if (row < p.M && col0 < p.N) store_row_chunk<T>(p, row_ptr, col0, v);
+                if (row < p.M && col0 < p.N && !rehearsal) store_row_chunk<T>(p, row_ptr, col0, v);
             } else if constexpr (sizeof(T) == 4) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) packed[j] = __float_as_uint(v[j]);
@@ -326,7 +357,9 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
             __syncwarp();
             bool multicast = false;
             if constexpr (GATHER) multicast = p.multicast != 0;
-            if (!multicast) {
+            if (rehearsal) {
+                __syncwarp();
+            } else if (!multicast) {
                 if (lane == 0) {
                     tma_store_3d(tmap_out, staging, static_cast<int32_t>(box_col), static_cast<int32_t>(m0 + quarter * 32),
                                  static_cast<int32_t>(batch));
@@ -358,6 +391,9 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
                 __syncwarp();          // every lane has read the segment before the next one is staged
             }
         }
+        // the next box's bias values move to the front (static indices: the array stays in registers)
+#pragma unroll
+        for (uint32_t c = 0; c + kLoadsPerBox < TileBias<T, BN, PARTS>::kChunks; ++c) tb.col[c] = tb.col[c + kLoadsPerBox];
     }
 }
 
@@ -587,26 +623,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t quarter = warp & 3;       // TMEM lanes this warp may read
         uint32_t local = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+        // The first pass of the loop is the rehearsal (see drain_accumulator): same call site, hence the same
+        // instructions, on the second accumulator buffer, which nothing writes before the second tile.
+        uint32_t rehearsal = (!GATHER && p.epilogue == kEpilogueStore) ? 1u : 0u;
+        for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles;) {
             const TileCoord tc = decode_tile(p, tile, BN);
             uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
-            const uint32_t buf = local & 1;
+            const uint32_t buf = rehearsal ? 1u : (local & 1);
             const uint32_t acc_phase = (local >> 1) & 1;
-            if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
-            tc_fence_after_sync();
+            TileBias<OutT, BN, 2> tile_bias = {};
+            if (!rehearsal) {
+                load_tile_bias<OutT, BN, 2>(p, (warp - 2) >> 2, quarter, lane, m0, n0, tile_bias);  // under the reduction
+                if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                tc_fence_after_sync();
+            }
             if constexpr (GATHER)
                 drain_accumulator<OutT, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                             (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
-                                                            0, &peer_maps);
+                                                            tile_bias, 0, &peer_maps);
             else if (sizeof(OutT) == 2 && p.epilogue == kEpilogueLstm) {
                 if constexpr (sizeof(OutT) == 2)
                     drain_accumulator_lstm<OutT, BN, 2>(p, (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, m0, n0);
             } else
                 drain_accumulator<OutT, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
-                                                      (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
+                                                      (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0, tile_bias,
+                                                      0, nullptr, rehearsal);
+            if (rehearsal) { rehearsal = 0; continue; }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+            tile += gridDim.x;
+            ++local;
         }
         drain_finish(lane);
         if (!ok) {
@@ -821,27 +868,37 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t quarter = warp & 3;
         uint32_t local = 0;
         bool ok = true;
-        for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++local) {
+        // first pass = rehearsal, as in gemm_tcgen05_kernel
+        uint32_t rehearsal = (!GATHER && p.epilogue == kEpilogueStore) ? 1u : 0u;
+        for (uint32_t tile = pair_id; ok && tile < p.num_tiles;) {
             const TileCoord tc = decode_tile(p, tile, BN);
             uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             m0 = m0 * 2 + cta_rank * kTileM;
-            const uint32_t buf = local & 1;
+            const uint32_t buf = rehearsal ? 1u : (local & 1);
             const uint32_t acc_phase = (local >> 1) & 1;
-            if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
-            tc_fence_after_sync();
+            TileBias<T, BN, 2> tile_bias = {};
+            if (!rehearsal) {
+                load_tile_bias<T, BN, 2>(p, (warp - 2) >> 2, quarter, lane, m0, n0, tile_bias);      // under the reduction
+                if (!mbar_wait_cluster(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
+                tc_fence_after_sync();
+            }
             if constexpr (GATHER)
                 drain_accumulator<T, BN, false, 2, true>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
                                                          (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0,
-                                                         0, &peer_maps);
+                                                         tile_bias, 0, &peer_maps);
             else if (sizeof(T) == 2 && p.epilogue == kEpilogueLstm) {
                 if constexpr (sizeof(T) == 2)
                     drain_accumulator_lstm<T, BN, 2>(p, (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, m0, n0);
             } else
                 drain_accumulator<T, BN, false, 2>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096,
-                                                   (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0);
+                                                   (warp - 2) >> 2, tmem_base + buf * BN, quarter, lane, batch, m0, n0, tile_bias,
+                                                   0, nullptr, rehearsal);
+            if (rehearsal) { rehearsal = 0; continue; }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&tmem_empty_bar[buf]), 0);
+            tile += num_pairs;
+            ++local;
         }
         drain_finish(lane);
         if (!ok && lane == 0) raise_abort(kStatusEpilogueTimeout);
@@ -1061,10 +1118,12 @@ gemm_tcgen05_split_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t batch = tc.obatch, m0 = tc.m0, n0 = tc.n0;
             const uint32_t buf = local % kAccBufs;
             const uint32_t acc_phase = (local / kAccBufs) & 1;
+            TileBias<T, BN, 1> tile_bias;
+            load_tile_bias<T, BN, 1>(p, 0, quarter, lane, m0, n0, tile_bias);                        // under the reduction
             if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), acc_phase, &abort_flag, p.wait_cycles)) { ok = false; break; }
             tc_fence_after_sync();
             drain_accumulator<T, BN, true, 1>(p, &tmap_out, smem_base + stages * kStageBytes + (warp - 2) * 4096, 0,
-                                              tmem_base + buf * 2 * BN, quarter, lane, batch, m0, n0,
+                                              tmem_base + buf * 2 * BN, quarter, lane, batch, m0, n0, tile_bias,
                                               tmem_base + buf * 2 * BN + BN);
             tc_fence_before_sync();
             __syncwarp();
