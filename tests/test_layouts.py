@@ -99,3 +99,21 @@ def test_argument_checks_need_no_device(lib):
     assert call(row, row, beta=one) == lib.cudaErrorInvalidValue                             # beta != 0 without B
     empty = _layout(lib, 0, L.ROW, 0, 8, ld=8)
     assert call(empty, empty) == lib.cudaSuccess                                             # nothing to do, no launch
+
+
+def test_host_mirror_layouts_without_a_device():
+    import torch
+    import swiftrt_b200 as srt
+    x = torch.empty((3, 5), dtype=torch.int8)
+    lx = srt.MatrixLayout.of(x)
+    assert (lx.order, lx.rows, lx.cols, lx.leading_dimension, lx.type) == (srt.Order.row, 3, 5, 5, srt.DataType.real8I)
+    lt = srt.MatrixLayout.of(x.t())                       # a transposed view is the col order (strides (1, rows))
+    assert (lt.order, lt.rows, lt.cols, lt.leading_dimension) == (srt.Order.col, 5, 3, 5)
+    lb = srt.MatrixLayout.of(torch.empty((4, 6, 8), dtype=torch.bfloat16))
+    assert (lb.batch_count, lb.batch_stride, lb.elements) == (4, 48, 4 * 48)
+    tiled = srt.MatrixLayout(srt.DataType.real8I, srt.Order.colTiledTC32x32, 33, 70)
+    assert tiled.leading_dimension == 32 * 64 and tiled.elements == 2 * 2048 + 2048
+    with pytest.raises(srt.MatmulError):
+        srt.MatrixLayout(srt.DataType.real8I, srt.Order.colTiledTC32x8, 8, 32)
+    with pytest.raises(ValueError):
+        srt.matrix_transform(x.view(-1), lx, lx)          # host tensors are refused: there is no CPU path
