@@ -50,12 +50,38 @@ struct OperandParams {
     uint32_t kstep;         // descriptor start-address increment per MMA (bytes >> 4)
 };
 
+// Division of a number below 2^31 by a divisor fixed on the host: floor(n / d) = umulhi(n, mul) >> shr with
+// mul = ceil(2^(31 + ceil(log2 d)) / d) (Granlund-Montgomery); d = 1 is passed through.  The tile walk divides by
+// five such numbers per tile, and a 32-bit hardware-less division is some thirty dependent instructions: about
+// 600 cycles per tile on each role's path, which is most of what a tile costs when it has one or two k-blocks.
+struct FastDiv {
+    uint32_t mul, shr, d;
+};
+
+inline FastDiv make_fast_div(uint32_t d)
+{
+    FastDiv f = {0u, 0u, d == 0 ? 1u : d};
+    if (f.d == 1) return f;
+    uint32_t lg = 0;
+    while ((1ull << lg) < f.d) ++lg;                       // ceil(log2 d)
+    const uint32_t pw = 31 + lg;
+    f.mul = static_cast<uint32_t>(((1ull << pw) + f.d - 1) / f.d);
+    f.shr = pw - 32;
+    return f;
+}
+
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f)
+{
+    return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.shr);
+}
+
 struct GemmParams {
     uint32_t M, N, K, batch;
     uint32_t tiles_m, tiles_n, tiles_per_batch, num_tiles;
     uint32_t k_blocks, kb_elems, group_m;
     uint32_t k_splits, kb_per_split;   // split-K: work unit = (tile, split); num_tiles counts units
     uint32_t tiles_total;              // output tiles over all batch items (= num_tiles / k_splits)
+    FastDiv by_tiles_total, by_tiles_per_batch, by_per_group, by_group_m, by_group_tail;   // set_tile_walk()
     OperandParams a, b;
     uint32_t idesc;
     uint32_t stage_tx_bytes;
@@ -142,20 +168,32 @@ struct TileCoord {
     uint32_t batch, obatch, m0, n0, kb0, kb1;
 };
 
+// the divisors of decode_tile, from the tile counts (host side, after tiles_m, tiles_n, tiles_per_batch, tiles_total
+// and group_m are set)
+inline void set_tile_walk(GemmParams& p)
+{
+    p.by_tiles_total = make_fast_div(p.tiles_total);
+    p.by_tiles_per_batch = make_fast_div(p.tiles_per_batch);
+    p.by_per_group = make_fast_div(p.group_m * p.tiles_n);
+    p.by_group_m = make_fast_div(p.group_m);
+    p.by_group_tail = make_fast_div(p.tiles_m % p.group_m);
+}
+
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, uint32_t unit, uint32_t bn)
 {
     TileCoord c;
-    const uint32_t split = unit / p.tiles_total;
+    const uint32_t split = fast_div(unit, p.by_tiles_total);
     const uint32_t tile = unit - split * p.tiles_total;
-    c.batch = tile / p.tiles_per_batch;
+    c.batch = fast_div(tile, p.by_tiles_per_batch);
     uint32_t t = tile - c.batch * p.tiles_per_batch;
     uint32_t per_group = p.group_m * p.tiles_n;
-    uint32_t group = t / per_group;
+    uint32_t group = fast_div(t, p.by_per_group);
     uint32_t first_m = group * p.group_m;
-    uint32_t gm = min(p.group_m, p.tiles_m - first_m);
+    uint32_t gm = min(p.group_m, p.tiles_m - first_m);      // group_m, or what is left of the rows in the last group
     uint32_t r = t - group * per_group;
-    c.m0 = (first_m + r % gm) * kTileM;
-    c.n0 = (r / gm) * bn;
+    const uint32_t col = fast_div(r, gm == p.group_m ? p.by_group_m : p.by_group_tail);
+    c.m0 = (first_m + (r - col * gm)) * kTileM;
+    c.n0 = col * bn;
     c.obatch = split * p.batch + c.batch;
     c.kb0 = split * p.kb_per_split;
     c.kb1 = min(p.k_blocks, c.kb0 + p.kb_per_split);
@@ -271,14 +309,16 @@ __device__ __forceinline__ void load_tile_bias(const GemmParams& p, uint32_t par
 {
     using TB = TileBias<T, BN, PARTS>;
     const T* const bias = static_cast<const T*>(p.bias);
-    const uint32_t row = m0 + quarter * 32 + lane;
     tb.row = 0.0f;
+#pragma unroll
+    for (uint32_t c = 0; c < TB::kChunks; ++c) tb.col[c] = 0.0f;
+    if (p.bias_mode == 0) return;
+    const uint32_t row = m0 + quarter * 32 + lane;
     if (p.bias_mode == 2 && row < p.M) tb.row = to_float<T>(__ldg(bias + static_cast<long long>(row) * p.bias_stride));
 #pragma unroll
     for (uint32_t c = 0; c < TB::kChunks; ++c) {
         const uint32_t bx = part + (c / TB::kLoadsPerBox) * PARTS;
         const uint32_t col = n0 + bx * TB::kColsPerBox + (c % TB::kLoadsPerBox) * 32 + lane;
-        tb.col[c] = 0.0f;
         if (p.bias_mode == 1 && bx < TB::kBoxes && col < p.N) tb.col[c] = to_float<T>(__ldg(bias + static_cast<long long>(col) * p.bias_stride));
     }
 }

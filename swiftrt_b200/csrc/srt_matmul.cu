@@ -836,6 +836,7 @@ cudaError_t prepare_tc(const Plan& plan, Prepared& pr)
     gp.k_blocks = (uint32_t)((Q.K + gp.kb_elems - 1) / gp.kb_elems);
     gp.kb_per_split = plan.splits > 1 ? plan.kb_per_split : gp.k_blocks;
     gp.group_m = pair ? 8 : 16;                           // 2048 rows of A per group either way
+    set_tile_walk(gp);
     gp.stages = (uint32_t)plan.pub.stages;
     gp.stage_tx_bytes = kATileBytes + b_rows * kRowBytes;
     // instruction descriptor: fp32 accumulator, input format, majorness, N >> 3, M >> 4
@@ -934,6 +935,7 @@ cudaError_t prepare_x3(const Plan& plan, Prepared& pr)
     gp.k_blocks = (uint32_t)((Q.K + 31) / 32);
     gp.kb_per_split = gp.k_blocks;
     gp.group_m = 8;
+    set_tile_walk(gp);
     gp.stages = (uint32_t)plan.pub.stages;
     gp.stage_tx_bytes = 0;
     // instruction descriptors: fp32 accumulator, both operands K-major, N = tile width, M = 256
