@@ -156,8 +156,9 @@ __device__ __forceinline__ float tf32_low_part(uint32_t x)
 {
     const float v = __uint_as_float(x);
     const float lo = v - __uint_as_float(x & 0xffffe000u);
-    const float small = lo != 0.0f ? lo : v * 9.31322574615478515625e-10f;   // 2^-30
-    return (x & 0x7f800000u) == 0x7f800000u ? v : small;
+    // |lo| > 0 is false for a zero low part and for the NaN that inf - inf or NaN - NaN gives, and v 2^-30 is then
+    // the stand-in of a finite v, and v itself for an infinity or a NaN: one ordered comparison covers all cases
+    return fabsf(lo) > 0.0f ? lo : v * 9.31322574615478515625e-10f;          // 2^-30
 }
 
 // work unit -> tile coordinates; m-tiles are visited in groups of group_m so that the CTAs running
