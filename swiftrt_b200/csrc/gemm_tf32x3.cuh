@@ -240,10 +240,8 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         st_shared_remote_u32(smem_u32(const_cast<uint32_t*>(&abort_flag)), cta_rank ^ 1u, 1u);
         atomicOr(&g_gemm_status, code);
     };
-    // the loads of this CTA for k-block iteration j of the pair's work list (every tile has p.k_blocks of them)
-    auto issue_loads = [&](uint32_t j) {
-        const uint32_t t_local = j / p.k_blocks, kb = j - t_local * p.k_blocks, stage = j % kStages;
-        const TileCoord tc = decode_tile(p, pair_id + t_local * num_pairs, BN);
+    // the loads of this CTA for k-block kb of tile tc into a stage
+    auto issue_stage = [&](const TileCoord& tc, uint32_t kb, uint32_t stage) {
         const uint32_t m0 = tc.m0 * 2 + cta_rank * kTileM, n0 = tc.n0 + cta_rank * (BN / 2);
         const uint32_t sa = smem_base + stage * kStageBytes;
         const uint32_t sbh = sa + 2 * kX3TileBytes, sbc = sbh + kBTileBytes;
@@ -255,6 +253,11 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tma_load_3d_pair(sbh, &tmap_bh, bar_b, static_cast<int32_t>(kb * 32), n0, tc.batch * p.b.batch_mul);
         tma_load_3d_pair(sbc, &tmap_bc, bar_b, static_cast<int32_t>(kb * 64), n0, tc.batch * p.b.batch_mul);
     };
+    // the same for k-block iteration j of the pair's work list (every tile has p.k_blocks of them): the teardown's form
+    auto issue_loads = [&](uint32_t j) {
+        const uint32_t t_local = j / p.k_blocks;
+        issue_stage(decode_tile(p, pair_id + t_local * num_pairs, BN), j - t_local * p.k_blocks, j % kStages);
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -263,9 +266,10 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             bool ok = true;
             grid_dependency_wait();                  // Bh / Bc come from the pack kernel launched just before
             for (uint32_t tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+                const TileCoord tc = decode_tile(p, tile, BN);       // once per tile: nothing is divided between a freed stage and its loads
                 for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
                     if (!mbar_wait_cluster(smem_u32(&empty_bar[stage]), phase ^ 1, &abort_flag, p.wait_cycles)) { ok = false; break; }
-                    issue_loads(issued);
+                    issue_stage(tc, kb, stage);
                     ++issued;
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
