@@ -56,7 +56,7 @@ KERNEL_NAMES = {1: "gemm_simt_kernel", 2: "gemm_tcgen05_kernel", 3: "gemm_tcgen0
                 5: "gemm_tf32x3_pair_kernel"}
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum from one ncu capture, see profiles/), one GPU,
 # default plan: workload -> (kernel id the figure belongs to, bytes)
-MEASURED_TRAFFIC = {"c5": (3, 9.38e9), "c2": (3, 42.08e6), "c3": (2, 8.5e6), "c4": (5, 316.8e6), "bf16_8192": (3, 1.206e9)}
+MEASURED_TRAFFIC = {"c5": (3, 9.38e9), "c2": (3, 42.08e6), "c3": (2, 8.5e6), "c4": (5, 317.8e6), "bf16_8192": (3, 1.206e9)}
 
 
 def peaks():
